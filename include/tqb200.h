@@ -1,0 +1,191 @@
+/*
+ * tqb200.h -- C ABI of libtqb200.so, the sm_100a (B200) implementation of the TurboQuant hot path.
+ *
+ * Every entry point takes raw DEVICE pointers (unless a parameter says "host"), explicit sizes and
+ * a CUDA stream (cudaStream_t passed as void*; NULL = the legacy default stream).  The caller
+ * allocates every output and every workspace; nothing here allocates device memory.  All calls
+ * are stream-ordered and asynchronous; none synchronises.  Return value: 0 on success, a negative
+ * TQB_ERR_* code otherwise, with a human-readable message available from tqb_last_error()
+ * (thread-local).  No exception crosses this boundary.
+ *
+ * Each declaration cites the interface of the upstream project (ansschh/turboquant-kv, paths
+ * relative to that repository) that it replaces.
+ *
+ * Conventions shared by all entry points (upstream turboquant_kv/reference.py):
+ *   - forward rotation  y = unit @ R^T  (y_j = sum_k unit_k R[j][k], reference.py:301);
+ *     inverse rotation  x = y @ R       (reference.py:362);  R is (dim, dim) float32, row-major;
+ *   - code = number of boundaries strictly below y (torch.searchsorted, left; reference.py:311);
+ *   - a packed row is `bits` planes of ceil(dim/8) bytes, plane i holds bit i of every code,
+ *     dimension 8m+t sits at bit 7-t of byte m, padding bits are zero (reference.py:191-224);
+ *     packed_dim = bits * ceil(dim/8).
+ */
+#ifndef TQB200_H_
+#define TQB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQB_OK 0
+#define TQB_ERR_INVALID (-1)     /* bad argument (shape, bit width, null pointer, alignment) */
+#define TQB_ERR_UNSUPPORTED (-2) /* valid upstream, outside what this build implements */
+#define TQB_ERR_CUDA (-3)        /* a CUDA runtime call failed; message carries its text */
+#define TQB_ERR_WORKSPACE (-4)   /* workspace smaller than tqb_*_workspace_bytes() */
+
+/* element type of floating-point inputs */
+#define TQB_F32 0
+#define TQB_F16 1
+#define TQB_BF16 2
+
+/* ABI version of this header (bumped on any signature change). */
+int tqb_abi_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char* tqb_last_error(void);
+/* Number of kernels launched by this library in this process (all threads), for accounting. */
+int64_t tqb_launch_count(void);
+
+/*
+ * Where quantised rows are written.  Input rows are numbered r = a * inner + b (0 <= b < inner).
+ *   dense / cache mode (slots == NULL):
+ *       out_row = a * stride_a + b * stride_b + offset + (pos ? pos[a / pos_div] : 0)
+ *   paged mode (slots != NULL): a = token, b = kv head (inner = kv_heads);
+ *       out_row = ((slots[a] / block_size) * inner + b) * block_size + slots[a] % block_size
+ *       tokens with slots[a] < 0 are skipped.
+ * A plain (n, packed_dim) output is {inner = 1, stride_a = 1, stride_b = 0, offset = 0}.
+ */
+typedef struct tqb_rowmap {
+    int64_t inner;
+    int64_t stride_a;
+    int64_t stride_b;
+    int64_t offset;
+    const int32_t* pos; /* device, optional */
+    int64_t pos_div;
+    const int64_t* slots; /* device, optional */
+    int32_t block_size;
+} tqb_rowmap;
+
+/* ---- bit-plane pack / unpack ------------------------------------------------------------
+ * Replaces torch.ops.turboquant.pack_codes / unpack_codes (csrc/registration.cpp:98-99,
+ * csrc/cuda/quant_pack.cu:52-81,117-148) and reference.py:191-255.
+ * codes (n, dim) uint8 <-> packed (n, bits*ceil(dim/8)) uint8; bits in 1..8, any dim >= 1. */
+int tqb_pack_codes(const uint8_t* codes, int64_t n, int dim, int bits, uint8_t* packed, void* stream);
+int tqb_unpack_codes(const uint8_t* packed, int64_t n, int dim, int bits, uint8_t* codes, void* stream);
+
+/* ---- Algorithm 1: quantize / dequantize ---------------------------------------------------
+ * Replaces reference.quantize_mse (reference.py:263-317), torch.ops.turboquant.rotate_and_quantize
+ * (csrc/registration.cpp:85-88, csrc/cuda/rotate_fused.cu:140-190) and
+ * turboquant::quantize_vectors (csrc/core/turboquant_core.cpp:277-343).
+ * x: (n, dim) rows of `dtype`, consecutive rows x_stride elements apart; arithmetic in float32.
+ * packed / norms are addressed through `map` (NULL = dense); packed rows are packed_dim bytes
+ * apart.  bits in 1..4, dim in 8..256 and a multiple of 8. */
+int tqb_quantize_mse(const void* x, int dtype, int64_t n, int dim, int64_t x_stride,
+                     const float* rotation, const float* boundaries, int bits, uint8_t* packed,
+                     float* norms, const tqb_rowmap* map, void* stream);
+
+/* Replaces reference.dequantize_mse (reference.py:320-367) and turboquant::dequantize_vectors
+ * (csrc/core/turboquant_core.cpp:345-401).  out: (n, dim) of out_dtype. */
+int tqb_dequantize_mse(const uint8_t* packed, const float* norms, int64_t n, int dim,
+                       const float* rotation, const float* centroids, int bits, void* out,
+                       int out_dtype, void* stream);
+
+/* ---- Algorithm 2: quantize / dequantize with the 1-bit QJL residual ------------------------
+ * Replaces reference.quantize_prod (reference.py:392-469).  `boundaries`/`centroids` are the
+ * (bits-1)-bit codebook, `qjl` the (dim, dim) Gaussian matrix S, `qjl_rot` = S @ R^T (dim, dim)
+ * precomputed by the caller.  Outputs (dense): mse_packed (n, (bits-1)*ceil(dim/8)), signs
+ * (n, ceil(dim/8)), res_norms (n), norms (n).  bits in 2..5. */
+int tqb_quantize_prod(const void* x, int dtype, int64_t n, int dim, int64_t x_stride,
+                      const float* rotation, const float* boundaries, const float* centroids,
+                      const float* qjl_rot, int bits, uint8_t* mse_packed, uint8_t* signs,
+                      float* res_norms, float* norms, void* stream);
+
+/* Replaces reference.dequantize_prod (reference.py:472-533). */
+int tqb_dequantize_prod(const uint8_t* mse_packed, const uint8_t* signs, const float* res_norms,
+                        const float* norms, int64_t n, int dim, const float* rotation,
+                        const float* centroids, const float* qjl, int bits, void* out,
+                        int out_dtype, void* stream);
+
+/* ---- operator-level attention over one packed stream ---------------------------------------
+ * Replaces torch.ops.turboquant.attention_scores_packed (csrc/registration.cpp:89-92,
+ * csrc/cuda/attn_scores.cu:111-178, turboquant_kv/ops.py:131-194): query (bh, dim) float32,
+ * one packed key stream (seq, packed_dim) shared by all bh queries; scores (bh, seq) float32,
+ * UNSCALED: scores[i][s] = key_norms[s] * sum_j (R q_i)_j * centroids[code_sj]. */
+int tqb_attention_scores_packed(const float* query, int64_t bh, int dim, const uint8_t* packed_keys,
+                                const float* key_norms, int64_t seq, const float* centroids,
+                                const float* rotation, int bits, float* scores, void* stream);
+
+/* Replaces torch.ops.turboquant.attention_values_packed (csrc/registration.cpp:93-96,
+ * csrc/cuda/attn_values.cu:121-187, turboquant_kv/ops.py:202-246):
+ * out[i] = (sum_s w[i][s] * value_norms[s] * centroids[code_s,:]) @ rotation_T, out (bh, dim). */
+int tqb_attention_values_packed(const float* weights, int64_t bh, int64_t seq, int dim,
+                                const uint8_t* packed_values, const float* value_norms,
+                                const float* centroids, const float* rotation_T, int bits,
+                                float* out, void* stream);
+
+/* ---- KV-cache append ---------------------------------------------------------------------
+ * Replaces the per-head quantize loop of QuantizedKVCache.append (turboquant_kv/cache.py:148-214)
+ * and of _LayerQuantStore.append (turboquant_kv/hf_integration.py:111-182): quantises n key rows
+ * and n value rows (each (n, dim), x_stride apart) in ONE launch, keys with (rot_k, bnd_k, kbits),
+ * values with (rot_v, bnd_v, vbits), and scatters them through `map` into the cache arrays. */
+int tqb_kv_append(const void* key, const void* value, int dtype, int64_t n, int dim, int64_t x_stride,
+                  const float* rot_k, const float* bnd_k, int kbits, const float* rot_v,
+                  const float* bnd_v, int vbits, uint8_t* k_packed, float* k_norms,
+                  uint8_t* v_packed, float* v_norms, const tqb_rowmap* map, void* stream);
+
+/* ---- fused decode attention over a packed KV cache ------------------------------------------
+ * Replaces QuantizedKVCache.attention_scores -> softmax -> attention_values
+ * (turboquant_kv/cache.py:282-339, vllm_plugin/__init__.py:391-403) and the dequantise-all step
+ * of TurboQuantCache.update (turboquant_kv/hf_integration.py:373-375) for one new token per
+ * sequence, without materialising dense K/V.
+ *
+ * query (batch, q_heads, dim) of q_dtype; q_heads = group * kv_heads, query head h uses KV head
+ * h / group.  out (batch, q_heads, dim) of out_dtype.  softmax(scale * q.k) over the first
+ * seq_lens[b] tokens (device int32[batch]); max_len (host) >= every seq_lens[b].
+ *
+ * Contiguous cache (block_tables == NULL): k_packed (batch, kv_heads, max_seq, pk) uint8,
+ * k_norms (batch, kv_heads, max_seq) float32, same for v; `max_seq` is the row pitch.
+ * Paged cache (block_tables != NULL): k_packed (num_blocks, kv_heads, block_size, pk), norms
+ * (num_blocks, kv_heads, block_size); block_tables (batch, max_blocks) int32 device;
+ * block_size a multiple of 16.
+ *
+ * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  workspace: device scratch of at least
+ * tqb_decode_attention_workspace_bytes(...) bytes, 256-byte aligned, not shared between calls that
+ * may overlap on the device. */
+size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, int kv_heads, int dim,
+                                            int64_t max_len);
+int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
+                         int dim, const uint8_t* k_packed, const float* k_norms,
+                         const uint8_t* v_packed, const float* v_norms, int64_t max_seq,
+                         const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
+                         int max_blocks, int block_size, const float* rot_k, const float* cent_k,
+                         int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,
+                         void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                         void* stream);
+
+/* ---- packed-code inner-product scan with top-k ------------------------------------------------
+ * Replaces turboquant::search_packed (csrc/core/turboquant_core.cpp:407-514) as bound by
+ * turboquant_kv._core.Index.search (csrc/core/bindings.cpp:100-135) and
+ * TurboQuantIndex._search_mse (turboquant_kv/search.py:206-227).
+ * queries (nq, dim) float32; packed (n, packed_dim); norms (n); out_scores (nq, k) float32
+ * descending, out_ids (nq, k) int64 = row + id_offset; ties ordered by ascending id; slots beyond
+ * n are filled with -inf / -1.  bits in 2..4 (1 through the generic path), dim a multiple of 8,
+ * k in 1..TQB_SCAN_MAX_K. */
+#define TQB_SCAN_MAX_K 256
+size_t tqb_scan_topk_workspace_bytes(int nq, int64_t n, int dim, int bits, int k);
+int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed, const float* norms,
+                  int64_t n, int dim, int bits, const float* rotation, const float* centroids,
+                  int k, int64_t id_offset, void* workspace, size_t workspace_bytes,
+                  float* out_scores, int64_t* out_ids, void* stream);
+
+/* Merge `parts` sorted candidate lists per query (the row-sharded search: one list per shard,
+ * gathered over NCCL) into the global top-k with the same ordering rule.
+ * scores (nq, parts, k) float32, ids (nq, parts, k) int64 -> out (nq, k). */
+int tqb_topk_merge(const float* scores, const int64_t* ids, int nq, int parts, int k,
+                   float* out_scores, int64_t* out_ids, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQB200_H_ */

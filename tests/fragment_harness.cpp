@@ -1,0 +1,144 @@
+// fragment_harness.cpp -- host replay of one warp tile of the decode-attention / scan kernels.
+//
+// Compiled by tests/test_fragment_maps.py with g++ against csrc/decode_bits.cuh (the very header
+// the CUDA kernels include).  For every one of the 32 lanes it performs the gathers, index-word
+// arithmetic and table lookups the kernel performs, places the results in the A / B operand
+// positions defined by mma.sync.m16n8k16, multiplies on the CPU, and returns the product so that
+// the test can compare it with a direct evaluation on unpacked codes.
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "decode_bits.cuh"
+
+using namespace tqb;
+
+namespace {
+
+// scores[row][col] += sum_k A[row][k] * B[k][col] with operands given per lane in fragment form.
+struct Frag {
+    float a[32][8];  // a0..a7 per lane
+    float b[32][4];  // b0..b3 per lane
+};
+
+void mma_replay(const Frag& f, float (&C)[16][8]) {
+    float A[16][16] = {}, B[16][8] = {};
+    for (int lane = 0; lane < 32; lane++) {
+        const int g = lane >> 2, t = lane & 3;
+        A[g][2 * t] = f.a[lane][0];          A[g][2 * t + 1] = f.a[lane][1];
+        A[g + 8][2 * t] = f.a[lane][2];      A[g + 8][2 * t + 1] = f.a[lane][3];
+        A[g][2 * t + 8] = f.a[lane][4];      A[g][2 * t + 9] = f.a[lane][5];
+        A[g + 8][2 * t + 8] = f.a[lane][6];  A[g + 8][2 * t + 9] = f.a[lane][7];
+        B[2 * t][g] = f.b[lane][0];          B[2 * t + 1][g] = f.b[lane][1];
+        B[2 * t + 8][g] = f.b[lane][2];      B[2 * t + 9][g] = f.b[lane][3];
+    }
+    for (int r = 0; r < 16; r++)
+        for (int c = 0; c < 8; c++) {
+            float s = 0.f;
+            for (int k = 0; k < 16; k++) s += A[r][k] * B[k][c];
+            C[r][c] += s;
+        }
+}
+
+template <int D, int BITS>
+void key_tile(const uint8_t* tile, const float* cent, const float* q /*[8][D]*/, float* out /*[16][8]*/) {
+    constexpr int NW = KeyWords<D>::NW;
+    const int pitch = BITS * D / 8;
+    float C[16][8] = {};
+    for (int ks = 0; ks < D / 16; ks++) {
+        Frag f{};
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            uint32_t P[NW][4];
+            gather_key_words<D, BITS>(tile, pitch, g, t, P);
+            for (int half = 0; half < 2; half++) {
+                const int e = 2 * ks + half;
+                for (int second = 0; second < 2; second++) {
+                    int u, word, bl;
+                    key_element_slot<D>(e, second != 0, u, word, bl);
+                    const uint32_t iw = pair_index_word<BITS>(P[word], u);
+                    const uint32_t x = (iw >> (8 * bl)) & 0xFF;
+                    int clo, chi;
+                    pair_index_codes<BITS>(x, clo, chi);
+                    f.a[lane][4 * half + 2 * second + 0] = cent[clo];
+                    f.a[lane][4 * half + 2 * second + 1] = cent[chi];
+                }
+                int dlo, dhi;
+                pair_dims(D, t, e, dlo, dhi);
+                f.b[lane][2 * half + 0] = q[g * D + dlo];
+                f.b[lane][2 * half + 1] = q[g * D + dhi];
+            }
+        }
+        mma_replay(f, C);
+    }
+    std::memcpy(out, C, sizeof(C));
+}
+
+// O^T[dim][head] = sum_token V^T[dim][token] * P^T[token][head]; out is [D][8].
+template <int D, int BITS>
+void value_tile(const uint8_t* tile, const float* cent, const float* pw /*[16 tokens][8 heads]*/, float* out) {
+    const int pitch = BITS * D / 8;
+    constexpr int BV = D / 64;
+    for (int mt = 0; mt < D / 16; mt++) {
+        Frag f{};
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            const int i = mt / 4, u = mt % 4;
+            const int c = BV * g + i;
+            for (int half = 0; half < 2; half++) {
+                const int ta = 2 * t + 8 * half, tb = ta + 1;
+                const uint32_t WA = gather_value_word<D, BITS>(tile, pitch, ta, c);
+                const uint32_t WB = gather_value_word<D, BITS>(tile, pitch, tb, c);
+                if (BITS == 2) {
+                    const uint32_t X = quad_index_v2(WA | (WB << 16), u);
+                    int ag, bg, ag8, bg8;
+                    quad_index_codes_v2(X, ag, bg, ag8, bg8);
+                    f.a[lane][4 * half + 0] = cent[ag];  f.a[lane][4 * half + 1] = cent[bg];
+                    f.a[lane][4 * half + 2] = cent[ag8]; f.a[lane][4 * half + 3] = cent[bg8];
+                } else {
+                    uint32_t Ze, Zo;
+                    token_pair_words(WA, WB, Ze, Zo);
+                    int ca, cb;
+                    token_pair_codes<BITS>(token_pair_index(Ze, Zo, 2 * u + 1), ca, cb);
+                    f.a[lane][4 * half + 0] = cent[ca];  f.a[lane][4 * half + 1] = cent[cb];
+                    token_pair_codes<BITS>(token_pair_index(Ze, Zo, 2 * u), ca, cb);
+                    f.a[lane][4 * half + 2] = cent[ca];  f.a[lane][4 * half + 3] = cent[cb];
+                }
+                // B = P^T: (k = tokens 2t+8*half, +1 ; col = head g)
+                f.b[lane][2 * half + 0] = pw[ta * 8 + g];
+                f.b[lane][2 * half + 1] = pw[tb * 8 + g];
+            }
+        }
+        float C[16][8] = {};
+        mma_replay(f, C);
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            int dg, dg8;
+            value_dims(D, g, mt, dg, dg8);
+            for (int j = 0; j < 2; j++) {
+                out[dg * 8 + 2 * t + j] = C[g][2 * t + j];
+                out[dg8 * 8 + 2 * t + j] = C[g + 8][2 * t + j];
+            }
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int replay_key_tile(int D, int bits, const uint8_t* tile, const float* cent, const float* q, float* out) {
+#define CASE(d, b) if (D == d && bits == b) { key_tile<d, b>(tile, cent, q, out); return 0; }
+    CASE(64, 2) CASE(64, 3) CASE(64, 4) CASE(128, 2) CASE(128, 3) CASE(128, 4)
+#undef CASE
+    return -1;
+}
+
+int replay_value_tile(int D, int bits, const uint8_t* tile, const float* cent, const float* pw, float* out) {
+#define CASE(d, b) if (D == d && bits == b) { value_tile<d, b>(tile, cent, pw, out); return 0; }
+    CASE(64, 2) CASE(64, 3) CASE(64, 4) CASE(128, 2) CASE(128, 3) CASE(128, 4)
+#undef CASE
+    return -1;
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+"""Host replay of the tensor-core fragment maps used by the decode-attention and scan kernels.
+
+csrc/decode_bits.cuh holds the bit-plane -> fragment index arithmetic as host/device functions.
+tests/fragment_harness.cpp replays a full 32-lane warp tile with them on the CPU; here the result
+is compared with a direct evaluation on unpacked codes.  This pins the index maps, table entry
+builders and dimension permutations without a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(ROOT, "turboquant-kv_b200", "csrc")
+
+
+@pytest.fixture(scope="module")
+def harness(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("frag") / "libfrag.so")
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-x", "c++", "-shared", "-fPIC", "-I", CSRC,
+                           os.path.join(ROOT, "tests", "fragment_harness.cpp"), "-o", out])
+    return ctypes.CDLL(out)
+
+
+def _ptr(a, t):
+    return a.ctypes.data_as(ctypes.POINTER(t))
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_key_tile_scores(harness, orc, dim, bits):
+    rng = np.random.default_rng(dim + bits)
+    codes = rng.integers(0, 1 << bits, size=(16, dim), dtype=np.uint8)
+    tile = orc.pack_codes(codes, bits)
+    cent = np.sort(rng.normal(size=1 << bits)).astype(np.float32)
+    q = rng.normal(size=(8, dim)).astype(np.float32)
+    out = np.zeros((16, 8), np.float32)
+    rc = harness.replay_key_tile(dim, bits, _ptr(tile, ctypes.c_uint8), _ptr(cent, ctypes.c_float),
+                                 _ptr(q, ctypes.c_float), _ptr(out, ctypes.c_float))
+    assert rc == 0
+    want = cent[codes] @ q.T
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_value_tile_accumulate(harness, orc, dim, bits):
+    rng = np.random.default_rng(7 * dim + bits)
+    codes = rng.integers(0, 1 << bits, size=(16, dim), dtype=np.uint8)
+    tile = orc.pack_codes(codes, bits)
+    cent = np.sort(rng.normal(size=1 << bits)).astype(np.float32)
+    pw = rng.random(size=(16, 8)).astype(np.float32)
+    out = np.zeros((dim, 8), np.float32)
+    rc = harness.replay_value_tile(dim, bits, _ptr(tile, ctypes.c_uint8), _ptr(cent, ctypes.c_float),
+                                   _ptr(pw, ctypes.c_float), _ptr(out, ctypes.c_float))
+    assert rc == 0
+    want = cent[codes].T @ pw
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-4)

@@ -1,0 +1,237 @@
+"""GPU parity: operator-level attention, the cache API and the fused decode kernel.
+
+Bar (float): within 1e-2 max-abs and cosine >= 0.9999 of the dequantise-then-attend result, which is
+what the oracle computes (oracle/tq_oracle.c, tqo_decode_attention) and what the golden fixtures
+hold from the upstream cache."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from util import attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("tag,dim,kb,vb", [("k4v2_d64", 64, 4, 2), ("k4v3_d128", 128, 4, 3), ("k2v4_d64", 64, 2, 4)])
+def test_operator_level_scores_and_values(orc, golden, tag, dim, kb, vb):
+    from turboquant_kv import ops
+
+    g = golden("attention")
+    q = g[f"{tag}_q"]
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(kb, dim)
+    _, cv = orc.lloyd_max_codebook(vb, dim)
+    for h in range(g[f"{tag}_k"].shape[0]):
+        kp, kn = g[f"{tag}_key_packed"][h], g[f"{tag}_key_norms"][h]
+        sc = ops.attention_scores_packed(cuda(q[:, h:h + 1, 0, :]), cuda(kp), cuda(kn), cuda(ck), cuda(rk), kb)
+        want = orc.attention_scores_packed(q[:, h:h + 1, 0, :], kp, kn, ck, rk, kb)
+        np.testing.assert_allclose(sc.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * np.abs(want).max())
+        ref_l = g[f"{tag}_logits"][:, h, 0, :] * math.sqrt(dim)
+        np.testing.assert_allclose(sc.cpu().numpy()[:, 0], ref_l, rtol=1e-3, atol=1e-4 * np.abs(ref_l).max())
+        w = torch.softmax(torch.from_numpy(g[f"{tag}_logits"][:, h, 0, :]), -1).numpy()[:, None, :]
+        vp, vn = g[f"{tag}_val_packed"][h], g[f"{tag}_val_norms"][h]
+        o = ops.attention_values_packed(cuda(w), cuda(vp), cuda(vn), cuda(cv), cuda(rv), vb)
+        np.testing.assert_allclose(o.cpu().numpy()[:, 0], g[f"{tag}_out"][:, h, 0, :], atol=2e-4)
+
+
+def test_torch_operator_library_is_registered():
+    from turboquant_kv import ops
+
+    ops.register_torch_ops()
+    codes = torch.randint(0, 16, (5, 64), dtype=torch.uint8, device="cuda")
+    packed = torch.ops.turboquant.pack_codes(codes, 4)
+    assert torch.equal(torch.ops.turboquant.unpack_codes(packed, 4, 64), codes)
+
+
+@pytest.mark.parametrize("tag,dim,kb,vb", [("k4v2_d64", 64, 4, 2), ("k4v3_d128", 128, 4, 3), ("k2v4_d64", 64, 2, 4)])
+def test_cache_api_matches_upstream(golden, tag, dim, kb, vb):
+    """append + attention_scores + attention_values + fused decode against the upstream cache's outputs."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    g = golden("attention")
+    k, v, q = g[f"{tag}_k"], g[f"{tag}_v"], g[f"{tag}_q"]
+    heads, seq, _ = k.shape
+    cache = QuantizedKVCache(TurboQuantConfig(key_bits=kb, value_bits=vb, seed=42), num_layers=1, max_seq_len=256,
+                             num_heads=heads, head_dim=dim, device="cuda")
+    cut = min(150, seq)
+    cache.append(0, cuda(k[:, :cut]), cuda(v[:, :cut]))
+    if cut < seq:
+        cache.append(0, cuda(k[:, cut:]), cuda(v[:, cut:]))
+    assert int(cache.seq_lens[0]) == seq
+    kp = cache._key_packed[0][:, :seq].cpu().numpy()
+    assert (kp != g[f"{tag}_key_packed"]).mean() < 1e-3          # boundary ties only
+    np.testing.assert_allclose(cache._key_norms[0][:, :seq].cpu().numpy(), g[f"{tag}_key_norms"], rtol=2e-6)
+    logits = cache.attention_scores(0, cuda(q))
+    ref_l = g[f"{tag}_logits"]
+    assert logits.shape == ref_l.shape
+    np.testing.assert_allclose(logits.cpu().numpy(), ref_l, rtol=2e-3, atol=2e-3 * np.abs(ref_l).max())
+    out = cache.attention_values(0, torch.softmax(logits, dim=-1))
+    attention_close(out.cpu().numpy(), g[f"{tag}_out"], max_abs=5e-3)
+    assert cache.memory_bytes() == int(g[f"{tag}_memory_bytes"])
+    assert abs(cache.compression_ratio - float(g[f"{tag}_compression_ratio"])) < 1e-9
+    # fused path, one query at a time (the cache holds a single sequence)
+    for b in range(q.shape[0]):
+        fused = cache.decode_attention(0, cuda(q[b:b + 1, :, 0, :]))
+        attention_close(fused.float().cpu().numpy(), g[f"{tag}_out"][b:b + 1, :, 0, :])
+    assert cache.decode_status() == 0
+
+
+def _fill(batch, kv_heads, ctx, dim, seed, outliers=True):
+    gen = torch.Generator().manual_seed(seed)
+    k = torch.randn(batch, kv_heads, ctx, dim, generator=gen)
+    v = torch.randn(batch, kv_heads, ctx, dim, generator=gen)
+    if outliers:
+        for h in range(kv_heads):
+            ch = torch.randperm(dim, generator=gen)[:4]
+            k[:, h, :, ch] *= 20.0
+    return k, v
+
+
+@pytest.mark.parametrize("dim,kb,vb,kv_heads,group,ctx", [
+    (64, 4, 2, 8, 4, 1024),     # Llama-3.2-1B geometry
+    (64, 4, 2, 2, 4, 1),
+    (64, 4, 2, 2, 4, 17),
+    (64, 4, 2, 2, 1, 333),
+    (64, 3, 3, 2, 8, 100),
+    (64, 2, 4, 1, 2, 250),
+    (128, 4, 3, 8, 4, 700),     # Llama-3-8B geometry
+    (128, 4, 4, 2, 4, 65),
+    (128, 3, 2, 2, 3, 129),
+    (128, 2, 2, 1, 1, 48),
+])
+def test_fused_decode_matches_dequantise_then_attend(orc, dim, kb, vb, kv_heads, group, ctx):
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    batch = 2
+    k, v = _fill(batch, kv_heads, ctx, dim, seed=4000 + ctx)
+    gen = torch.Generator().manual_seed(99)
+    q = torch.randn(batch, kv_heads * group, dim, generator=gen)
+    cache = QuantizedKVCache(TurboQuantConfig(key_bits=kb, value_bits=vb, seed=42), num_layers=2, max_seq_len=ctx + 3,
+                             num_heads=kv_heads, head_dim=dim, device="cuda", batch_size=batch)
+    cache.append(1, k.cuda().bfloat16(), v.cuda().bfloat16())
+    out = cache.decode_attention(1, q.cuda().bfloat16())
+    assert out.dtype == torch.bfloat16 and out.shape == (batch, kv_heads * group, dim)
+    assert cache.decode_status() == 0
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(kb, dim)
+    _, cv = orc.lloyd_max_codebook(vb, dim)
+    ref = orc.decode_attention(q.bfloat16().float().numpy(), cache._kp[1].cpu().numpy(), cache._kn[1].cpu().numpy(),
+                               cache._vp[1].cpu().numpy(), cache._vn[1].cpu().numpy(),
+                               np.full(batch, ctx, np.int32), rk, ck, kb, rv, cv, vb)
+    attention_close(out.float().cpu().numpy(), ref)
+    # the cache contents themselves equal the oracle's quantisation of the same bf16 inputs
+    kq = k.bfloat16().float().numpy().reshape(-1, dim)
+    bk, _ = orc.lloyd_max_codebook(kb, dim)
+    o_packed, o_norms = orc.quantize_mse(kq, kb, rk, bk)
+    got = cache._kp[1][:, :, :ctx].cpu().numpy().reshape(-1, o_packed.shape[1])
+    assert (got != o_packed).mean() < 1e-3
+
+
+def test_decode_appends_token_by_token(orc):
+    """Prefill, then single-token steps: every step attends over everything appended so far."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    batch, kv_heads, group, dim = 3, 2, 4, 64
+    k, v = _fill(batch, kv_heads, 40, dim, seed=7)
+    cache = QuantizedKVCache(TurboQuantConfig(seed=42), 1, 64, kv_heads, dim, device="cuda", batch_size=batch)
+    cache.append(0, k[:, :, :30].cuda(), v[:, :, :30].cuda())
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(4, dim)
+    _, cv = orc.lloyd_max_codebook(2, dim)
+    gen = torch.Generator().manual_seed(3)
+    for step in range(30, 40):
+        cache.append(0, k[:, :, step:step + 1].cuda(), v[:, :, step:step + 1].cuda())
+        q = torch.randn(batch, kv_heads * group, 1, dim, generator=gen)
+        out = cache.decode_attention(0, q.cuda())
+        assert out.shape == q.shape
+        ref = orc.decode_attention(q[:, :, 0].numpy(), cache._kp[0].cpu().numpy(), cache._kn[0].cpu().numpy(),
+                                   cache._vp[0].cpu().numpy(), cache._vn[0].cpu().numpy(),
+                                   np.full(batch, step + 1, np.int32), rk, ck, 4, rv, cv, 2)
+        attention_close(out[:, :, 0].cpu().numpy(), ref)
+
+
+def test_paged_decode_with_ragged_lengths(orc):
+    """vLLM-style pools, permuted block tables, different length per sequence, K4/V3 at head_dim 128."""
+    from turboquant_kv.vllm_plugin import TurboQuantAttentionImpl, TurboQuantKVCacheConfig, TurboQuantPagedKVCache
+
+    kv_heads, group, dim, bs = 4, 4, 128, 16
+    lens = [1, 16, 45, 200]
+    batch = len(lens)
+    nblocks = sum((l + bs - 1) // bs for l in lens) + 3
+    cfg = TurboQuantKVCacheConfig(key_bits=4, value_bits=3, block_size=bs, num_gpu_blocks=nblocks, seed=42)
+    pool = TurboQuantPagedKVCache(cfg, num_layers=1, num_heads=kv_heads, head_dim=dim, device="cuda")
+    perm = torch.randperm(nblocks, generator=torch.Generator().manual_seed(0)).tolist()
+    max_blocks = max((l + bs - 1) // bs for l in lens)
+    tables = torch.zeros(batch, max_blocks, dtype=torch.int32)
+    gen = torch.Generator().manual_seed(11)
+    ks, vs, nxt = [], [], 0
+    for b, l in enumerate(lens):
+        k = torch.randn(l, kv_heads, dim, generator=gen)
+        v = torch.randn(l, kv_heads, dim, generator=gen)
+        k[:, :, :4] *= 20.0
+        nb = (l + bs - 1) // bs
+        blocks = perm[nxt:nxt + nb]
+        nxt += nb
+        tables[b, :nb] = torch.tensor(blocks, dtype=torch.int32)
+        slots = torch.tensor([blocks[t // bs] * bs + t % bs for t in range(l)], dtype=torch.int64)
+        # all but the last token are written ahead; the last one goes through forward()
+        pool.append_slots(0, k[:-1].cuda(), v[:-1].cuda(), slots[:-1]) if l > 1 else None
+        ks.append(k)
+        vs.append(v)
+    q = torch.randn(batch, kv_heads * group, dim, generator=gen)
+
+    class Meta:
+        layer_id = 0
+        slot_mapping = torch.tensor([int(tables[b, (l - 1) // bs]) * bs + (l - 1) % bs for b, l in enumerate(lens)])
+        block_tables = tables
+        seq_lens = torch.tensor(lens, dtype=torch.int32)
+        max_seq_len = max(lens)
+
+    impl = TurboQuantAttentionImpl(kv_heads * group, dim, 1.0 / math.sqrt(dim), kv_heads)
+    new_k = torch.stack([k[-1] for k in ks])
+    new_v = torch.stack([v[-1] for v in vs])
+    out = impl.forward(q.cuda(), new_k.cuda(), new_v.cuda(), pool, Meta())
+    assert out.shape == (batch, kv_heads * group, dim)
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(3, dim)
+    for b, l in enumerate(lens):
+        kp, kn = orc.quantize_mse(ks[b].transpose(0, 1).reshape(-1, dim).numpy(), 4, rk, bk)
+        vp, vn = orc.quantize_mse(vs[b].transpose(0, 1).reshape(-1, dim).numpy(), 3, rv, bv)
+        ref = orc.decode_attention(q[b:b + 1].numpy(), kp.reshape(1, kv_heads, l, -1), kn.reshape(1, kv_heads, l),
+                                   vp.reshape(1, kv_heads, l, -1), vn.reshape(1, kv_heads, l),
+                                   np.array([l], np.int32), rk, ck, 4, rv, cv, 3)
+        attention_close(out[b:b + 1].cpu().numpy(), ref)
+
+
+def test_protected_layers_and_upstream_cache_checks():
+    """The behaviours upstream tests/test_cache.py pins: incremental lengths, compression ratio in (3, 10),
+    fp16-exact protected layers, outlier_channels accepted."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    cfg = TurboQuantConfig(key_bits=4, value_bits=2, protected_layers=1, outlier_channels=4)
+    cache = QuantizedKVCache(cfg, num_layers=2, max_seq_len=128, num_heads=4, head_dim=64, device="cuda")
+    assert cache._has_outliers
+    k, v = torch.randn(4, 10, 64, device="cuda"), torch.randn(4, 10, 64, device="cuda")
+    for layer in (0, 1):
+        cache.append(layer, k, v)
+        cache.append(layer, k[:, :5], v[:, :5])
+    assert cache.seq_lens.tolist() == [15, 15]
+    q = torch.randn(4, 1, 64, device="cuda")
+    exact = torch.matmul(q, torch.cat([k, k[:, :5]], 1).half().float().transpose(-2, -1)) / 8.0
+    assert torch.allclose(cache.attention_scores(0, q), exact, atol=1e-3)
+    approx = cache.attention_scores(1, q)
+    assert torch.corrcoef(torch.stack([approx.flatten(), exact.flatten()]))[0, 1] > 0.8
+    only_q = QuantizedKVCache(TurboQuantConfig(), 1, 128, 4, 64, device="cuda")
+    only_q.append(0, k, v)
+    assert 3 < only_q.compression_ratio < 10 and only_q.memory_bytes() > 0
+    with pytest.raises(RuntimeError):
+        QuantizedKVCache(TurboQuantConfig(mode="prod"), 1, 16, 2, 64, device="cuda").append(0, k[:2], v[:2])

@@ -1,0 +1,73 @@
+"""GPU tests of the HuggingFace cache class and the C-ABI error behaviour."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from util import attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def test_hf_cache_update_returns_old_dequantised_new_exact(orc):
+    from turboquant_kv import TurboQuantCache
+
+    cache = TurboQuantCache(key_bits=4, value_bits=2, seed=42)
+    gen = torch.Generator().manual_seed(0)
+    k0, v0 = torch.randn(2, 4, 12, 64, generator=gen).cuda(), torch.randn(2, 4, 12, 64, generator=gen).cuda()
+    k1, v1 = torch.randn(2, 4, 1, 64, generator=gen).cuda(), torch.randn(2, 4, 1, 64, generator=gen).cuda()
+    ka, va = cache.update(k0, v0, 0)
+    assert torch.equal(ka, k0) and torch.equal(va, v0)          # first call: everything is "new", exact
+    kb, vb = cache.update(k1, v1, 0)
+    assert kb.shape == (2, 4, 13, 64) and torch.equal(kb[:, :, 12:], k1) and torch.equal(vb[:, :, 12:], v1)
+    rk = orc.make_rotation_matrix(64, 42)
+    bk, ck = orc.lloyd_max_codebook(4, 64)
+    p, n = orc.quantize_mse(k0.cpu().numpy().reshape(-1, 64), 4, rk, bk)
+    want = orc.dequantize_mse(p, n, 4, 64, rk, ck).reshape(2, 4, 12, 64)
+    assert np.abs(kb[:, :, :12].cpu().numpy() - want).max() < 2e-2 * np.abs(want).max()
+    assert cache.get_seq_length(0) == 13 and len(cache) == 1 and cache.seen_tokens == 13
+    assert cache.memory_bytes() == 2 * 4 * 13 * (32 + 16 + 8)
+    # fast path: the same attention without the dense round trip
+    q = torch.randn(2, 8, 64, generator=gen).cuda()
+    out = cache.decode_attention(q, 0)
+    st = cache._layer_stores[0]
+    rv = orc.make_rotation_matrix(64, 43)
+    _, cv = orc.lloyd_max_codebook(2, 64)
+    ref = orc.decode_attention(q.cpu().numpy(), st._kp.cpu().numpy(), st._kn.cpu().numpy(), st._vp.cpu().numpy(),
+                               st._vn.cpu().numpy(), np.full(2, 13, np.int32), rk, ck, 4, rv, cv, 2)
+    attention_close(out.cpu().numpy(), ref)
+    k_it, v_it = cache[0]
+    assert k_it.shape == (2, 4, 13, 64)
+
+
+def test_hf_cache_protected_layers_keep_full_precision():
+    from turboquant_kv import TurboQuantCache
+
+    cache = TurboQuantCache(protected_layers=1)
+    k, v = torch.randn(1, 2, 3, 64, device="cuda"), torch.randn(1, 2, 3, 64, device="cuda")
+    ka, _ = cache.update(k, v, 0)
+    kb, _ = cache.update(k, v, 0)
+    assert torch.equal(kb, torch.cat([k, k], 2)) and cache.get_seq_length(0) == 6
+
+
+def test_c_abi_reports_errors_without_raising_across_the_boundary():
+    from turboquant_kv import _native as N
+
+    L = N.lib()
+    x = torch.zeros(4, 64, device="cuda")
+    rc = L.tqb_quantize_mse(N.ptr(x), 0, 4, 64, 64, N.ptr(x), N.ptr(x), 9, N.ptr(x), N.ptr(x), None, None)
+    assert rc == -1 and b"bit_width" in L.tqb_last_error()
+    rc = L.tqb_quantize_mse(N.ptr(x), 0, 4, 1000, 1000, N.ptr(x), N.ptr(x), 4, N.ptr(x), N.ptr(x), None, None)
+    assert rc == -2
+    rc = L.tqb_decode_attention(N.ptr(x), 0, 1, 4, 4, 64, N.ptr(x), N.ptr(x), N.ptr(x), N.ptr(x), 16, N.ptr(x), 16,
+                                None, 0, 0, N.ptr(x), N.ptr(x), 4, N.ptr(x), N.ptr(x), 2, ctypes.c_float(1.0),
+                                N.ptr(x), 16, N.ptr(x), 0, None)
+    assert rc == -4 and b"workspace" in L.tqb_last_error()
+    before = N.launch_count()
+    y = torch.zeros(4, 8, dtype=torch.uint8, device="cuda")
+    assert L.tqb_pack_codes(N.ptr(torch.zeros(4, 64, dtype=torch.uint8, device="cuda")), 4, 64, 1, N.ptr(y), None) == 0
+    assert N.launch_count() == before + 1
+    torch.cuda.synchronize()

@@ -1,0 +1,189 @@
+"""GPU parity: TurboQuantIndex.add / search against the golden fixtures, the oracle and (when built) the
+upstream C++ core.  Bar: top-k ids identical except between scores that float32 summation cannot separate;
+scores bit-identical to the oracle because the merge kernel re-scores in the upstream order."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from util import topk_ids_match
+
+pytestmark = pytest.mark.gpu
+
+
+def _db(rows, seed):
+    rng = np.random.default_rng(seed)
+    return np.round(np.clip(rng.gamma(0.5, 40.0, size=(rows, 128)), 0, 255)).astype(np.float32)
+
+
+@pytest.mark.parametrize("bits,mode", [(4, "mse"), (3, "mse"), (2, "mse"), (3, "prod")])
+def test_index_matches_upstream_fixture(orc, golden, bits, mode):
+    from turboquant_kv import TurboQuantIndex
+
+    g = golden("search")
+    db, qs = g["db"].astype(np.float32), g["queries"].astype(np.float32)
+    idx = TurboQuantIndex(dim=128, bit_width=bits, mode=mode, seed=42)
+    idx.add(torch.from_numpy(db[:2000]))           # host tensors: staged on the GPU
+    idx.add(torch.from_numpy(db[2000:]).cuda())    # incremental insertion, device tensor
+    assert idx.n_vectors == 3000
+    assert (idx._packed_codes.cpu().numpy() != g[f"packed_b{bits}_{mode}"]).mean() < 1e-4
+    np.testing.assert_allclose(idx._norms.cpu().numpy(), g[f"norms_b{bits}_{mode}"], rtol=2e-6)
+    # search over the upstream index contents so that only the scan is under test
+    idx._packed_codes = torch.from_numpy(g[f"packed_b{bits}_{mode}"]).cuda()
+    idx._norms = torch.from_numpy(g[f"norms_b{bits}_{mode}"]).cuda()
+    rot = orc.make_rotation_matrix(128, 42)
+    if mode == "prod":
+        idx._qjl_signs = torch.from_numpy(g[f"signs_b{bits}_{mode}"]).cuda()
+        idx._residual_norms = torch.from_numpy(g[f"res_norms_b{bits}_{mode}"]).cuda()
+        _, cent = orc.lloyd_max_codebook(bits - 1, 128)
+        S = orc.make_qjl_matrix(128, 128, 42)
+        o_sc, o_ids, allsc = orc.search_prod(qs, g[f"packed_b{bits}_{mode}"], g[f"signs_b{bits}_{mode}"],
+                                             g[f"res_norms_b{bits}_{mode}"], g[f"norms_b{bits}_{mode}"], rot, cent, S,
+                                             bits, 10, return_all=True)
+    else:
+        _, cent = orc.lloyd_max_codebook(bits, 128)
+        o_sc, o_ids, allsc = orc.search_mse(qs, g[f"packed_b{bits}_{mode}"], g[f"norms_b{bits}_{mode}"], rot, cent,
+                                            bits, 10, return_all=True)
+    sc, ids = idx.search(torch.from_numpy(qs), k=10)
+    assert sc.device.type == "cpu" and ids.dtype == torch.int64
+    topk_ids_match(ids.numpy(), g[f"ids_b{bits}_{mode}"], allsc)
+    np.testing.assert_allclose(sc.numpy(), g[f"scores_b{bits}_{mode}"], rtol=2e-5)
+    if mode == "mse":
+        assert np.array_equal(ids.numpy(), o_ids)
+        assert np.array_equal(sc.numpy(), o_sc), "re-scored results must equal the upstream-order float32 sums"
+
+
+@pytest.mark.parametrize("rows", [1, 5, 15, 16, 17, 1000, 50001])
+def test_scan_row_counts_and_padding(orc, rows):
+    from turboquant_kv import TurboQuantIndex
+
+    db = _db(rows, 5)
+    qs = _db(9, 6)
+    idx = TurboQuantIndex(dim=128, bit_width=4, seed=42)
+    idx.add(torch.from_numpy(db).cuda())
+    rot = orc.make_rotation_matrix(128, 42)
+    _, cent = orc.lloyd_max_codebook(4, 128)
+    k = 10
+    sc, ids = idx.search(torch.from_numpy(qs).cuda(), k=k)
+    kk = min(k, rows)
+    assert sc.shape == (9, kk)                      # k is clipped like the upstream Python path
+    o_sc, o_ids = orc.search_mse(qs, idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy(), rot, cent, 4, kk)
+    assert np.array_equal(ids.cpu().numpy(), o_ids)
+    assert np.array_equal(sc.cpu().numpy(), o_sc)
+
+
+@pytest.mark.parametrize("dim,bits", [(64, 4), (64, 2), (128, 3), (32, 4), (200, 3), (256, 1), (96, 2)])
+def test_scan_shapes_tensor_core_and_generic_paths(orc, dim, bits):
+    from turboquant_kv import TurboQuantIndex
+
+    rng = np.random.default_rng(dim * 10 + bits)
+    db = rng.normal(size=(4099, dim)).astype(np.float32)
+    qs = rng.normal(size=(7, dim)).astype(np.float32)
+    idx = TurboQuantIndex(dim=dim, bit_width=bits, seed=7)
+    idx.add(torch.from_numpy(db).cuda())
+    rot = orc.make_rotation_matrix(dim, 7)
+    _, cent = orc.lloyd_max_codebook(bits, dim)
+    sc, ids = idx.search(torch.from_numpy(qs).cuda(), k=25)
+    o_sc, o_ids, allsc = orc.search_mse(qs, idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy(), rot, cent,
+                                        bits, 25, return_all=True)
+    topk_ids_match(ids.cpu().numpy(), o_ids, allsc, rel_tie=1e-6)
+    np.testing.assert_allclose(sc.cpu().numpy(), o_sc, rtol=1e-6)
+
+
+def test_scan_duplicate_rows_order_by_id(orc):
+    from turboquant_kv import TurboQuantIndex
+
+    base = _db(64, 1)
+    db = np.concatenate([base] * 40)                # every row 40 times: massive exact ties
+    idx = TurboQuantIndex(dim=128, bit_width=4, seed=42)
+    idx.add(torch.from_numpy(db).cuda())
+    qs = _db(4, 2)
+    sc, ids = idx.search(torch.from_numpy(qs).cuda(), k=10)
+    rot = orc.make_rotation_matrix(128, 42)
+    _, cent = orc.lloyd_max_codebook(4, 128)
+    o_sc, o_ids = orc.search_mse(qs, idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy(), rot, cent, 4, 10)
+    assert np.array_equal(ids.cpu().numpy(), o_ids)
+    assert np.array_equal(sc.cpu().numpy(), o_sc)
+
+
+def test_scan_against_upstream_cpp_core(orc):
+    if orc.ref_lib() is None:
+        pytest.skip("oracle/_ref/libtq_ref.so not built")
+    from turboquant_kv import TurboQuantIndex
+
+    db, qs = _db(200_000, 1000), _db(16, 999)
+    idx = TurboQuantIndex(dim=128, bit_width=4, seed=42)
+    idx.add(torch.from_numpy(db).cuda())
+    sc, ids = idx.search(torch.from_numpy(qs).cuda(), k=10)
+    rot = orc.make_rotation_matrix(128, 42)
+    _, cent = orc.lloyd_max_codebook(4, 128)
+    r_sc, r_ids = orc.ref_search_packed(qs, idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy(), rot, cent, 4, 10)
+    assert np.array_equal(ids.cpu().numpy(), r_ids)
+    assert np.array_equal(sc.cpu().numpy(), r_sc)
+
+
+def test_many_queries_and_large_k(orc):
+    from turboquant_kv import TurboQuantIndex
+
+    db, qs = _db(30_000, 3), _db(700, 4)            # more queries than one scan call takes
+    idx = TurboQuantIndex(dim=128, bit_width=4, seed=42)
+    idx.add(torch.from_numpy(db).cuda())
+    sc, ids = idx.search(torch.from_numpy(qs).cuda(), k=100)
+    rot = orc.make_rotation_matrix(128, 42)
+    _, cent = orc.lloyd_max_codebook(4, 128)
+    o_sc, o_ids, allsc = orc.search_mse(qs, idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy(), rot, cent, 4, 100,
+                                        return_all=True)
+    topk_ids_match(ids.cpu().numpy(), o_ids, allsc, rel_tie=1e-6)
+    with pytest.raises(RuntimeError):
+        idx.search(torch.from_numpy(qs[:2]).cuda(), k=1000)
+
+
+def test_save_load_both_layouts(tmp_path, golden):
+    from turboquant_kv import TurboQuantIndex
+
+    g = golden("search")
+    db = torch.from_numpy(g["db"].astype(np.float32))
+    qs = torch.from_numpy(g["queries"].astype(np.float32)).cuda()
+    for mode, bits in (("mse", 4), ("prod", 3)):
+        idx = TurboQuantIndex.from_vectors(db, bit_width=bits, mode=mode, seed=42)
+        want = idx.search(qs, 10)
+        p = str(tmp_path / f"{mode}.idx")
+        idx.save(p)
+        back = TurboQuantIndex.load(p, seed=42)
+        assert back.mode == mode and back.n_vectors == 3000
+        got = back.search(qs, 10)
+        assert torch.equal(want[1], got[1]) and torch.equal(want[0], got[0])
+        size = os.path.getsize(p)
+        per_row = (bits if mode == "mse" else bits - 1) * 16 + 4 + (16 + 4 if mode == "prod" else 0)
+        assert size == 9 + 1 + 3000 * per_row
+    idx = TurboQuantIndex.from_vectors(db, bit_width=4, seed=42)
+    p = str(tmp_path / "core.tqix")
+    idx.save(p, format="tqix")
+    assert os.path.getsize(p) == 24 + 3000 * 68
+    back = TurboQuantIndex.load(p)
+    assert torch.equal(back.search(qs, 10)[1], idx.search(qs, 10)[1])
+
+
+def test_row_sharded_search_merges_to_the_global_answer(orc):
+    """Two shards on one GPU, merged with the merge kernel: same top-k as the unsharded index."""
+    from turboquant_kv import TurboQuantIndex
+    from turboquant_kv.distributed import shard_rows
+    from turboquant_kv.search import merge_topk
+
+    db, qs = _db(20_001, 8), torch.from_numpy(_db(33, 9)).cuda()
+    whole = TurboQuantIndex.from_vectors(torch.from_numpy(db).cuda(), bit_width=4, seed=42)
+    want_s, want_i = whole.search(qs, 10)
+    parts_s, parts_i = [], []
+    for r in range(3):
+        lo, hi = shard_rows(db.shape[0], 3, r)
+        shard = TurboQuantIndex(dim=128, bit_width=4, seed=42)
+        shard.id_offset = lo
+        shard.add(torch.from_numpy(db[lo:hi]).cuda())
+        s, i = shard.search(qs, 10)
+        parts_s.append(s)
+        parts_i.append(i)
+    got_s, got_i = merge_topk(torch.stack(parts_s, 1), torch.stack(parts_i, 1), 10)
+    assert torch.equal(got_i, want_i) and torch.equal(got_s, want_s)

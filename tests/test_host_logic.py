@@ -1,0 +1,187 @@
+"""CPU-only tests: host-side constant generators, the C-ABI surface, bookkeeping that needs no kernel,
+and the multi-process gather/merge logic on gloo ranks."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "tqb200.h")
+LIB = os.path.join(ROOT, "turboquant-kv_b200", "turboquant_kv", "libtqb200.so")
+
+
+def test_host_constants_match_upstream(golden):
+    """Codebooks, rotations and the QJL matrix are generated in Python; they must equal the upstream ones."""
+    import turboquant_kv.reference as R
+
+    g = golden("constants")
+    for bits in (1, 2, 3, 4):
+        for dim in (64, 128):
+            b, c = R.lloyd_max_codebook(bits, dim)
+            assert np.array_equal(b.numpy(), g[f"boundaries_b{bits}_d{dim}"])
+            assert np.array_equal(c.numpy(), g[f"centroids_b{bits}_d{dim}"])
+    for dim, seed in ((64, 42), (64, 43), (128, 42), (32, 7)):
+        assert np.array_equal(R.make_rotation_matrix(dim, seed).numpy(), g[f"rotation_qr_d{dim}_s{seed}"])
+    assert np.allclose(R.make_rotation_matrix(64, 42, "rht").numpy(), g["rotation_rht_d64_s42"], atol=1e-6)
+    assert np.allclose(R.make_rht_rotation(48, 5).numpy(), g["rotation_rht_d48_s5"], atol=1e-6)
+    for dim in (64, 128):
+        assert np.array_equal(R._make_qjl_matrix(dim, dim, 42, "cpu").numpy(), g[f"qjl_d{dim}_s42"])
+    with pytest.raises(ValueError):
+        R.make_rotation_matrix(8, 1, "nope")
+
+
+def test_codebook_properties():
+    """What upstream tests/test_reference.py checks of the codebook: analytic 1-bit value, counts, order, symmetry."""
+    import turboquant_kv.reference as R
+
+    for d in (64, 128, 256):
+        b, c = R.lloyd_max_codebook(1, d)
+        assert abs(float(c[1]) - np.sqrt(2 / np.pi) / np.sqrt(d)) < 1e-4 and abs(float(c[0]) + float(c[1])) < 1e-7
+    for bits in (1, 2, 3, 4):
+        b, c = R.lloyd_max_codebook(bits, 128)
+        assert b.shape == ((1 << bits) - 1,) and c.shape == (1 << bits,)
+        assert torch.all(c[1:] > c[:-1]) and torch.all(b[1:] > b[:-1])
+        assert torch.allclose(c, -c.flip(0), atol=1e-6)
+    rot = R.make_rotation_matrix(128, 42)
+    assert torch.allclose(rot @ rot.t(), torch.eye(128), atol=1e-5)
+    assert torch.equal(rot, R.make_rotation_matrix(128, 42)) and not torch.equal(rot, R.make_rotation_matrix(128, 43))
+
+
+def test_library_exports_every_declared_symbol():
+    """libtqb200.so loads without a GPU and exports exactly the entry points include/tqb200.h declares."""
+    sys.path.insert(0, os.path.join(ROOT, "turboquant-kv_b200", "csrc"))
+    import build as native_build
+
+    native_build.build()
+    declared = set(re.findall(r"\b(tqb_[a-z0-9_]+)\s*\(", open(HEADER).read()))
+    assert len(declared) >= 17
+    lib = ctypes.CDLL(LIB)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in tqb200.h but not exported"
+    lib.tqb_abi_version.restype = ctypes.c_int
+    assert lib.tqb_abi_version() == 1
+    out = subprocess.run(["nm", "-D", "--defined-only", LIB], capture_output=True, text=True).stdout
+    exported = set(re.findall(r" T (tqb_[a-z0-9_]+)", out))
+    assert exported == declared, exported ^ declared
+
+
+def test_argument_errors_need_no_gpu():
+    """Validation happens before any CUDA call: error codes and messages come back through the C ABI."""
+    lib = ctypes.CDLL(LIB)
+    lib.tqb_last_error.restype = ctypes.c_char_p
+    assert lib.tqb_pack_codes(None, ctypes.c_int64(4), 64, 9, None, None) == -1
+    assert b"bit_width must be 1-8" in lib.tqb_last_error()
+    assert lib.tqb_pack_codes(None, ctypes.c_int64(0), 64, 4, None, None) == 0        # empty input: no launch
+    lib.tqb_scan_topk_workspace_bytes.restype = ctypes.c_size_t
+    lib.tqb_scan_topk_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    assert lib.tqb_scan_topk_workspace_bytes(4, 1000, 128, 4, 10) > 0
+    assert lib.tqb_scan_topk_workspace_bytes(4, 1000, 128, 4, 100000) == 0
+
+
+def test_no_cpu_fallback():
+    """Without CUDA the product refuses to compute instead of falling back to anything."""
+    if torch.cuda.is_available():
+        pytest.skip("this check is for GPU-less machines")
+    import turboquant_kv as tq
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tq.quantize_mse(torch.randn(4, 64), 4)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tq.TurboQuantIndex(dim=64)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tq.QuantizedKVCache(tq.TurboQuantConfig(), 1, 16, 2, 64)
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "turboquant-kv_b200")
+    for base, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(base, f)).read()
+                assert "oracle" not in text.replace("the oracle", ""), f"{f} mentions the oracle folder"
+
+
+def test_config_and_sharding_bookkeeping():
+    from turboquant_kv import TurboQuantConfig
+    from turboquant_kv.distributed import DistributedQuantizedKVCache, shard_rows
+    from turboquant_kv.vllm_plugin import TurboQuantAttentionBackend, TurboQuantKVCacheConfig
+
+    c = TurboQuantConfig()
+    assert (c.key_bits, c.value_bits, c.mode, c.rotation, c.outlier_channels, c.protected_layers,
+            c.quantize_on_append, c.block_size, c.seed) == (4, 2, "mse", "dense_qr", 0, 0, True, 0, 42)
+    spans = [shard_rows(10_000_003, 8, r) for r in range(8)]
+    assert spans[0][0] == 0 and spans[-1][1] == 10_000_003
+    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
+    with pytest.raises(ValueError):
+        DistributedQuantizedKVCache(c, 1, 16, 6, 64, tp_size=4)
+    with pytest.raises(ValueError):
+        DistributedQuantizedKVCache(c, 1, 16, 8, 64, tp_size=4, tp_rank=4)
+    v = TurboQuantKVCacheConfig(key_bits=3, seed=5).to_turboquant_config()
+    assert v.key_bits == 3 and v.seed == 5 and v.quantize_on_append
+    assert TurboQuantAttentionBackend.get_name() == "turboquant"
+    assert TurboQuantAttentionBackend.get_kv_cache_shape(7, 16, 8, 128) == (2, 7, 16, 8, 128)
+
+
+def test_merge_topk_host_path_orders_by_score_then_id():
+    from turboquant_kv.search import merge_topk
+
+    s = torch.tensor([[[5.0, 3.0, 1.0], [5.0, 4.0, float("-inf")]]])
+    i = torch.tensor([[[7, 2, 9], [3, 8, -1]]])
+    ms, mi = merge_topk(s, i, 3)
+    assert mi.tolist() == [[3, 7, 8]] and ms.tolist() == [[5.0, 5.0, 4.0]]
+    ms, mi = merge_topk(s, i, 6)
+    assert mi.tolist() == [[3, 7, 8, 2, 9, -1]] and ms[0, -1] == float("-inf")
+
+
+_GLOO_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from turboquant_kv.distributed import gather_and_merge, shard_rows
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+# a fake "database" of scores: every rank owns a contiguous row range and reports its local top-k
+g = torch.Generator().manual_seed(123)
+Q, N, k = 5, 1001, 10
+scores = torch.randn(Q, N, generator=g)
+scores[:, 17] = scores[:, 600]           # an exact tie across shards: the lower id must win
+lo, hi = shard_rows(N, world, rank)
+ls, li = torch.topk(scores[:, lo:hi], k, dim=1)
+ms, mi = gather_and_merge(ls, li + lo, k)
+ws, wi = torch.topk(scores, k, dim=1)
+assert torch.equal(ms, ws), (rank, ms, ws)
+for q in range(Q):
+    assert sorted(mi[q].tolist()) == sorted(wi[q].tolist())
+    row = mi[q].tolist()
+    if 17 in row and 600 in row:
+        assert row.index(17) < row.index(600)
+# a shard that holds fewer than k rows pads with (-inf, -1)
+short = 3 if rank == 0 else k
+ls2 = torch.full((Q, k), float("-inf")); li2 = torch.full((Q, k), -1, dtype=torch.int64)
+ls2[:, :short], li2[:, :short] = ls[:, :short], (li + lo)[:, :short]
+ms2, mi2 = gather_and_merge(ls2, li2, k)
+assert (mi2 >= 0).all() and torch.isfinite(ms2).all()
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+'''
+
+
+@pytest.mark.timeout(300)
+def test_row_sharded_merge_on_two_gloo_ranks(tmp_path):
+    """world_size 2 on CPU: all-gather of per-shard candidates and the global merge."""
+    script = tmp_path / "worker.py"
+    script.write_text(_GLOO_WORKER)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29731", str(script),
+           os.path.join(ROOT, "turboquant-kv_b200")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=280)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert r.stdout.count("ok") == 2

@@ -1,0 +1,640 @@
+// scan.cu -- packed-code inner-product scan with top-k (TurboQuantIndex.search).
+//
+// Replaces turboquant::search_packed (upstream csrc/core/turboquant_core.cpp:407-514): for every
+// query, score_i = norm_i * sum_j (R q)_j * centroid[code_ij] over all database rows, keep the k best.
+//
+// Three launches:
+//   1. scan_prepare_kernel  rotates the queries (sequential float32 sums, the upstream order), and
+//                           writes them as mma.sync B fragments split into fp16 hi + lo parts.
+//   2. scan_kernel          persistent warps stream 16-row tiles of packed codes + norms through a
+//                           per-warp TMA ring (cp.async.bulk + mbarrier).  Codes become fp16 centroid
+//                           hi/lo pairs through a 256-entry shared-memory table indexed by one byte
+//                           (= two codes); two MMAs per 16 dims (c_hi x [q_hi | q_lo], c_lo x [q_hi | 0])
+//                           give float32-class scores for 4 queries at once.  Each warp keeps a sorted
+//                           candidate list of k+8 entries per query in shared memory; insertions are
+//                           warp-cooperative and rare once the threshold has risen.
+//   3. scan_merge_kernel    per query: selects the best k+8 of all warps' candidates, RE-SCORES them in
+//                           float32 in exactly the upstream summation order (table[j][code] added for
+//                           j = 0..d-1, then * norm), sorts by (score desc, id asc) and emits k.
+// The reported scores are therefore bit-identical to the upstream C++ arithmetic; the tensor-core
+// pass only has to rank well enough to put the true top-k among the k+8 survivors.
+//
+// Dims 64 and 128 with 2..4 bits take the tensor-core path; every other supported shape takes
+// scan_generic_kernel (one row per lane, float32 table lookups) with the same list and merge code.
+#include "common.cuh"
+#include "decode_bits.cuh"
+
+namespace tqb {
+
+constexpr int SCAN_TILE = 16;
+constexpr int SCAN_MARGIN = 8;          // extra candidates kept beyond k
+constexpr int SCAN_WARPS = 8;
+constexpr int QG = 4;                   // queries per tensor-core pass
+constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
+constexpr float QUERY_SCALE = 16.0f;
+constexpr uint32_t SCAN_WAIT_LIMIT = 1u << 22;
+constexpr int ID_NONE = 0x7fffffff;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void s_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void s_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool s_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SCAN_WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void s_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void s_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                      uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t s_pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// (score, id) ordering used everywhere: higher score first, lower id first among equal scores.
+__device__ __forceinline__ bool better(float s, int id, float ts, int tid) {
+    return s > ts || (s == ts && id < tid);
+}
+
+struct ScanParams {
+    const uint8_t* packed; const float* norms; int64_t n;
+    int dim, bits, nq, k, kk;           // kk = k + SCAN_MARGIN candidates kept per list
+    const float* rot; const float* cent; const float* queries;
+    int64_t id_offset;
+    int lists_per_query;                // candidate lists written per query (= warps in the grid)
+    // workspace views
+    int* status; float* qrot; uint32_t* qfrag; float* qscale;
+    float* cand_s; int* cand_id;        // (nq, lists_per_query, kk)
+    float* out_scores; int64_t* out_ids;
+};
+
+// ---- warp-cooperative sorted list in shared memory ----------------------------------------------
+// ls / li: kk entries sorted best-first.  Inserts (s, id) if it beats the last entry.  All 32 lanes
+// call with the same arguments.
+__device__ __forceinline__ void list_insert(float* ls, int* li, int kk, float s, int id, int lane) {
+    if (!better(s, id, ls[kk - 1], li[kk - 1])) return;
+    // position = number of entries better than the candidate
+    int cnt = 0;
+    for (int e = lane; e < kk; e += 32) cnt += better(ls[e], li[e], s, id) ? 1 : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    const int pos = cnt;
+    // shift [pos, kk-1) down by one: read everything first, then write
+    float ts[(TQB_SCAN_MAX_K + SCAN_MARGIN + 31) / 32];
+    int ti[(TQB_SCAN_MAX_K + SCAN_MARGIN + 31) / 32];
+    int c = 0;
+    for (int e = lane; e < kk; e += 32, c++) {
+        if (e > pos) { ts[c] = ls[e - 1]; ti[c] = li[e - 1]; }
+    }
+    __syncwarp();
+    c = 0;
+    for (int e = lane; e < kk; e += 32, c++) {
+        if (e > pos) { ls[e] = ts[c]; li[e] = ti[c]; }
+        else if (e == pos) { ls[e] = s; li[e] = id; }
+    }
+    __syncwarp();
+}
+
+
+// =================================================================================================
+// 1. query rotation (+ B fragments for the tensor-core path)
+// =================================================================================================
+// One CTA per group of QG queries.  q_rot[j] = sum_k q[k] * R[j][k], accumulated in k order with
+// separate multiply and add, the arithmetic of csrc/core/turboquant_core.cpp:425-433.
+// Fragment word layout: qfrag[group][ks][lane] = uint4 {B1 half0, B1 half1, B2 half0, B2 half1};
+// MMA column n = lane/4 holds query n/2 of the group: even n its fp16 hi part, odd n its lo part
+// (B1); B2 repeats the hi part in even columns and is zero in odd ones.
+__global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, int use_mma) {
+    extern __shared__ float sm[];
+    float* qin = sm;                    // dim
+    float* qr = sm + p.dim;             // QG * dim
+    __shared__ float qmax[QG];
+    const int grp = blockIdx.x;
+    if (grp == 0 && threadIdx.x == 0) *p.status = 0;
+    for (int jq = 0; jq < QG; jq++) {
+        const int q = grp * QG + jq;
+        __syncthreads();
+        if (q < p.nq) {
+            for (int k = threadIdx.x; k < p.dim; k += blockDim.x) qin[k] = p.queries[(int64_t)q * p.dim + k];
+        }
+        __syncthreads();
+        for (int j = threadIdx.x; j < p.dim; j += blockDim.x) {
+            float s = 0.0f;
+            if (q < p.nq) {
+                const float* row = p.rot + (int64_t)j * p.dim;
+                for (int k = 0; k < p.dim; k++) s = __fadd_rn(s, __fmul_rn(qin[k], row[k]));
+                p.qrot[(int64_t)q * p.dim + j] = s;
+            }
+            qr[jq * p.dim + j] = s;
+        }
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < QG) {
+        float mx = 0.0f;
+        for (int k = lane; k < p.dim; k += 32) mx = fmaxf(mx, fabsf(qr[warp * p.dim + k]));
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) {
+            qmax[warp] = mx;
+            const int q = grp * QG + warp;
+            if (q < p.nq) p.qscale[q] = mx / (CENT_SCALE * QUERY_SCALE);
+        }
+    }
+    __syncthreads();
+    if (!use_mma) return;
+    const int ksteps = p.dim >> 4;
+    for (int idx = threadIdx.x; idx < ksteps * 32; idx += blockDim.x) {
+        const int ks = idx >> 5, fl = idx & 31, g = fl >> 2, t = fl & 3;
+        const int jq = g >> 1, part = g & 1;
+        const float inv = qmax[jq] > 0.0f ? QUERY_SCALE / qmax[jq] : 0.0f;
+        uint32_t w[4];
+        for (int half = 0; half < 2; half++) {
+            int dlo, dhi;
+            pair_dims(p.dim, t, 2 * ks + half, dlo, dhi);
+            const float a = qr[jq * p.dim + dlo] * inv, b = qr[jq * p.dim + dhi] * inv;
+            const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
+            w[half] = part ? s_pack_half2(a - ah, b - bh) : s_pack_half2(ah, bh);
+            w[2 + half] = part ? 0u : s_pack_half2(ah, bh);
+        }
+        reinterpret_cast<uint4*>(p.qfrag)[((int64_t)grp * ksteps + ks) * 32 + fl] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// =================================================================================================
+// 2a. tensor-core scan
+// =================================================================================================
+template <int D, int BITS>
+struct ScanCfg {
+    static constexpr int PD = BITS * D / 8;
+    static constexpr int RT = SCAN_TILE * PD;              // rows of a tile
+    static constexpr int STAGE = RT + SCAN_TILE * 4;       // + norms
+    static constexpr int LUT_ENTRIES = 1 << (2 * BITS);
+    static constexpr int LUT_BYTES = LUT_ENTRIES * 32 * 8; // uint2 {hi pair, lo pair} per lane
+    static constexpr int KS = D / 16;
+};
+
+template <int D, int BITS, int NS>
+__global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanParams p) {
+    using C = ScanCfg<D, BITS>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint2* lut = reinterpret_cast<uint2*>(smem_raw);
+    uint8_t* ring_all = smem_raw + C::LUT_BYTES;
+    uint64_t* bars_all = reinterpret_cast<uint64_t*>(ring_all + (size_t)SCAN_WARPS * NS * C::STAGE);
+    float* lists_s = reinterpret_cast<float*>(bars_all + SCAN_WARPS * NS);
+    int* lists_i = reinterpret_cast<int*>(lists_s + SCAN_WARPS * QG * p.kk);
+    __shared__ float s_c[16];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int grp = blockIdx.y;
+    uint8_t* ring = ring_all + (size_t)warp * NS * C::STAGE;
+    const uint32_t bar0 = s_u32(bars_all + warp * NS);
+    float* ls = lists_s + (size_t)warp * QG * p.kk;
+    int* li = lists_i + (size_t)warp * QG * p.kk;
+
+    if (threadIdx.x < 16) s_c[threadIdx.x] = threadIdx.x < (1 << BITS) ? p.cent[threadIdx.x] * CENT_SCALE : 0.0f;
+    if (lane == 0)
+        for (int s = 0; s < NS; s++) s_mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int e = lane; e < QG * p.kk; e += 32) { ls[e] = -__builtin_huge_valf(); li[e] = ID_NONE; }
+    __syncthreads();
+    for (int x = warp; x < C::LUT_ENTRIES; x += SCAN_WARPS) {
+        int clo, chi;
+        pair_index_codes<BITS>((uint32_t)x, clo, chi);
+        const float a = s_c[clo], b = s_c[chi];
+        const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
+        lut[x * 32 + lane] = make_uint2(s_pack_half2(ah, bh), s_pack_half2(a - ah, b - bh));
+    }
+    __syncthreads();
+
+    // B fragments of this query group stay in registers for the whole scan
+    uint4 qf[C::KS];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
+#pragma unroll
+        for (int ks = 0; ks < C::KS; ks++) qf[ks] = src[ks * 32];
+    }
+    const int myq = grp * QG + t;                       // the query whose scores this lane receives
+    const float qsc = myq < p.nq ? p.qscale[myq] : 0.0f;
+    float thr_s = -__builtin_huge_valf();
+    int thr_i = ID_NONE;
+
+    // full tiles only: the last n % 16 rows are scored by the merge kernel
+    const int64_t ntiles = p.n / SCAN_TILE;
+    const int64_t wstride = (int64_t)gridDim.x * SCAN_WARPS;
+    const int64_t first = (int64_t)blockIdx.x * SCAN_WARPS + warp;
+
+    auto issue = [&](int64_t tile, int s) {
+        if (lane == 0) {
+            const int64_t row = tile * SCAN_TILE;
+            const uint32_t dst = s_u32(ring + (size_t)s * C::STAGE);
+            const uint32_t bar = bar0 + 8 * s;
+            s_mbar_expect_tx(bar, C::STAGE);
+            s_bulk_g2s(dst, p.packed + row * C::PD, C::RT, bar);
+            s_bulk_g2s(dst + C::RT, p.norms + row, SCAN_TILE * 4, bar);
+        }
+    };
+
+    int64_t ptile = first, ctile = first;
+    uint32_t issued = 0, consumed = 0;
+    while (issued < NS && ptile < ntiles) { issue(ptile, issued % NS); ptile += wstride; issued++; }
+    bool failed = false;
+
+    for (; ctile < ntiles; ctile += wstride) {
+        const int s = consumed % NS;
+        if (!s_mbar_wait(bar0 + 8 * s, (consumed / NS) & 1)) failed = true;
+        if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
+        const uint8_t* rt = ring + (size_t)s * C::STAGE;
+        const float* nr = reinterpret_cast<const float*>(rt + C::RT);
+        const int64_t row0 = ctile * SCAN_TILE;
+
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        uint32_t P[KeyWords<D>::NW][4];
+        gather_key_words<D, BITS>(rt, C::PD, g, t, P);
+        uint32_t iw[KeyWords<D>::NW][4];
+#pragma unroll
+        for (int w = 0; w < KeyWords<D>::NW; w++)
+#pragma unroll
+            for (int u = 0; u < 4; u++) iw[w][u] = pair_index_word<BITS>(P[w], u);
+#pragma unroll
+        for (int ks = 0; ks < C::KS; ks++) {
+            uint2 e[4];
+#pragma unroll
+            for (int half = 0; half < 2; half++)
+#pragma unroll
+                for (int second = 0; second < 2; second++) {
+                    int u, w, bl;
+                    key_element_slot<D>(2 * ks + half, second != 0, u, w, bl);
+                    e[2 * half + second] = lut[((iw[w][u] >> (8 * bl)) & 0xFFu) * 32 + lane];
+                }
+            s_mma(acc, e[0].x, e[1].x, e[2].x, e[3].x, qf[ks].x, qf[ks].y);
+            s_mma(acc, e[0].y, e[1].y, e[2].y, e[3].y, qf[ks].z, qf[ks].w);
+        }
+        const bool v0 = row0 + g < p.n, v1 = row0 + g + 8 < p.n;
+        const float sc0 = v0 ? (acc[0] + acc[1]) * (nr[g] * qsc) : 0.0f;
+        const float sc1 = v1 ? (acc[2] + acc[3]) * (nr[g + 8] * qsc) : 0.0f;
+        const int id0 = (int)(row0 + g), id1 = id0 + 8;
+
+        // ---- candidates: lanes whose score beats their query's threshold ----
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const float sc = r ? sc1 : sc0;
+            const int id = r ? id1 : id0;
+            const bool ok = (r ? v1 : v0) && myq < p.nq && better(sc, id, thr_s, thr_i);
+            uint32_t mask = __ballot_sync(0xffffffffu, ok);
+            while (mask) {
+                const int leader = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const float bs = __shfl_sync(0xffffffffu, sc, leader);
+                const int bid = __shfl_sync(0xffffffffu, id, leader);
+                const int bq = leader & 3;
+                list_insert(ls + bq * p.kk, li + bq * p.kk, p.kk, bs, bid, lane);
+                if (t == bq) { thr_s = ls[bq * p.kk + p.kk - 1]; thr_i = li[bq * p.kk + p.kk - 1]; }
+            }
+        }
+
+        __syncwarp();
+        if (ptile < ntiles) { issue(ptile, s); ptile += wstride; issued++; }
+        consumed++;
+    }
+
+    if (failed) {
+        if (lane == 0) atomicExch(p.status, 1);
+        for (uint32_t i = consumed; i < issued; i++) (void)s_mbar_wait(bar0 + 8 * (i % NS), (i / NS) & 1);
+    }
+    // ---- this warp's candidates -> global ----
+    __syncwarp();
+    const int64_t wid = (int64_t)blockIdx.x * SCAN_WARPS + warp;
+    for (int jq = 0; jq < QG; jq++) {
+        const int q = grp * QG + jq;
+        if (q >= p.nq) break;
+        const int64_t base = ((int64_t)q * p.lists_per_query + wid) * p.kk;
+        for (int e = lane; e < p.kk; e += 32) { p.cand_s[base + e] = ls[jq * p.kk + e]; p.cand_id[base + e] = li[jq * p.kk + e]; }
+    }
+}
+
+
+// =================================================================================================
+// 2b. generic scan: any dim (multiple of 8, <= 512), bits 1..4.  One query per blockIdx.y, one row per
+// lane; the float32 table and the summation order are the upstream ones, so these scores are exact.
+// =================================================================================================
+__global__ void __launch_bounds__(SCAN_WARPS * 32) scan_generic_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int levels = 1 << p.bits, bpp = (p.dim + 7) >> 3, pd = p.bits * bpp;
+    float* T = reinterpret_cast<float*>(smem_raw);                    // dim * levels
+    float* lists_s = T + p.dim * levels;
+    int* lists_i = reinterpret_cast<int*>(lists_s + SCAN_WARPS * p.kk);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q = blockIdx.y;
+    float* ls = lists_s + warp * p.kk;
+    int* li = lists_i + warp * p.kk;
+    for (int e = threadIdx.x; e < p.dim * levels; e += blockDim.x)
+        T[e] = __fmul_rn(p.qrot[(int64_t)q * p.dim + e / levels], p.cent[e % levels]);
+    for (int e = lane; e < p.kk; e += 32) { ls[e] = -__builtin_huge_valf(); li[e] = ID_NONE; }
+    __syncthreads();
+    float thr_s = -__builtin_huge_valf();
+    int thr_i = ID_NONE;
+    const int64_t n_main = p.n - p.n % SCAN_TILE;   // the tail belongs to the merge kernel
+    const int64_t stride = (int64_t)gridDim.x * SCAN_WARPS * 32;
+    for (int64_t base = ((int64_t)blockIdx.x * SCAN_WARPS + warp) * 32; base < n_main; base += stride) {
+        const int64_t r = base + lane;
+        const bool valid = r < n_main;
+        float sc = 0.0f;
+        if (valid) {
+            const uint8_t* row = p.packed + r * pd;
+            float dot = 0.0f;
+            for (int m = 0; m < bpp; m++) {
+                uint32_t pl[4] = {0, 0, 0, 0};
+                for (int b = 0; b < p.bits; b++) pl[b] = row[b * bpp + m];
+                const int lim = min(8, p.dim - 8 * m);
+                for (int t = 0; t < lim; t++) {
+                    const int sh = 7 - t;
+                    const uint32_t c = ((pl[0] >> sh) & 1u) | (((pl[1] >> sh) & 1u) << 1) |
+                                       (((pl[2] >> sh) & 1u) << 2) | (((pl[3] >> sh) & 1u) << 3);
+                    dot = __fadd_rn(dot, T[(8 * m + t) * levels + c]);
+                }
+            }
+            sc = __fmul_rn(dot, p.norms[r]);
+        }
+        uint32_t mask = __ballot_sync(0xffffffffu, valid && better(sc, (int)r, thr_s, thr_i));
+        while (mask) {
+            const int leader = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const float bs = __shfl_sync(0xffffffffu, sc, leader);
+            const int bid = __shfl_sync(0xffffffffu, (int)r, leader);
+            list_insert(ls, li, p.kk, bs, bid, lane);
+            thr_s = ls[p.kk - 1]; thr_i = li[p.kk - 1];
+        }
+    }
+    __syncwarp();
+    const int64_t wid = (int64_t)blockIdx.x * SCAN_WARPS + warp;
+    const int64_t out = ((int64_t)q * p.lists_per_query + wid) * p.kk;
+    for (int e = lane; e < p.kk; e += 32) { p.cand_s[out + e] = ls[e]; p.cand_id[out + e] = li[e]; }
+}
+
+// =================================================================================================
+// 3. merge: best kk candidates per query -> exact float32 re-score -> sort -> top k
+// =================================================================================================
+constexpr int MERGE_THREADS = 128;
+constexpr int MERGE_MAX = TQB_SCAN_MAX_K + SCAN_MARGIN + SCAN_TILE;   // selected + tail rows
+
+__global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int levels = 1 << p.bits, bpp = (p.dim + 7) >> 3, pd = p.bits * bpp;
+    float* T = reinterpret_cast<float*>(smem_raw);     // dim * levels
+    __shared__ float sel_s[MERGE_MAX];
+    __shared__ int sel_i[MERGE_MAX];
+    __shared__ float red_s[MERGE_THREADS / 32];
+    __shared__ int red_i[MERGE_THREADS / 32];
+    __shared__ float cur_s;
+    __shared__ int cur_i;
+    const int q = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < p.dim * levels; e += blockDim.x)
+        T[e] = __fmul_rn(p.qrot[(int64_t)q * p.dim + e / levels], p.cent[e % levels]);
+    const int64_t ncand = (int64_t)p.lists_per_query * p.kk;
+    const float* cs = p.cand_s + (int64_t)q * ncand;
+    const int* ci = p.cand_id + (int64_t)q * ncand;
+    // ---- selection by the scan's scores: round r takes the best candidate worse than round r-1's ----
+    float prev_s = __builtin_huge_valf();
+    int prev_i = -1;
+    int nsel = 0;
+    for (int r = 0; r < p.kk; r++) {
+        float bs = -__builtin_huge_valf();
+        int bi = ID_NONE;
+        for (int64_t e = tid; e < ncand; e += blockDim.x) {
+            const float s = cs[e];
+            const int id = ci[e];
+            if (id != ID_NONE && better(prev_s, prev_i, s, id) && better(s, id, bs, bi)) { bs = s; bi = id; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(os, oi, bs, bi)) { bs = os; bi = oi; }
+        }
+        if (lane == 0) { red_s[warp] = bs; red_i[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < MERGE_THREADS / 32; w++)
+                if (better(red_s[w], red_i[w], bs, bi)) { bs = red_s[w]; bi = red_i[w]; }
+            cur_s = bs; cur_i = bi;
+            if (bi != ID_NONE) { sel_i[r] = bi; }
+        }
+        __syncthreads();
+        prev_s = cur_s; prev_i = cur_i;
+        if (prev_i == ID_NONE) break;
+        nsel = r + 1;
+    }
+    // ---- tail rows (n % 16) always take part ----
+    const int tail = (int)(p.n % SCAN_TILE);
+    if (tid < tail) sel_i[nsel + tid] = (int)(p.n - tail + tid);
+    const int total = nsel + tail;
+    __syncthreads();
+    // ---- exact re-score, upstream order: dims ascending, add table entries, then * norm ----
+    for (int e = tid; e < total; e += blockDim.x) {
+        const int id = sel_i[e];
+        const uint8_t* row = p.packed + (int64_t)id * pd;
+        float dot = 0.0f;
+        for (int m = 0; m < bpp; m++) {
+            uint32_t pl[4] = {0, 0, 0, 0};
+            for (int b = 0; b < p.bits; b++) pl[b] = row[b * bpp + m];
+            const int lim = min(8, p.dim - 8 * m);
+            for (int t = 0; t < lim; t++) {
+                const int sh = 7 - t;
+                const uint32_t c = ((pl[0] >> sh) & 1u) | (((pl[1] >> sh) & 1u) << 1) |
+                                   (((pl[2] >> sh) & 1u) << 2) | (((pl[3] >> sh) & 1u) << 3);
+                dot = __fadd_rn(dot, T[(8 * m + t) * levels + c]);
+            }
+        }
+        sel_s[e] = __fmul_rn(dot, p.norms[id]);
+    }
+    __syncthreads();
+    // ---- rank by counting, emit the first k ----
+    for (int e = tid; e < total; e += blockDim.x) {
+        int rank = 0;
+        for (int o = 0; o < total; o++) rank += better(sel_s[o], sel_i[o], sel_s[e], sel_i[e]) ? 1 : 0;
+        if (rank < p.k) {
+            p.out_scores[(int64_t)q * p.k + rank] = sel_s[e];
+            p.out_ids[(int64_t)q * p.k + rank] = (int64_t)sel_i[e] + p.id_offset;
+        }
+    }
+    for (int e = total + tid; e < p.k; e += blockDim.x) {   // fewer rows than k: pad like upstream
+        p.out_scores[(int64_t)q * p.k + e] = -__builtin_huge_valf();
+        p.out_ids[(int64_t)q * p.k + e] = -1;
+    }
+}
+
+}  // namespace tqb
+
+// =================================================================================================
+// 4. merge of per-shard top-k lists (row-sharded search: one list per shard, gathered by the caller)
+// =================================================================================================
+namespace tqb {
+
+__device__ __forceinline__ bool better64(float s, int64_t id, float ts, int64_t tid) {
+    // padding entries (-1) lose against everything real
+    if (id < 0) return false;
+    if (tid < 0) return true;
+    return s > ts || (s == ts && id < tid);
+}
+
+__global__ void topk_merge_kernel(const float* __restrict__ scores, const int64_t* __restrict__ ids, int parts,
+                                  int k, float* __restrict__ out_scores, int64_t* __restrict__ out_ids) {
+    const int q = blockIdx.x;
+    const int total = parts * k;
+    const float* s = scores + (int64_t)q * total;
+    const int64_t* id = ids + (int64_t)q * total;
+    for (int e = threadIdx.x; e < k; e += blockDim.x) {   // defaults: padding
+        out_scores[(int64_t)q * k + e] = -__builtin_huge_valf();
+        out_ids[(int64_t)q * k + e] = -1;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        if (id[e] < 0) continue;
+        int rank = 0;
+        for (int o = 0; o < total; o++) rank += (o != e && better64(s[o], id[o], s[e], id[e])) ? 1 : 0;
+        if (rank < k) { out_scores[(int64_t)q * k + rank] = s[e]; out_ids[(int64_t)q * k + rank] = id[e]; }
+    }
+}
+
+struct ScanPlan {
+    size_t off_status, off_qrot, off_qfrag, off_qscale, off_cs, off_ci, total;
+    int kk, lists, ngroups;
+    bool mma;
+};
+
+static inline size_t s_align(size_t v) { return (v + 255) / 256 * 256; }
+
+static ScanPlan plan_scan(int nq, int64_t n, int dim, int bits, int k) {
+    ScanPlan pl{};
+    pl.mma = (dim == 64 || dim == 128) && bits >= 2 && bits <= 4;
+    pl.kk = k + SCAN_MARGIN;
+    pl.lists = sm_count() * SCAN_WARPS;
+    pl.ngroups = (nq + QG - 1) / QG;
+    size_t off = 0;
+    pl.off_status = off; off = s_align(off + 256);
+    pl.off_qrot = off;   off = s_align(off + (size_t)nq * dim * 4);
+    pl.off_qfrag = off;  off = s_align(off + (size_t)pl.ngroups * (dim / 16 + 1) * 32 * 16);
+    pl.off_qscale = off; off = s_align(off + (size_t)nq * 4);
+    const size_t cand = (size_t)nq * pl.lists * pl.kk;
+    pl.off_cs = off; off = s_align(off + cand * 4);
+    pl.off_ci = off; off = s_align(off + cand * 4);
+    pl.total = off;
+    (void)n;
+    return pl;
+}
+
+template <int D, int BITS>
+static int launch_scan(const ScanParams& p, int ngroups, cudaStream_t st) {
+    using C = ScanCfg<D, BITS>;
+    const size_t lists = (size_t)SCAN_WARPS * QG * p.kk * 8;
+    const size_t fixed = (size_t)C::LUT_BYTES + lists;
+    const int NS8 = (fixed + (size_t)SCAN_WARPS * 8 * (C::STAGE + 8) <= 200 * 1024);
+    const int ns = NS8 ? 8 : 4;
+    const size_t smem = fixed + (size_t)SCAN_WARPS * ns * (C::STAGE + 8);
+    if (smem > 220 * 1024) return fail(TQB_ERR_UNSUPPORTED, "scan_topk: k = %d needs %zu bytes of shared memory", p.k, smem);
+    dim3 grid(p.lists_per_query / SCAN_WARPS, ngroups);
+    if (ns == 8) {
+        auto kern = scan_kernel<D, BITS, 8>;
+        TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, SCAN_WARPS * 32, smem, st>>>(p);
+    } else {
+        auto kern = scan_kernel<D, BITS, 4>;
+        TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, SCAN_WARPS * 32, smem, st>>>(p);
+    }
+    return check_launch("scan");
+}
+
+}  // namespace tqb
+
+extern "C" size_t tqb_scan_topk_workspace_bytes(int nq, int64_t n, int dim, int bits, int k) {
+    if (nq <= 0 || dim <= 0 || k <= 0 || k > TQB_SCAN_MAX_K) return 0;
+    return tqb::plan_scan(nq, n, dim, bits, k).total;
+}
+
+extern "C" int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed, const float* norms,
+                             int64_t n, int dim, int bits, const float* rotation, const float* centroids,
+                             int k, int64_t id_offset, void* workspace, size_t workspace_bytes,
+                             float* out_scores, int64_t* out_ids, void* stream) {
+    using namespace tqb;
+    TQB_REQUIRE(nq >= 0 && n >= 0, "scan_topk: negative size");
+    TQB_REQUIRE(bits >= 1 && bits <= 4, "scan_topk: bit_width must be 1-4, got %d", bits);
+    TQB_REQUIRE(k >= 1, "scan_topk: k must be positive, got %d", k);
+    if (k > TQB_SCAN_MAX_K) return fail(TQB_ERR_UNSUPPORTED, "scan_topk: k = %d exceeds the limit %d", k, TQB_SCAN_MAX_K);
+    if (dim < 8 || dim > 512 || (dim & 7))
+        return fail(TQB_ERR_UNSUPPORTED, "scan_topk: dim must be a multiple of 8 in 8..512, got %d", dim);
+    if (n >= 0x7fffffff) return fail(TQB_ERR_UNSUPPORTED, "scan_topk: at most 2^31-2 rows per call (shard the index)");
+    if (nq == 0) return TQB_OK;
+    TQB_REQUIRE(queries && rotation && centroids && workspace && out_scores && out_ids, "scan_topk: null pointer");
+    TQB_REQUIRE(n == 0 || (packed && norms), "scan_topk: null database");
+    TQB_REQUIRE((uintptr_t)workspace % 256 == 0, "scan_topk: workspace must be 256-byte aligned");
+    const ScanPlan pl = plan_scan(nq, n, dim, bits, k);
+    if (workspace_bytes < pl.total)
+        return fail(TQB_ERR_WORKSPACE, "scan_topk: workspace %zu bytes < required %zu", workspace_bytes, pl.total);
+    if (pl.mma) TQB_REQUIRE(((uintptr_t)packed | (uintptr_t)norms) % 16 == 0, "scan_topk: database arrays must be 16-byte aligned");
+
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    ScanParams p{};
+    p.packed = packed; p.norms = norms; p.n = n; p.dim = dim; p.bits = bits; p.nq = nq; p.k = k; p.kk = pl.kk;
+    p.rot = rotation; p.cent = centroids; p.queries = queries; p.id_offset = id_offset;
+    p.status = reinterpret_cast<int*>(ws + pl.off_status);
+    p.qrot = reinterpret_cast<float*>(ws + pl.off_qrot);
+    p.qfrag = reinterpret_cast<uint32_t*>(ws + pl.off_qfrag);
+    p.qscale = reinterpret_cast<float*>(ws + pl.off_qscale);
+    p.cand_s = reinterpret_cast<float*>(ws + pl.off_cs);
+    p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
+    p.out_scores = out_scores; p.out_ids = out_ids;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    const int64_t ntiles = n / SCAN_TILE;
+    const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(sm_count(), ceil_div(ntiles, SCAN_WARPS)));
+    p.lists_per_query = gx * SCAN_WARPS;
+
+    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + QG) * dim, st>>>(p, pl.mma ? 1 : 0);
+    if (int e = check_launch("scan_prepare")) return e;
+
+    if (pl.mma) {
+        int e = TQB_ERR_UNSUPPORTED;
+#define TQB_CASE(d, b) if (dim == d && bits == b) e = launch_scan<d, b>(p, pl.ngroups, st);
+        TQB_CASE(64, 2) TQB_CASE(64, 3) TQB_CASE(64, 4) TQB_CASE(128, 2) TQB_CASE(128, 3) TQB_CASE(128, 4)
+#undef TQB_CASE
+        if (e) return e;
+    } else {
+        const size_t smem = sizeof(float) * (size_t)dim * (1 << bits) + (size_t)SCAN_WARPS * p.kk * 8;
+        TQB_CUDA(cudaFuncSetAttribute(scan_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid(gx, nq);
+        scan_generic_kernel<<<grid, SCAN_WARPS * 32, smem, st>>>(p);
+        if (int e = check_launch("scan_generic")) return e;
+    }
+    const size_t msmem = sizeof(float) * (size_t)dim * (1 << bits);
+    scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
+    return check_launch("scan_merge");
+}
+
+extern "C" int tqb_topk_merge(const float* scores, const int64_t* ids, int nq, int parts, int k,
+                              float* out_scores, int64_t* out_ids, void* stream) {
+    TQB_REQUIRE(nq >= 0 && parts >= 1 && k >= 1, "topk_merge: bad sizes");
+    if (nq == 0) return TQB_OK;
+    TQB_REQUIRE(scores && ids && out_scores && out_ids, "topk_merge: null pointer");
+    tqb::topk_merge_kernel<<<nq, 128, 0, (cudaStream_t)stream>>>(scores, ids, parts, k, out_scores, out_ids);
+    return tqb::check_launch("topk_merge");
+}

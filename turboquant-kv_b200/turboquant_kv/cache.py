@@ -1,0 +1,335 @@
+"""QuantizedKVCache -- packed TurboQuant KV cache, B200 build.
+
+Same constructor and methods as upstream ``turboquant_kv/cache.py:29-381`` (``append``,
+``attention_scores``, ``attention_values``, ``_dequantize_keys/_values``, ``memory_bytes``,
+``compression_ratio``).  Storage is written by the fused quantise kernels and read by kernels that
+work on the packed codes; nothing is dequantised to attend.
+
+Additions for serving (none changes upstream behaviour):
+  * ``batch_size=B`` gives every sequence of a batch its own cache rows (upstream keeps a single
+    sequence and silently drops ``key[1:]``, cache.py:157-160 -- still the behaviour when
+    ``batch_size`` is left at None);
+  * ``decode_attention(layer, query)``: the fused one-token decode step (scores, softmax, values,
+    grouped-query heads) in three kernel launches;
+  * per-layer sequence lengths also live on the device so the decode path never synchronises.
+
+Prod mode: upstream allocates ``key_bits`` planes per token but ``quantize_prod`` returns
+``key_bits - 1`` (cache.py:84-85 vs reference.py:441), so its ``append`` raises in that mode.  This
+build raises the same kind of error, with a message that says why.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _native as N
+from .config import TurboQuantConfig
+from .reference import _make_qjl_matrix, lloyd_max_codebook, make_rotation_matrix
+
+
+def _pad16(n: int) -> int:
+    return (n + 15) // 16 * 16
+
+
+class QuantizedKVCache:
+    """Pre-allocated packed keys/values for all layers of one model (or one tensor-parallel shard)."""
+
+    def __init__(self, config: TurboQuantConfig, num_layers: int, max_seq_len: int, num_heads: int,
+                 head_dim: int, device: str = "cuda", batch_size: Optional[int] = None):
+        N.require_cuda()
+        self.config = config
+        self.num_layers = num_layers
+        self.max_seq_len = max_seq_len
+        self.num_heads = num_heads
+        self.head_dim = head_dim
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("QuantizedKVCache (B200 build) lives on a CUDA device; there is no CPU path")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        if config.mode not in ("mse", "prod"):
+            raise ValueError(f"Unknown mode: {config.mode}")
+        self.batch_size = batch_size
+        self._batch = 1 if batch_size is None else int(batch_size)
+        self._pitch = _pad16(max_seq_len)  # rows per (sequence, head); tiles of 16 never straddle units
+
+        self.seq_lens = torch.zeros(num_layers, dtype=torch.long)  # host copy, as upstream
+        self._seq_lens_dev = torch.zeros(num_layers, self._batch, dtype=torch.int32, device=self.device)
+
+        dev = self.device
+        self._key_rotation = make_rotation_matrix(head_dim, seed=config.seed, method=config.rotation).to(dev)
+        self._val_rotation = make_rotation_matrix(head_dim, seed=config.seed + 1, method=config.rotation).to(dev)
+        self._key_codebook = lloyd_max_codebook(config.key_bits, head_dim)
+        self._val_codebook = lloyd_max_codebook(config.value_bits, head_dim)
+        self._kb_dev = tuple(t.to(dev) for t in self._key_codebook)
+        self._vb_dev = tuple(t.to(dev) for t in self._val_codebook)
+
+        self._has_outliers = config.outlier_channels > 0
+        if self._has_outliers:  # built and unused, exactly like upstream
+            self._key_codebook_outlier = lloyd_max_codebook(config.key_bits + 1, head_dim)
+            self._val_codebook_outlier = lloyd_max_codebook(config.value_bits + 1, head_dim)
+
+        self._is_prod = config.mode == "prod"
+        if self._is_prod:
+            self._key_S = _make_qjl_matrix(head_dim, head_dim, config.seed, dev)
+            self._val_S = _make_qjl_matrix(head_dim, head_dim, config.seed + 1, dev)
+            self._key_codebook_prod = lloyd_max_codebook(config.key_bits - 1, head_dim)
+            self._val_codebook_prod = lloyd_max_codebook(config.value_bits - 1, head_dim)
+
+        bpp = (head_dim + 7) // 8
+        self._pk, self._pv = config.key_bits * bpp, config.value_bits * bpp
+        B, H, P = self._batch, num_heads, self._pitch
+
+        def codes(width):
+            return [torch.zeros(B, H, P, width, dtype=torch.uint8, device=dev) for _ in range(num_layers)]
+
+        def scalars():
+            return [torch.zeros(B, H, P, dtype=torch.float32, device=dev) for _ in range(num_layers)]
+
+        self._kp, self._kn, self._vp, self._vn = codes(self._pk), scalars(), codes(self._pv), scalars()
+
+        self._protected = config.protected_layers > 0
+        if self._protected:
+            self._key_fp = [torch.zeros(B, H, max_seq_len, head_dim, dtype=torch.float16, device=dev)
+                            for _ in range(config.protected_layers)]
+            self._val_fp = [torch.zeros(B, H, max_seq_len, head_dim, dtype=torch.float16, device=dev)
+                            for _ in range(config.protected_layers)]
+        self._workspace: Optional[torch.Tensor] = None
+
+    # ---- upstream-shaped views of the storage: (num_heads, max_seq_len, ...) when batch_size is None
+    def _view(self, store):
+        out = [t[:, :, : self.max_seq_len] for t in store]
+        return [t[0] for t in out] if self.batch_size is None else out
+
+    @property
+    def _key_packed(self):
+        return self._view(self._kp)
+
+    @property
+    def _key_norms(self):
+        return self._view(self._kn)
+
+    @property
+    def _val_packed(self):
+        return self._view(self._vp)
+
+    @property
+    def _val_norms(self):
+        return self._view(self._vn)
+
+    def _is_protected_layer(self, layer_id: int) -> bool:
+        return self._protected and layer_id < self.config.protected_layers
+
+    # ------------------------------------------------------------------------------------------
+    def append(self, layer_id: int, key: torch.Tensor, value: torch.Tensor):
+        """Quantise and store new tokens.
+
+        key / value: (num_heads, new, head_dim), or (batch, num_heads, new, head_dim).  Without
+        ``batch_size`` only batch item 0 is kept (upstream behaviour); with it, ``batch`` must match.
+        """
+        if key.dim() == 4:
+            if self.batch_size is None:
+                key, value = key[:1], value[:1]
+            elif key.shape[0] != self._batch:
+                raise RuntimeError(f"expected batch {self._batch}, got {key.shape[0]}")
+        else:
+            assert key.dim() == 3, f"Expected 3D key, got {key.dim()}D"
+            if self._batch != 1:
+                raise RuntimeError("a batched cache needs (batch, heads, new, head_dim) inputs")
+            key, value = key.unsqueeze(0), value.unsqueeze(0)
+        B, H, T, D = key.shape
+        if H != self.num_heads or D != self.head_dim:
+            raise RuntimeError(f"expected (*, {self.num_heads}, new, {self.head_dim}), got {tuple(key.shape)}")
+        pos = int(self.seq_lens[layer_id])
+        if pos + T > self.max_seq_len:
+            raise RuntimeError(f"cache overflow: {pos} + {T} > max_seq_len {self.max_seq_len}")
+
+        if self._is_protected_layer(layer_id):
+            self._key_fp[layer_id][:, :, pos:pos + T] = key.to(self.device).half()
+            self._val_fp[layer_id][:, :, pos:pos + T] = value.to(self.device).half()
+        elif self._is_prod:
+            raise RuntimeError(
+                "QuantizedKVCache in prod mode: upstream stores key_bits planes per token but quantize_prod "
+                "yields key_bits - 1, so upstream append() fails with a shape error; not supported here either")
+        else:
+            k = self._as_rows(key)
+            v = self._as_rows(value)
+            # rows are (batch*head, token); the write position is read on the device so that a captured
+            # CUDA graph of a decode step keeps appending at the right place when replayed
+            rm = N.RowMap(T, self._pitch, 1, 0, N.ptr(self._seq_lens_dev[layer_id]), H, None, 1)
+            cfg = self.config
+            with torch.cuda.device(self.device):
+                N.check(N.lib().tqb_kv_append(
+                    N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), B * H * T, D, D,
+                    N.ptr(self._key_rotation), N.ptr(self._kb_dev[0]), cfg.key_bits,
+                    N.ptr(self._val_rotation), N.ptr(self._vb_dev[0]), cfg.value_bits,
+                    N.ptr(self._kp[layer_id]), N.ptr(self._kn[layer_id]),
+                    N.ptr(self._vp[layer_id]), N.ptr(self._vn[layer_id]),
+                    rm, N.stream_of(k)))
+        self.seq_lens[layer_id] += T
+        self._seq_lens_dev[layer_id] += T
+
+    def _as_rows(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.to(self.device)
+        if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            x = x.float()
+        return x.contiguous()
+
+    # ------------------------------------------------------------------------------------------
+    def _dequantize(self, layer_id: int, packed, norms, bits, rotation, centroids, fp_store):
+        seq = int(self.seq_lens[layer_id])
+        B, H, D = self._batch, self.num_heads, self.head_dim
+        if seq == 0:
+            out = torch.zeros(B, H, 0, D, dtype=torch.float32, device=self.device)
+        elif self._is_protected_layer(layer_id):
+            out = fp_store[layer_id][:, :, :seq].float()
+        else:
+            p = packed[layer_id][:, :, :seq].contiguous().view(B * H * seq, -1)
+            n = norms[layer_id][:, :, :seq].contiguous().view(-1)
+            out = torch.empty(B * H * seq, D, dtype=torch.float32, device=self.device)
+            with torch.cuda.device(self.device):
+                N.check(N.lib().tqb_dequantize_mse(N.ptr(p), N.ptr(n), B * H * seq, D, N.ptr(rotation),
+                                                   N.ptr(centroids), bits, N.ptr(out), N.F32, N.stream_of(p)))
+            out = out.view(B, H, seq, D)
+        return out[0] if self.batch_size is None else out
+
+    def _dequantize_keys(self, layer_id: int) -> torch.Tensor:
+        """Dense keys (num_heads, seq, head_dim) float32 (with a leading batch dim for batched caches)."""
+        return self._dequantize(layer_id, self._kp, self._kn, self.config.key_bits, self._key_rotation,
+                                self._kb_dev[1], getattr(self, "_key_fp", None))
+
+    def _dequantize_values(self, layer_id: int) -> torch.Tensor:
+        return self._dequantize(layer_id, self._vp, self._vn, self.config.value_bits, self._val_rotation,
+                                self._vb_dev[1], getattr(self, "_val_fp", None))
+
+    # ------------------------------------------------------------------------------------------
+    def attention_scores(self, layer_id: int, query: torch.Tensor) -> torch.Tensor:
+        """Logits q.k / sqrt(head_dim) straight from the packed keys.
+
+        query: (batch, num_heads, seq_q, head_dim) or (num_heads, seq_q, head_dim); every batch item
+        attends to the same cached sequence (upstream semantics).  Returns (..., seq_q, seq_kv).
+        """
+        if self._batch != 1:
+            raise RuntimeError("attention_scores follows upstream's single-sequence semantics; "
+                               "use decode_attention on a batched cache")
+        has_batch = query.dim() == 4
+        q = query if has_batch else query.unsqueeze(0)
+        q = q.reshape(q.shape[0], self.num_heads, -1, self.head_dim).to(self.device).float()
+        nb, H, sq, D = q.shape
+        seq = int(self.seq_lens[layer_id])
+        scale = 1.0 / math.sqrt(D)
+        if self._is_protected_layer(layer_id) or seq == 0:
+            keys = self._dequantize_keys(layer_id)
+            keys = keys if keys.dim() == 3 else keys[0]
+            logits = torch.matmul(q, keys.transpose(-2, -1).unsqueeze(0)) * scale
+        else:
+            logits = torch.empty(nb, H, sq, seq, dtype=torch.float32, device=self.device)
+            with torch.cuda.device(self.device):
+                for h in range(H):
+                    qh = q[:, h].reshape(nb * sq, D).contiguous()
+                    out = torch.empty(nb * sq, seq, dtype=torch.float32, device=self.device)
+                    pk = self._kp[layer_id][0, h, :seq]
+                    kn = self._kn[layer_id][0, h, :seq]
+                    N.check(N.lib().tqb_attention_scores_packed(
+                        N.ptr(qh), nb * sq, D, N.ptr(pk), N.ptr(kn), seq, N.ptr(self._kb_dev[1]),
+                        N.ptr(self._key_rotation), self.config.key_bits, N.ptr(out), N.stream_of(qh)))
+                    logits[:, h] = out.view(nb, sq, seq)
+            logits *= scale
+        return logits if has_batch else logits.squeeze(0)
+
+    def attention_values(self, layer_id: int, attn_weights: torch.Tensor) -> torch.Tensor:
+        """Weighted sum of the cached values: (..., seq_q, seq_kv) -> (..., seq_q, head_dim)."""
+        if self._batch != 1:
+            raise RuntimeError("attention_values follows upstream's single-sequence semantics; "
+                               "use decode_attention on a batched cache")
+        has_batch = attn_weights.dim() == 4
+        w = (attn_weights if has_batch else attn_weights.unsqueeze(0)).to(self.device).float()
+        nb, H, sq, seq = w.shape
+        D = self.head_dim
+        if self._is_protected_layer(layer_id) or seq == 0:
+            vals = self._dequantize_values(layer_id)
+            vals = vals if vals.dim() == 3 else vals[0]
+            out = torch.matmul(w, vals.unsqueeze(0))
+        else:
+            out = torch.empty(nb, H, sq, D, dtype=torch.float32, device=self.device)
+            with torch.cuda.device(self.device):
+                for h in range(H):
+                    wh = w[:, h].reshape(nb * sq, seq).contiguous()
+                    oh = torch.empty(nb * sq, D, dtype=torch.float32, device=self.device)
+                    pv = self._vp[layer_id][0, h, :seq]
+                    vn = self._vn[layer_id][0, h, :seq]
+                    N.check(N.lib().tqb_attention_values_packed(
+                        N.ptr(wh), nb * sq, seq, D, N.ptr(pv), N.ptr(vn), N.ptr(self._vb_dev[1]),
+                        N.ptr(self._val_rotation), self.config.value_bits, N.ptr(oh), N.stream_of(wh)))
+                    out[:, h] = oh.view(nb, sq, D)
+        return out if has_batch else out.squeeze(0)
+
+    # ------------------------------------------------------------------------------------------
+    def decode_attention(self, layer_id: int, query: torch.Tensor, scale: Optional[float] = None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """softmax(scale * q K^T) V for ONE new token per sequence, fused, over the packed cache.
+
+        query: (batch, q_heads, head_dim) or (batch, q_heads, 1, head_dim); q_heads must be a multiple of
+        the cache's (KV) heads -- query head h reads KV head h // group.  Returns the query's shape, in
+        the query's dtype.  Stream-ordered, no host synchronisation.
+        """
+        if self._is_protected_layer(layer_id) or self._is_prod:
+            raise RuntimeError("decode_attention covers MSE-quantised layers")
+        squeeze = query.dim() == 4
+        q = (query[:, :, 0] if squeeze else query).to(self.device)
+        if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            q = q.float()
+        q = q.contiguous()
+        B, HQ, D = q.shape
+        if B != self._batch or D != self.head_dim or HQ % self.num_heads:
+            raise RuntimeError(f"query {tuple(query.shape)} does not fit cache (batch {self._batch}, "
+                               f"kv heads {self.num_heads}, head_dim {self.head_dim})")
+        if scale is None:
+            scale = 1.0 / math.sqrt(D)
+        max_len = self._pitch if torch.cuda.is_current_stream_capturing() else int(self.seq_lens[layer_id])
+        need = max(N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self._pitch),
+                   N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, max_len))
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        res = out if out is not None else torch.empty(B, HQ, D, dtype=q.dtype, device=self.device)
+        cfg = self.config
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_decode_attention(
+                N.ptr(q), N.dtype_code(q.dtype), B, HQ, self.num_heads, D,
+                N.ptr(self._kp[layer_id]), N.ptr(self._kn[layer_id]), N.ptr(self._vp[layer_id]),
+                N.ptr(self._vn[layer_id]), self._pitch, N.ptr(self._seq_lens_dev[layer_id]), max_len,
+                None, 0, 0, N.ptr(self._key_rotation), N.ptr(self._kb_dev[1]), cfg.key_bits,
+                N.ptr(self._val_rotation), N.ptr(self._vb_dev[1]), cfg.value_bits, float(scale),
+                N.ptr(self._workspace), self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype),
+                N.stream_of(q)))
+        return res.unsqueeze(2) if squeeze else res
+
+    def decode_status(self) -> int:
+        """0 when every bounded device-side wait of the last decode_attention completed (synchronises)."""
+        return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
+
+    # ------------------------------------------------------------------------------------------
+    def memory_bytes(self) -> int:
+        """Bytes of packed codes + norms in use (upstream formula, cache.py:341-365), per stored sequence."""
+        total = 0
+        for layer_id in range(self.num_layers):
+            seq = int(self.seq_lens[layer_id])
+            if seq == 0:
+                continue
+            if self._is_protected_layer(layer_id):
+                total += 2 * self.num_heads * seq * self.head_dim * 2
+                continue
+            per_token = self._pk + self._pv + 8
+            if self._is_prod:
+                per_token += 2 * ((self.head_dim + 7) // 8) + 8
+            total += self.num_heads * seq * per_token
+        return total * self._batch
+
+    @property
+    def compression_ratio(self) -> float:
+        """fp16 bytes of the same tokens divided by memory_bytes()."""
+        fp16 = sum(2 * self.num_heads * int(s) * self.head_dim * 2 for s in self.seq_lens) * self._batch
+        used = self.memory_bytes()
+        return fp16 / used if used else 0.0

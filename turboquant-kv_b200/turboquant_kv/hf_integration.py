@@ -1,0 +1,241 @@
+"""HuggingFace Transformers integration -- ``TurboQuantCache``, B200 build.
+
+Same constructor and ``DynamicCache`` surface as upstream ``turboquant_kv/hf_integration.py:267-555``
+(``update``, ``get_seq_length``, ``get_max_length``, ``get_usable_length``, ``reorder_cache``,
+``from_config``, ``seen_tokens``, ``memory_bytes``, ``__len__/__getitem__/__iter__``).
+
+``update`` keeps upstream's contract -- it returns dense tensors: every OLD token dequantised, the NEW
+tokens exact (hf_integration.py:383-390) -- but all sequences of a batch share one packed store
+(batch, heads, capacity, packed_dim) that the fused kernels write and read; the per-head, per-batch
+Python loops of upstream are gone.  ``decode_attention`` is the fast path that skips the dense
+round trip altogether for one-token steps.
+"""
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from . import _native as N
+from .config import TurboQuantConfig
+from .reference import lloyd_max_codebook, make_rotation_matrix
+
+_TRANSFORMERS_AVAILABLE = False
+_DynamicCache: type = object
+try:
+    from transformers import DynamicCache as _HFDynamicCache
+
+    _DynamicCache = _HFDynamicCache  # type: ignore[misc]
+    _TRANSFORMERS_AVAILABLE = True
+except ImportError:  # pragma: no cover
+    pass
+
+
+class _LayerQuantStore:
+    """Packed keys and values of one layer for a whole batch; capacity doubles as tokens arrive."""
+
+    def __init__(self, tq_config: TurboQuantConfig, batch: int, num_heads: int, head_dim: int, device):
+        if tq_config.mode != "mse":
+            raise RuntimeError("TurboQuantCache (B200 build) implements mode='mse'")
+        self.tq_config, self.batch, self.num_heads, self.head_dim = tq_config, batch, num_heads, head_dim
+        self.device = torch.device(device)
+        self.seq_len = 0
+        self.capacity = 0
+        cfg = tq_config
+        self._key_rotation = make_rotation_matrix(head_dim, seed=cfg.seed, method=cfg.rotation).to(device)
+        self._val_rotation = make_rotation_matrix(head_dim, seed=cfg.seed + 1, method=cfg.rotation).to(device)
+        self._key_codebook = tuple(t.to(device) for t in lloyd_max_codebook(cfg.key_bits, head_dim))
+        self._val_codebook = tuple(t.to(device) for t in lloyd_max_codebook(cfg.value_bits, head_dim))
+        bpp = (head_dim + 7) // 8
+        self._pk, self._pv = cfg.key_bits * bpp, cfg.value_bits * bpp
+        self._kp = self._kn = self._vp = self._vn = None
+        self._len_dev = torch.zeros(batch, dtype=torch.int32, device=device)
+        self._workspace: Optional[torch.Tensor] = None
+
+    def _reserve(self, need: int) -> None:
+        if need <= self.capacity:
+            return
+        cap = max(256, self.capacity)
+        while cap < need:
+            cap *= 2
+        B, H, dev = self.batch, self.num_heads, self.device
+
+        def grown(old, shape, dtype):
+            new = torch.zeros(shape, dtype=dtype, device=dev)
+            if old is not None and self.seq_len:
+                new[:, :, : self.seq_len] = old[:, :, : self.seq_len]
+            return new
+
+        self._kp = grown(self._kp, (B, H, cap, self._pk), torch.uint8)
+        self._vp = grown(self._vp, (B, H, cap, self._pv), torch.uint8)
+        self._kn = grown(self._kn, (B, H, cap), torch.float32)
+        self._vn = grown(self._vn, (B, H, cap), torch.float32)
+        self.capacity = cap
+
+    def append(self, key: torch.Tensor, value: torch.Tensor) -> None:
+        """key / value: (batch, heads, new, head_dim)."""
+        B, H, T, D = key.shape
+        self._reserve(self.seq_len + T)
+        k = key.contiguous() if key.dtype in (torch.float32, torch.float16, torch.bfloat16) else key.float().contiguous()
+        v = value.to(k.dtype).contiguous()
+        cfg = self.tq_config
+        rm = N.RowMap(T, self.capacity, 1, self.seq_len, None, 1, None, 1)
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_kv_append(
+                N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), B * H * T, D, D,
+                N.ptr(self._key_rotation), N.ptr(self._key_codebook[0]), cfg.key_bits,
+                N.ptr(self._val_rotation), N.ptr(self._val_codebook[0]), cfg.value_bits,
+                N.ptr(self._kp), N.ptr(self._kn), N.ptr(self._vp), N.ptr(self._vn), rm, N.stream_of(k)))
+        self.seq_len += T
+        self._len_dev += T
+
+    def _dense(self, packed, norms, bits, rotation, centroids, dtype) -> torch.Tensor:
+        B, H, S, D = self.batch, self.num_heads, self.seq_len, self.head_dim
+        if S == 0:
+            return torch.zeros(B, H, 0, D, dtype=dtype, device=self.device)
+        p = packed[:, :, :S].contiguous().view(B * H * S, -1)
+        n = norms[:, :, :S].contiguous().view(-1)
+        out = torch.empty(B * H * S, D, dtype=dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_dequantize_mse(N.ptr(p), N.ptr(n), B * H * S, D, N.ptr(rotation), N.ptr(centroids),
+                                               bits, N.ptr(out), N.dtype_code(dtype), N.stream_of(p)))
+        return out.view(B, H, S, D)
+
+    def get_keys(self, dtype=torch.float32) -> torch.Tensor:
+        return self._dense(self._kp, self._kn, self.tq_config.key_bits, self._key_rotation, self._key_codebook[1], dtype)
+
+    def get_values(self, dtype=torch.float32) -> torch.Tensor:
+        return self._dense(self._vp, self._vn, self.tq_config.value_bits, self._val_rotation, self._val_codebook[1], dtype)
+
+    def decode_attention(self, query: torch.Tensor, scale: Optional[float]) -> torch.Tensor:
+        q = query.contiguous()
+        B, HQ, D = q.shape
+        need = N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self.capacity)
+        need = max(need, N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self.seq_len))
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        out = torch.empty_like(q)
+        cfg = self.tq_config
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_decode_attention(
+                N.ptr(q), N.dtype_code(q.dtype), B, HQ, self.num_heads, D, N.ptr(self._kp), N.ptr(self._kn),
+                N.ptr(self._vp), N.ptr(self._vn), self.capacity, N.ptr(self._len_dev), self.seq_len, None, 0, 0,
+                N.ptr(self._key_rotation), N.ptr(self._key_codebook[1]), cfg.key_bits, N.ptr(self._val_rotation),
+                N.ptr(self._val_codebook[1]), cfg.value_bits, float(scale if scale is not None else 1.0 / math.sqrt(D)),
+                N.ptr(self._workspace), self._workspace.numel(), N.ptr(out), N.dtype_code(out.dtype), N.stream_of(q)))
+        return out
+
+    def packed_bytes(self) -> int:
+        per_token = self._pk + self._pv + 8
+        return self.batch * self.num_heads * self.seq_len * per_token
+
+
+class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
+    """``DynamicCache`` whose layers hold TurboQuant codes instead of fp16 tensors."""
+
+    def __init__(self, key_bits: int = 4, value_bits: int = 2, mode: str = "mse", rotation: str = "dense_qr",
+                 protected_layers: int = 0, seed: int = 42, **kwargs: Any) -> None:
+        if _TRANSFORMERS_AVAILABLE:
+            super().__init__(**kwargs)
+        self.tq_config = TurboQuantConfig(key_bits=key_bits, value_bits=value_bits, mode=mode, rotation=rotation,
+                                          protected_layers=protected_layers, quantize_on_append=True, seed=seed)
+        self._protected_layers = protected_layers
+        self._layer_stores: Dict[int, _LayerQuantStore] = {}
+        self._fp_key_cache: Dict[int, List[torch.Tensor]] = {}
+        self._fp_value_cache: Dict[int, List[torch.Tensor]] = {}
+
+    def _store(self, layer_idx: int, like: torch.Tensor) -> _LayerQuantStore:
+        st = self._layer_stores.get(layer_idx)
+        if st is None:
+            if not like.is_cuda:
+                raise RuntimeError("TurboQuantCache (B200 build) needs CUDA key/value states; there is no CPU path")
+            B, H, _, D = like.shape
+            st = _LayerQuantStore(self.tq_config, B, H, D, like.device)
+            self._layer_stores[layer_idx] = st
+        return st
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs: Optional[Dict[str, Any]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Quantise and store the new tokens; return (all_keys, all_values), each
+        (batch, kv_heads, total, head_dim): old tokens dequantised, new tokens exact."""
+        if layer_idx < self._protected_layers:
+            self._fp_key_cache.setdefault(layer_idx, []).append(key_states)
+            self._fp_value_cache.setdefault(layer_idx, []).append(value_states)
+            return torch.cat(self._fp_key_cache[layer_idx], dim=2), torch.cat(self._fp_value_cache[layer_idx], dim=2)
+        st = self._store(layer_idx, key_states)
+        dt = key_states.dtype if key_states.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        k_old, v_old = st.get_keys(dt), st.get_values(dt)
+        st.append(key_states, value_states)
+        return (torch.cat([k_old.to(key_states.dtype), key_states], dim=2),
+                torch.cat([v_old.to(value_states.dtype), value_states], dim=2))
+
+    def append_only(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int) -> None:
+        """Store new tokens without building the dense history (pair with ``decode_attention``)."""
+        self._store(layer_idx, key_states).append(key_states, value_states)
+
+    def decode_attention(self, query: torch.Tensor, layer_idx: int, scale: Optional[float] = None) -> torch.Tensor:
+        """Fused attention of one new query token per sequence over the packed layer.
+
+        query: (batch, q_heads, head_dim) or (batch, q_heads, 1, head_dim)."""
+        st = self._layer_stores[layer_idx]
+        squeeze = query.dim() == 4
+        out = st.decode_attention(query[:, :, 0] if squeeze else query, scale)
+        return out.unsqueeze(2) if squeeze else out
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        if layer_idx < self._protected_layers:
+            return sum(c.shape[2] for c in self._fp_key_cache.get(layer_idx, []))
+        st = self._layer_stores.get(layer_idx)
+        return 0 if st is None else st.seq_len
+
+    def get_max_length(self) -> Optional[int]:
+        return None
+
+    def get_usable_length(self, new_seq_length: int, layer_idx: int = 0) -> int:
+        return self.get_seq_length(layer_idx)
+
+    def reorder_cache(self, beam_idx: torch.LongTensor) -> None:
+        """Beam reordering: exact for protected layers; packed rows of quantised layers are gathered."""
+        for li in list(self._fp_key_cache.keys()):
+            self._fp_key_cache[li] = [c.index_select(0, beam_idx.to(c.device)) for c in self._fp_key_cache[li]]
+            self._fp_value_cache[li] = [c.index_select(0, beam_idx.to(c.device)) for c in self._fp_value_cache[li]]
+        if self._layer_stores:
+            warnings.warn("TurboQuantCache.reorder_cache: beam search reordering is not fully supported for "
+                          "quantised layers. Results may be incorrect. Use greedy or sampling decoding instead.",
+                          stacklevel=2)
+
+    @classmethod
+    def from_config(cls, key_bits: int = 4, value_bits: int = 2, mode: str = "mse", rotation: str = "dense_qr",
+                    protected_layers: int = 0, seed: int = 42) -> "TurboQuantCache":
+        return cls(key_bits=key_bits, value_bits=value_bits, mode=mode, rotation=rotation,
+                   protected_layers=protected_layers, seed=seed)
+
+    @property
+    def seen_tokens(self) -> int:
+        lengths = [self.get_seq_length(i) for i in range(max(len(self._layer_stores), 1))]
+        lengths.extend(self.get_seq_length(i) for i in self._fp_key_cache)
+        return max(lengths) if lengths else 0
+
+    def memory_bytes(self) -> int:
+        """Bytes of packed codes and norms (protected fp16 layers not counted, as upstream)."""
+        return sum(st.packed_bytes() for st in self._layer_stores.values())
+
+    def __len__(self) -> int:
+        return len(self._layer_stores) + len(self._fp_key_cache)
+
+    def __getitem__(self, layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if layer_idx < self._protected_layers and layer_idx in self._fp_key_cache:
+            return torch.cat(self._fp_key_cache[layer_idx], dim=2), torch.cat(self._fp_value_cache[layer_idx], dim=2)
+        st = self._layer_stores.get(layer_idx)
+        if st is None:
+            raise IndexError(f"No cached data for layer {layer_idx}")
+        return st.get_keys(), st.get_values()
+
+    def __iter__(self):
+        for idx in sorted(set(self._layer_stores) | set(self._fp_key_cache)):
+            yield self[idx]
+
+
+__all__ = ["TurboQuantCache"]

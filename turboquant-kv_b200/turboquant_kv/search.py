@@ -1,0 +1,238 @@
+"""TurboQuantIndex -- brute-force inner-product search over TurboQuant-compressed vectors, B200 build.
+
+Same surface as upstream ``turboquant_kv/search.py:37-317`` (constructor, ``from_vectors``, ``add``,
+``search``, ``save``, ``load``).  The database lives in GPU memory in the upstream packed layout;
+``add`` runs the fused quantise kernel, ``search`` (MSE mode) runs the streaming packed-code scan with
+top-k selection (csrc/scan.cu), which replaces both the Python path (unpack everything, gather an
+(N, d) float matrix, one (Q, N) matmul, torch.topk; search.py:206-227) and the optional C++ core
+(csrc/core/turboquant_core.cpp:407-514).
+
+Tensors may be passed on the host or on the GPU; results come back on the device of the queries.
+Results: scores descending, ids int64; equal scores are ordered by ascending id; ``k`` is clipped
+to the number of stored vectors like the upstream Python path.
+
+Prod mode keeps upstream's formulation (reconstruct, then q . x): rows are reconstructed chunk by
+chunk with the dequantize_prod kernel and scored with a dense matmul.
+"""
+from __future__ import annotations
+
+import struct
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+from .reference import (_make_qjl_matrix, dequantize_prod, lloyd_max_codebook, make_rotation_matrix,
+                        quantize_mse, quantize_prod)
+
+HEADER_FORMAT = "<BII"  # bit_width (u8), dim (u32), n_vectors (u32) -- upstream search.py:29
+HEADER_SIZE = struct.calcsize(HEADER_FORMAT)
+MODE_MSE, MODE_PROD = 0, 1
+TQIX_MAGIC, TQIX_VERSION = 0x54514958, 1  # upstream csrc/core/turboquant_core.cpp:520-521
+
+_QUERY_CHUNK = 512      # queries per scan call (bounds the candidate workspace)
+_PROD_ROW_CHUNK = 1 << 18
+
+
+def merge_topk(scores: torch.Tensor, ids: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merge per-shard results.  scores / ids: (Q, parts, k); entries with id -1 are padding.
+
+    Ordering rule of the scan: score descending, then id ascending.  CUDA tensors go through the
+    merge kernel; host tensors (used by the multi-process logic on CPU ranks) through a stable sort.
+    """
+    q, parts, kk = scores.shape
+    if scores.is_cuda and kk == k:
+        s = scores.contiguous().float()
+        i = ids.contiguous().to(torch.int64)
+        out_s = torch.empty(q, k, dtype=torch.float32, device=s.device)
+        out_i = torch.empty(q, k, dtype=torch.int64, device=s.device)
+        with torch.cuda.device(s.device):
+            N.check(N.lib().tqb_topk_merge(N.ptr(s), N.ptr(i), q, parts, k, N.ptr(out_s), N.ptr(out_i),
+                                           N.stream_of(s)))
+        return out_s, out_i
+    s = scores.reshape(q, parts * kk).float()
+    i = ids.reshape(q, parts * kk).to(torch.int64)
+    s = torch.where(i < 0, torch.full_like(s, float("-inf")), s)
+    big = torch.where(i < 0, torch.full_like(i, torch.iinfo(torch.int64).max), i)
+    order = torch.argsort(big, dim=1, stable=True)                      # id ascending ...
+    s1, i1 = torch.gather(s, 1, order), torch.gather(i, 1, order)
+    order = torch.argsort(s1, dim=1, descending=True, stable=True)      # ... then score descending
+    s2, i2 = torch.gather(s1, 1, order)[:, :k], torch.gather(i1, 1, order)[:, :k]
+    if s2.shape[1] < k:
+        pad = k - s2.shape[1]
+        s2 = torch.cat([s2, s2.new_full((q, pad), float("-inf"))], 1)
+        i2 = torch.cat([i2, i2.new_full((q, pad), -1)], 1)
+    return s2, i2
+
+
+class TurboQuantIndex:
+    """Compressed vector index; ``mode`` "mse" (Algorithm 1) or "prod" (Algorithm 2)."""
+
+    def __init__(self, dim: int, bit_width: int = 3, mode: str = "mse", rotation: str = "dense_qr",
+                 seed: int = 42, device=None):
+        if mode not in ("mse", "prod"):
+            raise ValueError(f"Unknown mode: {mode}")
+        N.require_cuda()
+        self.dim, self.bit_width, self.mode = dim, bit_width, mode
+        self.rotation_method, self.seed = rotation, seed
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._use_cpp = False  # upstream attribute: no host C++ core in this build
+        self._rotation = make_rotation_matrix(dim, seed=seed, method=rotation).to(self.device)
+        mse_bits = bit_width if mode == "mse" else bit_width - 1
+        if mode == "prod" and mse_bits < 1:
+            raise ValueError(f"Prod mode requires bits >= 2, got {bit_width}")
+        self._codebook = tuple(t.to(self.device) for t in lloyd_max_codebook(mse_bits, dim))
+        self._S_matrix = _make_qjl_matrix(dim, dim, seed, self.device) if mode == "prod" else None
+        self._packed_codes: Optional[torch.Tensor] = None
+        self._norms: Optional[torch.Tensor] = None
+        self._qjl_signs: Optional[torch.Tensor] = None
+        self._residual_norms: Optional[torch.Tensor] = None
+        self.n_vectors = 0
+        self.id_offset = 0           # added to every returned id (row-sharded indexes)
+        self._workspace: Optional[torch.Tensor] = None
+
+    @classmethod
+    def from_vectors(cls, vectors: torch.Tensor, bit_width: int = 3, mode: str = "mse",
+                     rotation: str = "dense_qr", seed: int = 42, device=None) -> "TurboQuantIndex":
+        idx = cls(dim=vectors.shape[-1], bit_width=bit_width, mode=mode, rotation=rotation, seed=seed, device=device)
+        idx.add(vectors)
+        return idx
+
+    # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def _grow(old: Optional[torch.Tensor], new: torch.Tensor) -> torch.Tensor:
+        return new if old is None else torch.cat([old, new], dim=0)
+
+    def add(self, vectors: torch.Tensor):
+        """Quantise and append (N, dim) or (dim,) vectors."""
+        if vectors.dim() == 1:
+            vectors = vectors.unsqueeze(0)
+        assert vectors.shape[-1] == self.dim
+        x = vectors.to(self.device)
+        if self.mode == "mse":
+            packed, norms = quantize_mse(x, self.bit_width, dim=self.dim, rotation=self._rotation,
+                                         codebook=self._codebook)
+        else:
+            packed, signs, res, norms = quantize_prod(x, self.bit_width, dim=self.dim, rotation=self._rotation,
+                                                      codebook=self._codebook, S_matrix=self._S_matrix)
+            self._qjl_signs = self._grow(self._qjl_signs, signs)
+            self._residual_norms = self._grow(self._residual_norms, res)
+        self._packed_codes = self._grow(self._packed_codes, packed)
+        self._norms = self._grow(self._norms, norms)
+        self.n_vectors += x.shape[0]
+
+    # ------------------------------------------------------------------------------------------
+    def search(self, queries: torch.Tensor, k: int = 10) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Top-k inner products: (scores (Q, k) float32, ids (Q, k) int64)."""
+        if queries.dim() == 1:
+            queries = queries.unsqueeze(0)
+        assert self.n_vectors > 0, "Index is empty"
+        home = queries.device
+        q = queries.to(self.device, torch.float32).contiguous()
+        k = min(k, self.n_vectors)
+        scores, ids = (self._search_mse if self.mode == "mse" else self._search_prod)(q, k)
+        return scores.to(home), ids.to(home)
+
+    def _search_mse(self, q: torch.Tensor, k: int):
+        if k > N.SCAN_MAX_K:
+            raise RuntimeError(f"k = {k} exceeds the scan's limit of {N.SCAN_MAX_K}")
+        nq = q.shape[0]
+        out_s = torch.empty(nq, k, dtype=torch.float32, device=self.device)
+        out_i = torch.empty(nq, k, dtype=torch.int64, device=self.device)
+        L = N.lib()
+        with torch.cuda.device(self.device):
+            for lo in range(0, nq, _QUERY_CHUNK):
+                qc = q[lo:lo + _QUERY_CHUNK]
+                n = qc.shape[0]
+                need = L.tqb_scan_topk_workspace_bytes(n, self.n_vectors, self.dim, self.bit_width, k)
+                if self._workspace is None or self._workspace.numel() < need:
+                    self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+                N.check(L.tqb_scan_topk(N.ptr(qc), n, N.ptr(self._packed_codes), N.ptr(self._norms),
+                                        self.n_vectors, self.dim, self.bit_width, N.ptr(self._rotation),
+                                        N.ptr(self._codebook[1]), k, self.id_offset, N.ptr(self._workspace),
+                                        self._workspace.numel(), N.ptr(out_s[lo:lo + n]), N.ptr(out_i[lo:lo + n]),
+                                        N.stream_of(qc)))
+        return out_s, out_i
+
+    def _search_prod(self, q: torch.Tensor, k: int):
+        best_s = best_i = None
+        for lo in range(0, self.n_vectors, _PROD_ROW_CHUNK):
+            hi = min(self.n_vectors, lo + _PROD_ROW_CHUNK)
+            recon = dequantize_prod(self._packed_codes[lo:hi], self._qjl_signs[lo:hi], self._residual_norms[lo:hi],
+                                    self._norms[lo:hi], self.bit_width, self.dim, rotation=self._rotation,
+                                    codebook=self._codebook, S_matrix=self._S_matrix)
+            sc = q @ recon.t()
+            kk = min(k, hi - lo)
+            s, i = torch.topk(sc, kk, dim=-1)
+            i = i + lo + self.id_offset
+            if kk < k:
+                s = torch.cat([s, s.new_full((s.shape[0], k - kk), float("-inf"))], 1)
+                i = torch.cat([i, i.new_full((i.shape[0], k - kk), -1)], 1)
+            if best_s is None:
+                best_s, best_i = s, i
+            else:
+                best_s, best_i = merge_topk(torch.stack([best_s, s], 1), torch.stack([best_i, i], 1), k)
+        return best_s, best_i
+
+    # ------------------------------------------------------------------------------------------
+    def save(self, path: str, format: str = "python"):
+        """Write the index.  "python": upstream search.py:254-277 (header <BII, mode byte, codes, norms
+        [, signs, residual norms]).  "tqix": upstream C++ core layout, MSE only
+        (csrc/core/turboquant_core.cpp:559-580: magic, version, dim, bits, seed, n as u32, codes, norms)."""
+        codes = self._packed_codes.cpu().numpy().tobytes() if self.n_vectors else b""
+        norms = self._norms.cpu().numpy().tobytes() if self.n_vectors else b""
+        with open(path, "wb") as f:
+            if format == "tqix":
+                if self.mode != "mse":
+                    raise ValueError("the TQIX layout stores MSE indexes only")
+                f.write(struct.pack("<6I", TQIX_MAGIC, TQIX_VERSION, self.dim, self.bit_width,
+                                    self.seed & 0xFFFFFFFF, self.n_vectors))
+                f.write(codes)
+                f.write(norms)
+                return
+            if format != "python":
+                raise ValueError(f"Unknown format: {format}")
+            f.write(struct.pack(HEADER_FORMAT, self.bit_width, self.dim, self.n_vectors))
+            f.write(struct.pack("<B", MODE_MSE if self.mode == "mse" else MODE_PROD))
+            f.write(codes)
+            f.write(norms)
+            if self.mode == "prod" and self.n_vectors:
+                f.write(self._qjl_signs.cpu().numpy().tobytes())
+                f.write(self._residual_norms.cpu().numpy().tobytes())
+
+    @classmethod
+    def load(cls, path: str, rotation: str = "dense_qr", seed: int = 42, device=None) -> "TurboQuantIndex":
+        """Read either on-disk layout (recognised by the TQIX magic)."""
+        import numpy as np
+
+        with open(path, "rb") as f:
+            blob = f.read()
+        if len(blob) >= 24 and struct.unpack_from("<I", blob, 0)[0] == TQIX_MAGIC:
+            _, version, dim, bits, file_seed, n = struct.unpack_from("<6I", blob, 0)
+            if version != TQIX_VERSION:
+                raise RuntimeError("Unsupported TQIDX version")
+            mode, off, seed = "mse", 24, file_seed
+        else:
+            bits, dim, n = struct.unpack_from(HEADER_FORMAT, blob, 0)
+            mode = "mse" if blob[HEADER_SIZE] == MODE_MSE else "prod"
+            off = HEADER_SIZE + 1
+        bpp = (dim + 7) // 8
+        pbytes = (bits if mode == "mse" else bits - 1) * bpp
+
+        def take(count, dtype, width):
+            nonlocal off
+            nbytes = count * width
+            if off + nbytes > len(blob):
+                raise RuntimeError(f"Read error / truncated file: {path}")
+            arr = np.frombuffer(blob, dtype=dtype, count=nbytes // np.dtype(dtype).itemsize, offset=off).copy()
+            off += nbytes
+            return torch.from_numpy(arr)
+
+        idx = cls(dim=dim, bit_width=bits, mode=mode, rotation=rotation, seed=seed, device=device)
+        idx._packed_codes = take(n, np.uint8, pbytes).reshape(n, pbytes).to(idx.device)
+        idx._norms = take(n, np.float32, 4).to(idx.device)
+        if mode == "prod":
+            idx._qjl_signs = take(n, np.uint8, bpp).reshape(n, bpp).to(idx.device)
+            idx._residual_norms = take(n, np.float32, 4).to(idx.device)
+        idx.n_vectors = n
+        return idx
