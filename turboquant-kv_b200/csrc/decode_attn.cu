@@ -30,7 +30,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_INF = -__builtin_huge_valf();
 constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score exceeds m + 4 (log2)
 constexpr int TILE = 16;                // tokens per MMA tile
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -282,6 +282,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
             }
             const uint32_t dst = smem_u32(ring + (size_t)s * C::STAGE);
             const uint32_t bar = bar0 + 8 * s;
+            // order this warp's earlier generic-proxy reads of the stage before the async-proxy overwrite
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(bar, C::STAGE);
             bulk_g2s(dst, p.k_packed + row * C::PK, C::KT, bar);
             bulk_g2s(dst + C::KT, p.v_packed + row * C::PV, C::VT, bar);

@@ -32,7 +32,7 @@ constexpr int SCAN_WARPS = 8;
 constexpr int QG = 4;                   // queries per tensor-core pass
 constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
 constexpr float QUERY_SCALE = 16.0f;
-constexpr uint32_t SCAN_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t SCAN_WAIT_LIMIT = 1u << 20;
 constexpr int ID_NONE = 0x7fffffff;
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -247,6 +247,8 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
             const int64_t row = tile * SCAN_TILE;
             const uint32_t dst = s_u32(ring + (size_t)s * C::STAGE);
             const uint32_t bar = bar0 + 8 * s;
+            // order this warp's earlier generic-proxy reads of the stage before the async-proxy overwrite
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             s_mbar_expect_tx(bar, C::STAGE);
             s_bulk_g2s(dst, p.packed + row * C::PD, C::RT, bar);
             s_bulk_g2s(dst + C::RT, p.norms + row, SCAN_TILE * 4, bar);
