@@ -372,12 +372,7 @@ def parity_check(torch, data, device) -> dict:
     s, h, ctx = data["kn"].shape
     cache = QuantizedKVCache(TurboQuantConfig(key_bits=KEY_BITS, value_bits=VALUE_BITS, seed=42), 1, ctx, h, HEAD_DIM,
                              device=str(device), batch_size=s)
-    cache._kp[0][:, :, :ctx].copy_(torch.from_numpy(data["kp"]))
-    cache._vp[0][:, :, :ctx].copy_(torch.from_numpy(data["vp"]))
-    cache._kn[0][:, :, :ctx].copy_(torch.from_numpy(data["kn"]))
-    cache._vn[0][:, :, :ctx].copy_(torch.from_numpy(data["vn"]))
-    cache.seq_lens[0] = ctx
-    cache._seq_lens_dev[0] = ctx
+    cache.load_packed(0, *(torch.from_numpy(data[k]) for k in ("kp", "kn", "vp", "vn")))
     got = cache.decode_attention(0, torch.from_numpy(data["q"]).to(device)).float().cpu().numpy()
     ref = data["out"]
     cos = float((got * ref).sum() / np.sqrt((got * got).sum() * (ref * ref).sum()))
@@ -513,8 +508,78 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     return res
 
 
+def run_case(args) -> None:
+    """Single-kernel cases for profilers: a few eager launches of one hot kernel, timed with CUDA events.
+
+    decode    one layer-call = decode_attention over `--layers` layers of the decode workload
+    scan      single-query passes of the 4-bit index scan over `--scan-rows` rows
+    quantize  quantize_mse of `--rows` float32 vectors of dim 128 at 4 bits
+    """
+    import torch
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks = measured_peaks()
+    K, W = args.steps, args.warmup
+    out = {"case": args.case}
+
+    def timed(fn):
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize()
+        ev = []
+        for _ in range(K):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            ev.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+
+    if args.case == "decode":
+        global LAYERS
+        LAYERS = args.layers
+        cache = build_cache(torch, args.ctx, KV_HEADS, device, 8)
+        q = torch.randn(BATCH, Q_HEADS, HEAD_DIM, device=device).bfloat16()
+        o = torch.empty_like(q)
+        ms = timed(lambda: [cache.decode_attention(l, q, out=o) for l in range(LAYERS)]) / LAYERS
+        nbytes = BATCH * KV_HEADS * args.ctx * BYTES_PER_TOKEN_HEAD
+        out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                   status=cache.decode_status())
+    elif args.case == "scan":
+        from turboquant_kv import TurboQuantIndex
+
+        idx = TurboQuantIndex(dim=128, bit_width=4, seed=42, device=device)
+        gam = torch.distributions.Gamma(torch.tensor(0.5, device=device), torch.tensor(1.0 / 40.0, device=device))
+        for c0 in range(0, args.scan_rows, 1_000_000):
+            idx.add(gam.sample((min(1_000_000, args.scan_rows - c0), 128)).clamp_(0, 255).round_())
+        qs = gam.sample((max(args.queries_per_call, 1), 128)).clamp_(0, 255).round_()
+        ms = timed(lambda: idx.search(qs, 10))
+        nbytes = args.scan_rows * 68 * math.ceil(qs.shape[0] / 4)
+        out.update(ms_per_call=ms, queries=qs.shape[0], bytes=nbytes, gbs=nbytes / ms / 1e6,
+                   frac=nbytes / ms / 1e6 / peaks["hbm_gbs"])
+    elif args.case == "quantize":
+        from turboquant_kv import quantize_mse
+        from turboquant_kv.reference import lloyd_max_codebook, make_rotation_matrix
+
+        x = torch.randn(args.rows, 128, device=device)
+        rot = make_rotation_matrix(128, 42).to(device)
+        cb = tuple(t.to(device) for t in lloyd_max_codebook(4, 128))
+        ms = timed(lambda: quantize_mse(x, 4, rotation=rot, codebook=cb))
+        nbytes = args.rows * (512 + 68)
+        out.update(ms_per_call=ms, rows=args.rows, vectors_per_s=args.rows / ms * 1e3, gbs=nbytes / ms / 1e6,
+                   tflops=2 * 128 * 128 * args.rows / ms / 1e9)
+    print(json.dumps(out), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, choices=["decode", "scan", "quantize"],
+                    help="run one single-kernel case (for profilers) instead of the benchmark")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="--case decode: layers to build")
+    ap.add_argument("--rows", type=int, default=65536, help="--case quantize: vectors")
+    ap.add_argument("--queries-per-call", type=int, default=1, help="--case scan: queries per search call")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -531,6 +596,9 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.case:
+        run_case(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

@@ -124,15 +124,39 @@ int tqb_attention_values_packed(const float* weights, int64_t bh, int64_t seq, i
                                 const float* centroids, const float* rotation_T, int bits,
                                 float* out, void* stream);
 
+/* ---- packed KV cache: storage layout ----------------------------------------------------------
+ * The cache is NOT stored in the upstream bit-plane layout: decode attention is bound by instruction
+ * issue, and turning bit planes into tensor-core operands costs more instructions than everything
+ * else in the kernel.  Tokens are stored in RECORDS of 16 tokens of one (sequence, KV head), laid out
+ * in the order the consuming mma.sync lanes read them (csrc/tiled_layout.cuh documents every bit):
+ *     [32 lanes x dim*kbits/16 bytes of key codes][32 lanes x dim*vbits/16 bytes of value codes]
+ *     [16 key norms f32][16 value norms f32]            = 2*dim*(kbits+vbits) + 128 bytes,
+ * the same codes and the same bytes per token as upstream.  A token SLOT is a flat index
+ * slot = unit * pitch + position (pitch a multiple of 16); its record is slot / 16.  Contiguous cache:
+ * unit = sequence * kv_heads + head, pitch = padded max_seq.  Paged cache: unit = block * kv_heads +
+ * head, pitch = block_size.  tqb_kv_export / tqb_kv_import convert slots to and from upstream rows. */
+int64_t tqb_kv_record_bytes(int dim, int kbits, int vbits);
+
 /* ---- KV-cache append ---------------------------------------------------------------------
  * Replaces the per-head quantize loop of QuantizedKVCache.append (turboquant_kv/cache.py:148-214)
  * and of _LayerQuantStore.append (turboquant_kv/hf_integration.py:111-182): quantises n key rows
  * and n value rows (each (n, dim), x_stride apart) in ONE launch, keys with (rot_k, bnd_k, kbits),
- * values with (rot_v, bnd_v, vbits), and scatters them through `map` into the cache arrays. */
+ * values with (rot_v, bnd_v, vbits), and writes input row r to token slot map(r) of `store`
+ * (tqb_rowmap gives the slot; dense rows when map is NULL).  dim in {64, 128}, bits in 2..4. */
 int tqb_kv_append(const void* key, const void* value, int dtype, int64_t n, int dim, int64_t x_stride,
                   const float* rot_k, const float* bnd_k, int kbits, const float* rot_v,
-                  const float* bnd_v, int vbits, uint8_t* k_packed, float* k_norms,
-                  uint8_t* v_packed, float* v_norms, const tqb_rowmap* map, void* stream);
+                  const float* bnd_v, int vbits, uint8_t* store, const tqb_rowmap* map, void* stream);
+
+/* Upstream-layout view of n token slots: row r of the outputs is slot map(r).  k_packed (n, kbits*dim/8),
+ * k_norms (n), v_packed (n, vbits*dim/8), v_norms (n); any output may be NULL.  This is what backs the
+ * upstream attributes QuantizedKVCache._key_packed / _key_norms / ... (cache.py:89-106). */
+int tqb_kv_export(const uint8_t* store, int64_t n, int dim, int kbits, int vbits, const tqb_rowmap* map,
+                  uint8_t* k_packed, float* k_norms, uint8_t* v_packed, float* v_norms, void* stream);
+
+/* Inverse of tqb_kv_export: writes upstream-layout rows into token slots (inputs may be NULL). */
+int tqb_kv_import(uint8_t* store, int64_t n, int dim, int kbits, int vbits, const tqb_rowmap* map,
+                  const uint8_t* k_packed, const float* k_norms, const uint8_t* v_packed,
+                  const float* v_norms, void* stream);
 
 /* ---- fused decode attention over a packed KV cache ------------------------------------------
  * Replaces QuantizedKVCache.attention_scores -> softmax -> attention_values
@@ -144,20 +168,18 @@ int tqb_kv_append(const void* key, const void* value, int dtype, int64_t n, int 
  * h / group.  out (batch, q_heads, dim) of out_dtype.  softmax(scale * q.k) over the first
  * seq_lens[b] tokens (device int32[batch]); max_len (host) >= every seq_lens[b].
  *
- * Contiguous cache (block_tables == NULL): k_packed (batch, kv_heads, max_seq, pk) uint8,
- * k_norms (batch, kv_heads, max_seq) float32, same for v; `max_seq` is the row pitch.
- * Paged cache (block_tables != NULL): k_packed (num_blocks, kv_heads, block_size, pk), norms
- * (num_blocks, kv_heads, block_size); block_tables (batch, max_blocks) int32 device;
- * block_size a multiple of 16.
+ * store: the record store described above.  Contiguous cache (block_tables == NULL): unit =
+ * b * kv_heads + head, `max_seq` = token pitch of a unit (multiple of 16).  Paged cache: block_tables
+ * (batch, max_blocks) int32 device, block_size a multiple of 16.
  *
  * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  workspace: device scratch of at least
  * tqb_decode_attention_workspace_bytes(...) bytes, 256-byte aligned, not shared between calls that
- * may overlap on the device. */
+ * may overlap on the device.  Its first 4 bytes are a status word the kernels set to non-zero when a
+ * bounded device-side wait expired (results are then invalid). */
 size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, int kv_heads, int dim,
                                             int64_t max_len);
 int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
-                         int dim, const uint8_t* k_packed, const float* k_norms,
-                         const uint8_t* v_packed, const float* v_norms, int64_t max_seq,
+                         int dim, const uint8_t* store, int64_t max_seq,
                          const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
                          int max_blocks, int block_size, const float* rot_k, const float* cent_k,
                          int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,

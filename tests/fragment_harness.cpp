@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "decode_bits.cuh"
+#include "tiled_layout.cuh"
 
 using namespace tqb;
 
@@ -123,6 +124,104 @@ void value_tile(const uint8_t* tile, const float* cent, const float* pw /*[16 to
     }
 }
 
+
+// ---- tiled (fragment-major) layout: writer = tl_*_slot, reader = what the decode kernel does ----
+void write_bits(uint8_t* p, int bit, int bits, uint32_t v) {
+    for (int i = 0; i < bits; i++) {
+        p[(bit + i) >> 3] &= (uint8_t)~(1u << ((bit + i) & 7));
+        p[(bit + i) >> 3] |= (uint8_t)(((v >> i) & 1u) << ((bit + i) & 7));
+    }
+}
+
+void tiled_build(int D, int KB, int VB, const uint8_t* kcodes /*[16][D]*/, const uint8_t* vcodes, uint8_t* rec) {
+    std::memset(rec, 0, tl_record_bytes(D, KB, VB));
+    uint8_t* ksec = rec;
+    uint8_t* vsec = rec + tl_key_section(D, KB);
+    for (int r = 0; r < 16; r++)
+        for (int d = 0; d < D; d++) {
+            int base, bit;
+            tl_key_slot(D, KB, r, d, base, bit);
+            write_bits(ksec + base, bit, KB, kcodes[r * D + d]);
+            tl_val_slot(D, VB, r, d, base, bit);
+            write_bits(vsec + base, bit, VB, vcodes[r * D + d]);
+        }
+}
+
+template <int NW>
+void load_words(const uint8_t* p, uint32_t (&w)[NW], int nbytes) {
+    for (int i = 0; i < NW; i++) w[i] = 0;
+    std::memcpy(w, p, nbytes);
+}
+
+void tiled_key_tile(int D, int KB, int VB, const uint8_t* rec, const float* cent, const float* q, float* out) {
+    const int KL = tl_key_lane_bytes(D, KB);
+    float C[16][8] = {};
+    for (int ks = 0; ks < D / 16; ks++) {
+        Frag f{};
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            uint32_t kw[8];
+            load_words(rec + lane * KL, kw, KL);
+            for (int half = 0; half < 2; half++) {
+                for (int second = 0; second < 2; second++) {
+                    const uint32_t x = tl_field(kw, tl_key_field_bit(D, KB, ks, half, second), 2 * KB);
+                    int clo, chi;
+                    tl_key_field_codes(x, KB, clo, chi);
+                    f.a[lane][4 * half + 2 * second + 0] = cent[clo];
+                    f.a[lane][4 * half + 2 * second + 1] = cent[chi];
+                }
+                const int d = 16 * ks + 8 * half + 2 * t;   // natural B fragment
+                f.b[lane][2 * half + 0] = q[g * D + d];
+                f.b[lane][2 * half + 1] = q[g * D + d + 1];
+            }
+        }
+        mma_replay(f, C);
+    }
+    std::memcpy(out, C, sizeof(C));
+}
+
+void tiled_value_tile(int D, int KB, int VB, const uint8_t* rec, const float* cent, const float* pw, float* out) {
+    const int VL = tl_val_lane_bytes(D, VB);
+    const uint8_t* vsec = rec + tl_key_section(D, KB);
+    for (int mt = 0; mt < D / 16; mt++) {
+        Frag f{};
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            uint32_t vw[8];
+            load_words(vsec + lane * VL, vw, VL);
+            for (int half = 0; half < 2; half++) {
+                const int ta = 2 * t + 8 * half, tb = ta + 1;
+                if (VB == 2) {
+                    const uint32_t x = tl_field(vw, tl_val_field_bit(VB, mt, half, 0), 8);
+                    int ag, bg, ag8, bg8;
+                    tl_val_quad_codes(x, ag, bg, ag8, bg8);
+                    f.a[lane][4 * half + 0] = cent[ag];  f.a[lane][4 * half + 1] = cent[bg];
+                    f.a[lane][4 * half + 2] = cent[ag8]; f.a[lane][4 * half + 3] = cent[bg8];
+                } else {
+                    for (int s = 0; s < 2; s++) {
+                        const uint32_t x = tl_field(vw, tl_val_field_bit(VB, mt, half, s), 2 * VB);
+                        int ca, cb;
+                        tl_val_pair_codes(x, VB, ca, cb);
+                        f.a[lane][4 * half + 2 * s + 0] = cent[ca];
+                        f.a[lane][4 * half + 2 * s + 1] = cent[cb];
+                    }
+                }
+                f.b[lane][2 * half + 0] = pw[ta * 8 + g];
+                f.b[lane][2 * half + 1] = pw[tb * 8 + g];
+            }
+        }
+        float C[16][8] = {};
+        mma_replay(f, C);
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane >> 2, t = lane & 3;
+            for (int j = 0; j < 2; j++) {
+                out[(16 * mt + g) * 8 + 2 * t + j] = C[g][2 * t + j];
+                out[(16 * mt + g + 8) * 8 + 2 * t + j] = C[g + 8][2 * t + j];
+            }
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -139,6 +238,19 @@ int replay_value_tile(int D, int bits, const uint8_t* tile, const float* cent, c
     CASE(64, 2) CASE(64, 3) CASE(64, 4) CASE(128, 2) CASE(128, 3) CASE(128, 4)
 #undef CASE
     return -1;
+}
+
+
+int tiled_record_bytes(int D, int KB, int VB) { return tl_record_bytes(D, KB, VB); }
+
+// Builds a record from codes with the writer-side slot functions, then replays the reader side.
+int replay_tiled(int D, int KB, int VB, const uint8_t* kcodes, const uint8_t* vcodes, const float* ck,
+                 const float* cv, const float* q, const float* pw, float* scores, float* outv, uint8_t* rec) {
+    if (!(D == 64 || D == 128) || KB < 2 || KB > 4 || VB < 2 || VB > 4) return -1;
+    tiled_build(D, KB, VB, kcodes, vcodes, rec);
+    tiled_key_tile(D, KB, VB, rec, ck, q, scores);
+    tiled_value_tile(D, KB, VB, rec, cv, pw, outv);
+    return 0;
 }
 
 }  // extern "C"

@@ -60,3 +60,30 @@ def test_value_tile_accumulate(harness, orc, dim, bits):
     assert rc == 0
     want = cent[codes].T @ pw
     np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("kb,vb", [(4, 2), (4, 3), (4, 4), (3, 3), (2, 2), (3, 4), (2, 3)])
+def test_tiled_layout_roundtrip(harness, dim, kb, vb):
+    """Fragment-major cache layout: the writer-side slots and the reader-side fields agree."""
+    rng = np.random.default_rng(dim + 10 * kb + vb)
+    kc = rng.integers(0, 1 << kb, size=(16, dim), dtype=np.uint8)
+    vc = rng.integers(0, 1 << vb, size=(16, dim), dtype=np.uint8)
+    ck = np.sort(rng.normal(size=1 << kb)).astype(np.float32)
+    cv = np.sort(rng.normal(size=1 << vb)).astype(np.float32)
+    q = rng.normal(size=(8, dim)).astype(np.float32)
+    pw = rng.random(size=(16, 8)).astype(np.float32)
+    scores = np.zeros((16, 8), np.float32)
+    outv = np.zeros((dim, 8), np.float32)
+    nbytes = harness.tiled_record_bytes(dim, kb, vb)
+    assert nbytes == 2 * dim * (kb + vb) + 128
+    rec = np.zeros(nbytes, np.uint8)
+    rc = harness.replay_tiled(dim, kb, vb, _ptr(kc, ctypes.c_uint8), _ptr(vc, ctypes.c_uint8), _ptr(ck, ctypes.c_float),
+                              _ptr(cv, ctypes.c_float), _ptr(q, ctypes.c_float), _ptr(pw, ctypes.c_float),
+                              _ptr(scores, ctypes.c_float), _ptr(outv, ctypes.c_float), _ptr(rec, ctypes.c_uint8))
+    assert rc == 0
+    np.testing.assert_allclose(scores, ck[kc] @ q.T, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(outv, cv[vc].T @ pw, rtol=1e-4, atol=1e-4)
+    # every code bit is stored exactly once: the code sections are fully used
+    used = 2 * dim * (kb + vb)
+    assert rec[used:].sum() == 0

@@ -20,6 +20,14 @@ def cuda(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+def exported(cache, layer, seq):
+    """Upstream-layout numpy copies (batch, heads, seq, ...) of a QuantizedKVCache layer."""
+    B, H = cache._batch, cache.num_heads
+    kp, kn, vp, vn = cache._export(layer, seq)
+    return (kp.view(B, H, seq, -1).cpu().numpy(), kn.view(B, H, seq).cpu().numpy(),
+            vp.view(B, H, seq, -1).cpu().numpy(), vn.view(B, H, seq).cpu().numpy())
+
+
 @pytest.mark.parametrize("tag,dim,kb,vb", [("k4v2_d64", 64, 4, 2), ("k4v3_d128", 128, 4, 3), ("k2v4_d64", 64, 2, 4)])
 def test_operator_level_scores_and_values(orc, golden, tag, dim, kb, vb):
     from turboquant_kv import ops
@@ -123,16 +131,17 @@ def test_fused_decode_matches_dequantise_then_attend(orc, dim, kb, vb, kv_heads,
     rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
     _, ck = orc.lloyd_max_codebook(kb, dim)
     _, cv = orc.lloyd_max_codebook(vb, dim)
-    ref = orc.decode_attention(q.bfloat16().float().numpy(), cache._kp[1].cpu().numpy(), cache._kn[1].cpu().numpy(),
-                               cache._vp[1].cpu().numpy(), cache._vn[1].cpu().numpy(),
+    kp, kn, vp, vn = exported(cache, 1, ctx)
+    ref = orc.decode_attention(q.bfloat16().float().numpy(), kp, kn, vp, vn,
                                np.full(batch, ctx, np.int32), rk, ck, kb, rv, cv, vb)
     attention_close(out.float().cpu().numpy(), ref)
     # the cache contents themselves equal the oracle's quantisation of the same bf16 inputs
     kq = k.bfloat16().float().numpy().reshape(-1, dim)
     bk, _ = orc.lloyd_max_codebook(kb, dim)
     o_packed, o_norms = orc.quantize_mse(kq, kb, rk, bk)
-    got = cache._kp[1][:, :, :ctx].cpu().numpy().reshape(-1, o_packed.shape[1])
+    got = kp.reshape(-1, o_packed.shape[1])
     assert (got != o_packed).mean() < 1e-3
+    np.testing.assert_allclose(kn.reshape(-1), o_norms, rtol=2e-6)
 
 
 def test_decode_appends_token_by_token(orc):
@@ -152,8 +161,8 @@ def test_decode_appends_token_by_token(orc):
         q = torch.randn(batch, kv_heads * group, 1, dim, generator=gen)
         out = cache.decode_attention(0, q.cuda())
         assert out.shape == q.shape
-        ref = orc.decode_attention(q[:, :, 0].numpy(), cache._kp[0].cpu().numpy(), cache._kn[0].cpu().numpy(),
-                                   cache._vp[0].cpu().numpy(), cache._vn[0].cpu().numpy(),
+        kp, kn, vp, vn = exported(cache, 0, step + 1)
+        ref = orc.decode_attention(q[:, :, 0].numpy(), kp, kn, vp, vn,
                                    np.full(batch, step + 1, np.int32), rk, ck, 4, rv, cv, 2)
         attention_close(out[:, :, 0].cpu().numpy(), ref)
 
@@ -235,3 +244,42 @@ def test_protected_layers_and_upstream_cache_checks():
     assert 3 < only_q.compression_ratio < 10 and only_q.memory_bytes() > 0
     with pytest.raises(RuntimeError):
         QuantizedKVCache(TurboQuantConfig(mode="prod"), 1, 16, 2, 64, device="cuda").append(0, k[:2], v[:2])
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("kb,vb", [(4, 2), (4, 3), (4, 4), (3, 3), (2, 2), (3, 2), (2, 4)])
+def test_record_store_export_import_roundtrip(orc, dim, kb, vb):
+    """Upstream rows -> records -> upstream rows is the identity, at ragged positions, and what append()
+    stores equals the oracle's quantisation of the same inputs."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    rng = np.random.default_rng(dim + kb * 10 + vb)
+    B, H, seq = 2, 3, 37
+    cache = QuantizedKVCache(TurboQuantConfig(key_bits=kb, value_bits=vb, seed=42), 1, 50, H, dim, device="cuda", batch_size=B)
+    kp = rng.integers(0, 256, size=(B, H, seq, kb * dim // 8), dtype=np.uint8)
+    vp = rng.integers(0, 256, size=(B, H, seq, vb * dim // 8), dtype=np.uint8)
+    kn = rng.random(size=(B, H, seq)).astype(np.float32)
+    vn = rng.random(size=(B, H, seq)).astype(np.float32)
+    cache.load_packed(0, cuda(kp), cuda(kn), cuda(vp), cuda(vn))
+    assert int(cache.seq_lens[0]) == seq
+    g_kp, g_kn, g_vp, g_vn = exported(cache, 0, seq)
+    assert np.array_equal(g_kp, kp) and np.array_equal(g_vp, vp)
+    assert np.array_equal(g_kn, kn) and np.array_equal(g_vn, vn)
+    # overwrite in place (the clear-then-set path) and append behind it
+    cache.load_packed(0, cuda(255 - kp), cuda(kn), cuda(255 - vp), cuda(vn))
+    g_kp, _, g_vp, _ = exported(cache, 0, seq)
+    assert np.array_equal(g_kp, 255 - kp) and np.array_equal(g_vp, 255 - vp)
+    k = torch.randn(B, H, 5, dim, generator=torch.Generator().manual_seed(1))
+    v = torch.randn(B, H, 5, dim, generator=torch.Generator().manual_seed(2))
+    cache.append(0, k.cuda(), v.cuda())
+    g_kp, g_kn, g_vp, g_vn = exported(cache, 0, seq + 5)
+    assert np.array_equal(g_kp[:, :, :seq], 255 - kp)
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, _ = orc.lloyd_max_codebook(kb, dim)
+    bv, _ = orc.lloyd_max_codebook(vb, dim)
+    o_kp, o_kn = orc.quantize_mse(k.numpy().reshape(-1, dim), kb, rk, bk)
+    o_vp, o_vn = orc.quantize_mse(v.numpy().reshape(-1, dim), vb, rv, bv)
+    assert (g_kp[:, :, seq:].reshape(o_kp.shape) != o_kp).mean() < 2e-3
+    assert (g_vp[:, :, seq:].reshape(o_vp.shape) != o_vp).mean() < 2e-3
+    np.testing.assert_allclose(g_kn[:, :, seq:].reshape(-1), o_kn, rtol=2e-6)
+    np.testing.assert_allclose(g_vn[:, :, seq:].reshape(-1), o_vn, rtol=2e-6)

@@ -36,8 +36,8 @@ def test_hf_cache_update_returns_old_dequantised_new_exact(orc):
     st = cache._layer_stores[0]
     rv = orc.make_rotation_matrix(64, 43)
     _, cv = orc.lloyd_max_codebook(2, 64)
-    ref = orc.decode_attention(q.cpu().numpy(), st._kp.cpu().numpy(), st._kn.cpu().numpy(), st._vp.cpu().numpy(),
-                               st._vn.cpu().numpy(), np.full(2, 13, np.int32), rk, ck, 4, rv, cv, 2)
+    kp, kn, vp, vn = (t.cpu().numpy() for t in st.export())
+    ref = orc.decode_attention(q.cpu().numpy(), kp, kn, vp, vn, np.full(2, 13, np.int32), rk, ck, 4, rv, cv, 2)
     attention_close(out.cpu().numpy(), ref)
     k_it, v_it = cache[0]
     assert k_it.shape == (2, 4, 13, 64)
@@ -62,7 +62,7 @@ def test_c_abi_reports_errors_without_raising_across_the_boundary():
     assert rc == -1 and b"bit_width" in L.tqb_last_error()
     rc = L.tqb_quantize_mse(N.ptr(x), 0, 4, 1000, 1000, N.ptr(x), N.ptr(x), 4, N.ptr(x), N.ptr(x), None, None)
     assert rc == -2
-    rc = L.tqb_decode_attention(N.ptr(x), 0, 1, 4, 4, 64, N.ptr(x), N.ptr(x), N.ptr(x), N.ptr(x), 16, N.ptr(x), 16,
+    rc = L.tqb_decode_attention(N.ptr(x), 0, 1, 4, 4, 64, N.ptr(x), 16, N.ptr(x), 16,
                                 None, 0, 0, N.ptr(x), N.ptr(x), 4, N.ptr(x), N.ptr(x), 2, ctypes.c_float(1.0),
                                 N.ptr(x), 16, N.ptr(x), 0, None)
     assert rc == -4 and b"workspace" in L.tqb_last_error()

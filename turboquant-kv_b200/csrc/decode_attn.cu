@@ -22,7 +22,7 @@
 // Every wait is bounded: a warp that gives up records it in the status word at the start of the
 // workspace, drains nothing further and returns, so a lost copy cannot hang the device.
 #include "common.cuh"
-#include "decode_bits.cuh"
+#include "tiled_layout.cuh"
 
 namespace tqb {
 
@@ -87,10 +87,9 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 
 // ---- launch parameters --------------------------------------------------------------------------
 struct DecodeParams {
-    const uint8_t* k_packed; const float* k_norms;
-    const uint8_t* v_packed; const float* v_norms;
+    const uint8_t* store;            // tiled records (tiled_layout.cuh)
     const int32_t* seq_lens; const int32_t* block_tables;
-    int64_t max_seq;                 // row pitch of a unit (contiguous cache)
+    int64_t max_seq;                 // token pitch of a unit (contiguous cache), multiple of 16
     int batch, q_heads, kv_heads, group, max_blocks, block_size;
     int chunk, nchunks;              // tokens per (unit, chunk) work item
     const float* cent_k; const float* cent_v;
@@ -110,7 +109,7 @@ struct DecodeWorkspace {
 // 1. query rotation -> B fragments
 // =================================================================================================
 // One CTA (4 warps) per unit.  Fragment element (ks, lane = 4g+t, half) of head g holds the rotated,
-// normalised query coordinates pair_dims(D, t, 2ks+half); heads >= group are zero columns.
+// normalised query coordinates (16ks + 8half + 2t, +1); heads >= group are zero columns.
 template <typename T>
 __global__ void __launch_bounds__(128) rotate_query_kernel(const T* __restrict__ q, int q_heads, int kv_heads,
                                                            int group, int dim, const float* __restrict__ R,
@@ -156,8 +155,7 @@ __global__ void __launch_bounds__(128) rotate_query_kernel(const T* __restrict__
         const int g = fl >> 2, t = fl & 3;
         float lo = 0.0f, hi = 0.0f;
         if (g < group && qmax[g] > 0.0f) {
-            int dlo, dhi;
-            pair_dims(dim, t, 2 * ks + half, dlo, dhi);
+            const int dlo = 16 * ks + 8 * half + 2 * t, dhi = dlo + 1;   // k index = dimension
             const float inv = 1.0f / qmax[g];
             lo = qr[g][dlo] * inv;
             hi = qr[g][dhi] * inv;
@@ -168,33 +166,75 @@ __global__ void __launch_bounds__(128) rotate_query_kernel(const T* __restrict__
 
 
 // =================================================================================================
-// 2. streaming partial attention
+// 2. streaming partial attention over tiled records
 // =================================================================================================
 template <int D, int KB, int VB>
 struct DecodeCfg {
-    static constexpr int PK = KB * D / 8;                 // packed key row bytes
-    static constexpr int PV = VB * D / 8;
-    static constexpr int KT = TILE * PK;                  // tile bytes
-    static constexpr int VT = TILE * PV;
-    static constexpr int STAGE = KT + VT + 2 * TILE * 4;  // + key norms + value norms
+    static constexpr int KL = D * KB / 16, VL = D * VB / 16;       // bytes per lane
+    static constexpr int KSEC = 32 * KL, VSEC = 32 * VL;
+    static constexpr int REC = KSEC + VSEC + 128;                   // one 16-token record
     static constexpr int LUTK_ENTRIES = 1 << (2 * KB);
-    static constexpr int LUTV_ENTRIES = 1 << (VB == 2 ? 8 : 2 * VB);
-    static constexpr int LUTV_WORDS = VB == 2 ? 2 : 1;    // 8-byte entries for 2-bit values
+    static constexpr int LUTV_ENTRIES = VB == 2 ? 256 : (1 << (2 * VB));
+    static constexpr int LUTV_WORDS = VB == 2 ? 2 : 1;             // 8-byte entries for 2-bit values
     static constexpr int LUTK_BYTES = LUTK_ENTRIES * 32 * 4;
     static constexpr int LUTV_BYTES = LUTV_ENTRIES * 32 * 4 * LUTV_WORDS;
-    static constexpr int MT = D / 16;                     // m-tiles of O^T / k-steps of the scores
-    static constexpr int BV = D / 64;                     // value byte columns per thread
+    static constexpr int MT = D / 16;                               // m-tiles of O^T / k-steps of the scores
+    static constexpr int WARPS = D == 64 ? 16 : 8;
+    static constexpr int RPS = D == 64 ? 4 : 2;                     // records per pipeline stage
+    static constexpr int NS = D == 64 ? 2 : 4;                      // stages per warp
+    static constexpr int STAGE = RPS * REC;
+    static constexpr size_t SMEM = (size_t)LUTK_BYTES + LUTV_BYTES + (size_t)WARPS * NS * STAGE + WARPS * NS * 8 + 128;
 };
 
-// Position of a warp in its stream of tiles: items (unit, chunk) are dealt round-robin to warps,
-// tiles inside an item are consecutive.
-struct TileCursor {
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// A lane's chunk of NB bytes -> 32-bit registers, with the widest loads the chunk's alignment allows.
+template <int NB>
+__device__ __forceinline__ void load_chunk(const uint8_t* p, uint32_t (&w)[NB / 4]) {
+    if (NB % 16 == 0) {
+#pragma unroll
+        for (int i = 0; i < NB / 16; i++) {
+            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if (NB % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < NB / 8; i++) {
+            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NB / 4; i++) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+    }
+}
+
+// Byte offset of a table entry: (field value) << SHIFT, taken straight out of the chunk registers.
+// `bit` and `bits` are compile-time constants after unrolling, so this is one shift and one mask
+// (a funnel shift when the field straddles two registers).
+template <int NW, int SHIFT>
+__device__ __forceinline__ uint32_t lut_offset(const uint32_t (&w)[NW], int bit, int bits) {
+    const int i = bit >> 5, s = bit & 31;
+    uint32_t v;
+    if (s + bits <= 32) v = (s >= SHIFT) ? (w[i] >> (s - SHIFT)) : (w[i] << (SHIFT - s));
+    else v = __funnelshift_r(w[i], w[(i + 1) < NW ? (i + 1) : i], s) << SHIFT;
+    return v & (((1u << bits) - 1u) << SHIFT);
+}
+
+// Position of a warp in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to
+// warps; an item is cut into blocks of RPS records.
+template <int RPS>
+struct StageCursor {
     int64_t item, total_items, stride;
-    int tile, ntiles;         // inside the current item
+    int blk, nblk, ntiles;
     int unit, b, h, chunk_idx, tok0, tok_end;
     __device__ __forceinline__ bool valid() const { return item < total_items; }
+    __device__ __forceinline__ int tiles_here() const { return min(RPS, ntiles - blk * RPS); }
     __device__ __forceinline__ void open(const DecodeParams& p) {
-        // find the next item that has tokens
         while (item < total_items) {
             unit = (int)(item / p.nchunks);
             chunk_idx = (int)(item - (int64_t)unit * p.nchunks);
@@ -205,26 +245,28 @@ struct TileCursor {
             tok_end = min(S, tok0 + p.chunk);
             if (tok0 < tok_end) {
                 ntiles = (tok_end - tok0 + TILE - 1) / TILE;
-                tile = 0;
+                nblk = (ntiles + RPS - 1) / RPS;
+                blk = 0;
                 return;
             }
             item += stride;
         }
     }
     __device__ __forceinline__ void next(const DecodeParams& p) {
-        if (++tile == ntiles) { item += stride; open(p); }
+        if (++blk == nblk) { item += stride; open(p); }
     }
 };
 
-template <int D, int KB, int VB, bool PAGED, int WARPS, int NS>
-__global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const DecodeParams p) {
+template <int D, int KB, int VB, bool PAGED>
+__global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::WARPS * 32, 1) decode_partial_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KB, VB>;
+    constexpr int WARPS = C::WARPS, NS = C::NS, RPS = C::RPS;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint32_t* lutK = reinterpret_cast<uint32_t*>(smem_raw);
-    uint32_t* lutV = reinterpret_cast<uint32_t*>(smem_raw + C::LUTK_BYTES);
-    uint8_t* ring_all = smem_raw + C::LUTK_BYTES + C::LUTV_BYTES;
+    uint8_t* lutK_b = smem_raw;
+    uint8_t* lutV_b = smem_raw + C::LUTK_BYTES;
+    uint8_t* ring_all = lutV_b + C::LUTV_BYTES;
     uint64_t* bars_all = reinterpret_cast<uint64_t*>(ring_all + (size_t)WARPS * NS * C::STAGE);
-    __shared__ float s_ck[16], s_cv[16];
+    float* s_c = reinterpret_cast<float*>(bars_all + WARPS * NS);   // 16 key + 16 value centroids
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -232,8 +274,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
     const uint32_t bar0 = smem_u32(bars_all + warp * NS);
 
     if (threadIdx.x < 16) {
-        s_ck[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
-        s_cv[threadIdx.x] = threadIdx.x < (1 << VB) ? p.cent_v[threadIdx.x] : 0.0f;
+        s_c[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
+        s_c[16 + threadIdx.x] = threadIdx.x < (1 << VB) ? p.cent_v[threadIdx.x] : 0.0f;
     }
     if (lane == 0)
         for (int s = 0; s < NS; s++) mbar_init(bar0 + 8 * s, 1);
@@ -241,68 +283,74 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
     __syncthreads();
 
     // ---- lookup tables: entry x replicated for the 32 lanes at word x*32 + lane (no bank conflicts)
-    for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS) {
-        int clo, chi;
-        pair_index_codes<KB>((uint32_t)x, clo, chi);
-        lutK[x * 32 + lane] = pack_half2(s_ck[clo], s_ck[chi]);
-    }
-    for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS) {
-        if (VB == 2) {
-            int ag, bg, ag8, bg8;
-            quad_index_codes_v2((uint32_t)x, ag, bg, ag8, bg8);
-            reinterpret_cast<uint2*>(lutV)[x * 32 + lane] =
-                make_uint2(pack_half2(s_cv[ag], s_cv[bg]), pack_half2(s_cv[ag8], s_cv[bg8]));
-        } else {
-            int ca, cb;
-            token_pair_codes<VB>((uint32_t)x, ca, cb);
-            lutV[x * 32 + lane] = pack_half2(s_cv[ca], s_cv[cb]);
+    {
+        uint32_t* lutK = reinterpret_cast<uint32_t*>(lutK_b);
+        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS) {
+            int clo, chi;
+            tl_key_field_codes((uint32_t)x, KB, clo, chi);
+            lutK[x * 32 + lane] = pack_half2(s_c[clo], s_c[chi]);
+        }
+        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS) {
+            if (VB == 2) {
+                int ag, bg, ag8, bg8;
+                tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
+                reinterpret_cast<uint2*>(lutV_b)[x * 32 + lane] =
+                    make_uint2(pack_half2(s_c[16 + ag], s_c[16 + bg]), pack_half2(s_c[16 + ag8], s_c[16 + bg8]));
+            } else {
+                int ca, cb;
+                tl_val_pair_codes((uint32_t)x, VB, ca, cb);
+                reinterpret_cast<uint32_t*>(lutV_b)[x * 32 + lane] = pack_half2(s_c[16 + ca], s_c[16 + cb]);
+            }
         }
     }
     __syncthreads();
+    const uint8_t* lutK_lane = lutK_b + lane * 4;
+    const uint8_t* lutV_lane = lutV_b + lane * 4 * C::LUTV_WORDS;
 
-    const int64_t total_warps = (int64_t)gridDim.x * WARPS;
-    TileCursor pc, cc;  // producer / consumer cursors over the same stream
+    StageCursor<RPS> pc, cc;   // producer / consumer cursors over the same stream
     pc.item = (int64_t)blockIdx.x * WARPS + warp;
     pc.total_items = (int64_t)p.batch * p.kv_heads * p.nchunks;
-    pc.stride = total_warps;
-    pc.tile = pc.ntiles = 0;
+    pc.stride = (int64_t)gridDim.x * WARPS;
+    pc.blk = pc.nblk = pc.ntiles = 0;
     pc.open(p);
     cc = pc;
 
-    // issue the copies of the producer cursor's tile into stage s (lane 0 only)
-    auto issue = [&](const TileCursor& cur, int s) {
+    // lane 0 issues the bulk copies of one stage: a run of records of one unit (contiguous cache) or
+    // record by record through the block table (paged cache)
+    auto issue = [&](const StageCursor<RPS>& cur, int s) {
         if (lane == 0) {
-            const int tok = cur.tok0 + cur.tile * TILE;
-            int64_t row;
-            if (PAGED) {
-                const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tok / p.block_size];
-                row = ((int64_t)blk * p.kv_heads + cur.h) * p.block_size + tok % p.block_size;
-            } else {
-                row = (int64_t)cur.unit * p.max_seq + tok;
-            }
+            const int nt = cur.tiles_here();
+            const int tile0 = cur.tok0 / TILE + cur.blk * RPS;
             const uint32_t dst = smem_u32(ring + (size_t)s * C::STAGE);
             const uint32_t bar = bar0 + 8 * s;
             // order this warp's earlier generic-proxy reads of the stage before the async-proxy overwrite
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, C::STAGE);
-            bulk_g2s(dst, p.k_packed + row * C::PK, C::KT, bar);
-            bulk_g2s(dst + C::KT, p.v_packed + row * C::PV, C::VT, bar);
-            bulk_g2s(dst + C::KT + C::VT, p.k_norms + row, TILE * 4, bar);
-            bulk_g2s(dst + C::KT + C::VT + TILE * 4, p.v_norms + row, TILE * 4, bar);
+            mbar_expect_tx(bar, (uint32_t)(nt * C::REC));
+            if (PAGED) {
+                const int rpb = p.block_size / TILE;   // records per page
+                for (int i = 0; i < nt; i++) {
+                    const int tile = tile0 + i;
+                    const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
+                    const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
+                    bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, bar);
+                }
+            } else {
+                const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + tile0;
+                bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), bar);
+            }
         }
     };
 
     uint32_t issued = 0, consumed = 0;
     while (issued < NS && pc.valid()) { issue(pc, issued % NS); pc.next(p); issued++; }
 
-    // per-item state
     float m0 = NEG_INF, m1 = NEG_INF, l0 = 0.0f, l1 = 0.0f, qs0 = 0.0f, qs1 = 0.0f;
     float O[C::MT][4];
     uint32_t qf[C::MT][2];
     bool failed = false;
 
     while (cc.valid()) {
-        if (cc.tile == 0) {
+        if (cc.blk == 0) {
             m0 = m1 = NEG_INF; l0 = l1 = 0.0f;
 #pragma unroll
             for (int mt = 0; mt < C::MT; mt++) { O[mt][0] = O[mt][1] = O[mt][2] = O[mt][3] = 0.0f; }
@@ -315,108 +363,97 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
         const int s = consumed % NS;
         if (!mbar_wait(bar0 + 8 * s, (consumed / NS) & 1)) failed = true;
         if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
+        const int nt = cc.tiles_here();
+        const int tok_blk = cc.tok0 + cc.blk * RPS * TILE;
 
-        const uint8_t* kt = ring + (size_t)s * C::STAGE;
-        const uint8_t* vt = kt + C::KT;
-        const float* nk = reinterpret_cast<const float*>(vt + C::VT);
-        const float* nv = nk + TILE;
-        const int tokb = cc.tok0 + cc.tile * TILE;
-        const bool val_g = tokb + g < cc.tok_end, val_g8 = tokb + g + 8 < cc.tok_end;
+#pragma unroll 1
+        for (int i = 0; i < nt; i++) {
+            const uint8_t* rec = ring + (size_t)s * C::STAGE + i * C::REC;
+            const float* nk = reinterpret_cast<const float*>(rec + C::KSEC + C::VSEC);
+            const float* nv = nk + TILE;
+            const int tokb = tok_blk + i * TILE;
+            const bool val_g = tokb + g < cc.tok_end, val_g8 = tokb + g + 8 < cc.tok_end;
 
-        // ---- scores: 16 tokens x 8 heads ----
-        float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        {
-            uint32_t P[KeyWords<D>::NW][4];
-            gather_key_words<D, KB>(kt, C::PK, g, t, P);
-            uint32_t iw[KeyWords<D>::NW][4];
+            // ---- scores: 16 tokens x 8 heads ----
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            {
+                uint32_t kw[C::KL / 4];
+                load_chunk<C::KL>(rec + lane * C::KL, kw);
 #pragma unroll
-            for (int w = 0; w < KeyWords<D>::NW; w++)
-#pragma unroll
-                for (int u = 0; u < 4; u++) iw[w][u] = pair_index_word<KB>(P[w], u);
-#pragma unroll
-            for (int ks = 0; ks < C::MT; ks++) {
-                uint32_t a[4];
-#pragma unroll
-                for (int half = 0; half < 2; half++)
-#pragma unroll
-                    for (int second = 0; second < 2; second++) {
-                        int u, w, bl;
-                        key_element_slot<D>(2 * ks + half, second != 0, u, w, bl);
-                        const uint32_t x = (iw[w][u] >> (8 * bl)) & 0xFFu;
-                        a[2 * half + second] = lutK[x * 32 + lane];
-                    }
-                mma_f16(sc, a, qf[ks][0], qf[ks][1]);
-            }
-        }
-        const float nkg = val_g ? nk[g] : 0.0f, nkg8 = val_g8 ? nk[g + 8] : 0.0f;
-        float s0 = val_g ? sc[0] * (nkg * qs0) : NEG_INF, s1 = val_g ? sc[1] * (nkg * qs1) : NEG_INF;
-        float s2 = val_g8 ? sc[2] * (nkg8 * qs0) : NEG_INF, s3 = val_g8 ? sc[3] * (nkg8 * qs1) : NEG_INF;
-
-        // ---- online softmax, lazy maximum ----
-        float tm0 = fmaxf(s0, s2), tm1 = fmaxf(s1, s3);
-        if (__any_sync(0xffffffffu, (tm0 > m0 + RESCALE_SLACK) || (tm1 > m1 + RESCALE_SLACK))) {
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
-                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
-            }
-            const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
-            const float f0 = (mn0 == NEG_INF) ? 1.0f : exp2f(m0 - mn0);
-            const float f1 = (mn1 == NEG_INF) ? 1.0f : exp2f(m1 - mn1);
-            l0 *= f0; l1 *= f1;
-#pragma unroll
-            for (int mt = 0; mt < C::MT; mt++) { O[mt][0] *= f0; O[mt][2] *= f0; O[mt][1] *= f1; O[mt][3] *= f1; }
-            m0 = mn0; m1 = mn1;
-        }
-        const float mu0 = (m0 == NEG_INF) ? 0.0f : m0, mu1 = (m1 == NEG_INF) ? 0.0f : m1;
-        const float p0 = exp2f(s0 - mu0), p1 = exp2f(s1 - mu1), p2 = exp2f(s2 - mu0), p3 = exp2f(s3 - mu1);
-        l0 += p0 + p2; l1 += p1 + p3;
-        const float nvg = val_g ? nv[g] : 0.0f, nvg8 = val_g8 ? nv[g + 8] : 0.0f;
-        // P^T as B operand: (k = tokens, col = head) through two 8x8 transposes
-        const uint32_t pb0 = movmatrix_trans(pack_half2_sat(p0 * nvg, p1 * nvg));
-        const uint32_t pb1 = movmatrix_trans(pack_half2_sat(p2 * nvg8, p3 * nvg8));
-
-        // ---- O^T += V^T P^T : (dims x tokens) x (tokens x heads) ----
-#pragma unroll
-        for (int i = 0; i < C::BV; i++) {
-            const int c = C::BV * g + i;
-            const uint32_t WA0 = gather_value_word<D, VB>(vt, C::PV, 2 * t, c);
-            const uint32_t WB0 = gather_value_word<D, VB>(vt, C::PV, 2 * t + 1, c);
-            const uint32_t WA1 = gather_value_word<D, VB>(vt, C::PV, 2 * t + 8, c);
-            const uint32_t WB1 = gather_value_word<D, VB>(vt, C::PV, 2 * t + 9, c);
-            if (VB == 2) {
-                const uint32_t W0 = WA0 | (WB0 << 16), W1 = WA1 | (WB1 << 16);
-                const uint2* lut2 = reinterpret_cast<const uint2*>(lutV);
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const uint2 e0 = lut2[quad_index_v2(W0, u) * 32 + lane];
-                    const uint2 e1 = lut2[quad_index_v2(W1, u) * 32 + lane];
-                    const uint32_t a[4] = {e0.x, e0.y, e1.x, e1.y};
-                    mma_f16(O[4 * i + u], a, pb0, pb1);
-                }
-            } else {
-                uint32_t Ze0, Zo0, Ze1, Zo1;
-                token_pair_words(WA0, WB0, Ze0, Zo0);
-                token_pair_words(WA1, WB1, Ze1, Zo1);
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int ks = 0; ks < C::MT; ks++) {
                     uint32_t a[4];
-                    a[0] = lutV[token_pair_index(Ze0, Zo0, 2 * u + 1) * 32 + lane];
-                    a[1] = lutV[token_pair_index(Ze0, Zo0, 2 * u) * 32 + lane];
-                    a[2] = lutV[token_pair_index(Ze1, Zo1, 2 * u + 1) * 32 + lane];
-                    a[3] = lutV[token_pair_index(Ze1, Zo1, 2 * u) * 32 + lane];
-                    mma_f16(O[4 * i + u], a, pb0, pb1);
+#pragma unroll
+                    for (int half = 0; half < 2; half++)
+#pragma unroll
+                        for (int second = 0; second < 2; second++) {
+                            const uint32_t off = lut_offset<C::KL / 4, 7>(kw, tl_key_field_bit(D, KB, ks, half, second), 2 * KB);
+                            a[2 * half + second] = *reinterpret_cast<const uint32_t*>(lutK_lane + off);
+                        }
+                    mma_f16(sc, a, qf[ks][0], qf[ks][1]);
+                }
+            }
+            const float nkg = val_g ? nk[g] : 0.0f, nkg8 = val_g8 ? nk[g + 8] : 0.0f;
+            const float s0 = val_g ? sc[0] * (nkg * qs0) : NEG_INF, s1 = val_g ? sc[1] * (nkg * qs1) : NEG_INF;
+            const float s2 = val_g8 ? sc[2] * (nkg8 * qs0) : NEG_INF, s3 = val_g8 ? sc[3] * (nkg8 * qs1) : NEG_INF;
+
+            // ---- online softmax, lazy maximum ----
+            float tm0 = fmaxf(s0, s2), tm1 = fmaxf(s1, s3);
+            if (__any_sync(0xffffffffu, (tm0 > m0 + RESCALE_SLACK) || (tm1 > m1 + RESCALE_SLACK))) {
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
+                    tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
+                }
+                const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
+                const float f0 = (mn0 == NEG_INF) ? 1.0f : ex2_approx(m0 - mn0);
+                const float f1 = (mn1 == NEG_INF) ? 1.0f : ex2_approx(m1 - mn1);
+                l0 *= f0; l1 *= f1;
+#pragma unroll
+                for (int mt = 0; mt < C::MT; mt++) { O[mt][0] *= f0; O[mt][2] *= f0; O[mt][1] *= f1; O[mt][3] *= f1; }
+                m0 = mn0; m1 = mn1;
+            }
+            const float mu0 = (m0 == NEG_INF) ? 0.0f : m0, mu1 = (m1 == NEG_INF) ? 0.0f : m1;
+            const float p0 = ex2_approx(s0 - mu0), p1 = ex2_approx(s1 - mu1);
+            const float p2 = ex2_approx(s2 - mu0), p3 = ex2_approx(s3 - mu1);
+            l0 += p0 + p2; l1 += p1 + p3;
+            const float nvg = val_g ? nv[g] : 0.0f, nvg8 = val_g8 ? nv[g + 8] : 0.0f;
+            // P^T as B operand: (k = tokens, col = head) through two 8x8 transposes
+            const uint32_t pb0 = movmatrix_trans(pack_half2_sat(p0 * nvg, p1 * nvg));
+            const uint32_t pb1 = movmatrix_trans(pack_half2_sat(p2 * nvg8, p3 * nvg8));
+
+            // ---- O^T += V^T P^T : (dims x tokens) x (tokens x heads) ----
+            {
+                uint32_t vw[C::VL / 4];
+                load_chunk<C::VL>(rec + C::KSEC + lane * C::VL, vw);
+#pragma unroll
+                for (int mt = 0; mt < C::MT; mt++) {
+                    uint32_t a[4];
+                    if (VB == 2) {
+                        const uint2 e0 = *reinterpret_cast<const uint2*>(
+                            lutV_lane + lut_offset<C::VL / 4, 8>(vw, tl_val_field_bit(VB, mt, 0, 0), 8));
+                        const uint2 e1 = *reinterpret_cast<const uint2*>(
+                            lutV_lane + lut_offset<C::VL / 4, 8>(vw, tl_val_field_bit(VB, mt, 1, 0), 8));
+                        a[0] = e0.x; a[1] = e0.y; a[2] = e1.x; a[3] = e1.y;
+                    } else {
+#pragma unroll
+                        for (int half = 0; half < 2; half++)
+#pragma unroll
+                            for (int rs = 0; rs < 2; rs++)
+                                a[2 * half + rs] = *reinterpret_cast<const uint32_t*>(
+                                    lutV_lane + lut_offset<C::VL / 4, 7>(vw, tl_val_field_bit(VB, mt, half, rs), 2 * VB));
+                    }
+                    mma_f16(O[mt], a, pb0, pb1);
                 }
             }
         }
 
-        // ---- stage is free: refill it with the tile NS ahead ----
+        // ---- stage is free: refill it with the stage NS ahead ----
         __syncwarp();
         if (pc.valid()) { issue(pc, s); pc.next(p); issued++; }
         consumed++;
 
         // ---- end of item: write the partial (rotated space, unnormalised) ----
-        if (cc.tile + 1 == cc.ntiles) {
+        if (cc.blk + 1 == cc.nblk) {
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
                 l0 += __shfl_xor_sync(0xffffffffu, l0, o);
@@ -430,8 +467,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
             }
 #pragma unroll
             for (int mt = 0; mt < C::MT; mt++) {
-                int dg, dg8;
-                value_dims(D, g, mt, dg, dg8);
+                const int dg = 16 * mt + g, dg8 = dg + 8;
                 if (h0 < p.group) {
                     p.part_acc[(pbase + h0) * D + dg] = O[mt][0];
                     p.part_acc[(pbase + h0) * D + dg8] = O[mt][2];
@@ -452,7 +488,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_partial_kernel(const Dec
         for (uint32_t i = consumed; i < issued; i++) (void)mbar_wait(bar0 + 8 * (i % NS), (i / NS) & 1);
     }
 }
-
 
 // =================================================================================================
 // 3. merge of the chunks + inverse value rotation
@@ -488,7 +523,6 @@ __global__ void decode_merge_kernel(const DecodeParams p, int dim, const float* 
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-constexpr int DEC_WARPS = 8;
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -511,7 +545,7 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     DecodeWorkspace w{};
     const int64_t units = (int64_t)batch * kv_heads;
     const int group = q_heads / kv_heads;
-    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), (int64_t)sm_count() * DEC_WARPS);
+    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), (int64_t)sm_count() * (dim == 64 ? 16 : 8));
     w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
     size_t off = 0;
     w.off_status = off; off = align_up(off + 256, 256);
@@ -528,13 +562,11 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
 template <int D, int KB, int VB, bool PAGED>
 static int launch_partial(const DecodeParams& p, cudaStream_t st) {
     using C = DecodeCfg<D, KB, VB>;
-    constexpr int NS = (C::STAGE * DEC_WARPS * 8 + C::LUTK_BYTES + C::LUTV_BYTES <= 200 * 1024) ? 8 : 4;
-    const size_t smem = (size_t)C::LUTK_BYTES + C::LUTV_BYTES + (size_t)DEC_WARPS * NS * C::STAGE + DEC_WARPS * NS * 8;
-    auto kern = decode_partial_kernel<D, KB, VB, PAGED, DEC_WARPS, NS>;
-    TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    auto kern = decode_partial_kernel<D, KB, VB, PAGED>;
+    TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     const int64_t items = (int64_t)p.batch * p.kv_heads * p.nchunks;
-    const int grid = (int)std::min<int64_t>(sm_count(), ceil_div(items, DEC_WARPS));
-    kern<<<grid, DEC_WARPS * 32, smem, st>>>(p);
+    const int grid = (int)std::min<int64_t>(sm_count(), ceil_div(items, C::WARPS));
+    kern<<<grid, C::WARPS * 32, C::SMEM, st>>>(p);
     return check_launch("decode_partial");
 }
 
@@ -557,8 +589,7 @@ extern "C" size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, i
 }
 
 extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
-                                    int dim, const uint8_t* k_packed, const float* k_norms,
-                                    const uint8_t* v_packed, const float* v_norms, int64_t max_seq,
+                                    int dim, const uint8_t* store, int64_t max_seq,
                                     const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
                                     int max_blocks, int block_size, const float* rot_k, const float* cent_k,
                                     int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,
@@ -573,7 +604,7 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
         return fail(TQB_ERR_UNSUPPORTED, "decode_attention: head_dim must be 64 or 128, got %d", dim);
     if (group > 8) return fail(TQB_ERR_UNSUPPORTED, "decode_attention: at most 8 query heads per KV head, got %d", group);
     if (batch == 0) return TQB_OK;
-    TQB_REQUIRE(query && k_packed && k_norms && v_packed && v_norms && seq_lens && rot_k && cent_k && rot_v &&
+    TQB_REQUIRE(query && store && seq_lens && rot_k && cent_k && rot_v &&
                 cent_v && workspace && out, "decode_attention: null pointer");
     TQB_REQUIRE(max_len >= 0, "decode_attention: negative max_len");
     const bool paged = block_tables != nullptr;
@@ -584,8 +615,7 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
         TQB_REQUIRE(max_seq % 16 == 0 && max_seq >= max_len, "decode_attention: max_seq (%lld) must be a multiple of 16 and >= max_len (%lld)",
                     (long long)max_seq, (long long)max_len);
     }
-    TQB_REQUIRE(((uintptr_t)k_packed | (uintptr_t)v_packed | (uintptr_t)k_norms | (uintptr_t)v_norms) % 16 == 0,
-                "decode_attention: cache arrays must be 16-byte aligned");
+    TQB_REQUIRE((uintptr_t)store % 16 == 0, "decode_attention: the record store must be 16-byte aligned");
     TQB_REQUIRE((uintptr_t)workspace % 256 == 0, "decode_attention: workspace must be 256-byte aligned");
     const DecodeWorkspace w = plan_workspace(batch, q_heads, kv_heads, dim, max_len);
     if (workspace_bytes < w.total)
@@ -593,7 +623,7 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
 
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     DecodeParams p{};
-    p.k_packed = k_packed; p.k_norms = k_norms; p.v_packed = v_packed; p.v_norms = v_norms;
+    p.store = store;
     p.seq_lens = seq_lens; p.block_tables = block_tables; p.max_seq = max_seq;
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = group;
     p.max_blocks = max_blocks; p.block_size = block_size; p.chunk = w.chunk; p.nchunks = w.nchunks;

@@ -13,6 +13,7 @@
 // S residual = (S R^T)(R unit - c); the caller passes qjl_rot = S R^T.  ||residual|| is the same in
 // both spaces because R is orthogonal.
 #include "rowgemm.cuh"
+#include "tiled_layout.cuh"
 
 namespace tqb {
 
@@ -29,7 +30,52 @@ struct QuantArgs {
     uint8_t* packed; float* norms;
     uint8_t* signs; float* res_norms;  // Prod only (dense)
     RowMap map;
+    int tiled;                  // 0: upstream rows; 1 / 2: key / value section of the tiled KV store
+    int kb, vb;                 // tiled store geometry (bits of keys and values)
 };
+
+// Clear-then-set of a bit field in 32-bit words; safe against concurrent writers of OTHER bits of
+// the same word (two tokens of a pair share value bytes, 3-bit fields straddle bytes).
+__device__ __forceinline__ void tl_atomic_write(uint32_t* words, int absbit, int nbits, uint32_t v) {
+    const int w = absbit >> 5, s = absbit & 31;
+    const uint32_t mask = (1u << nbits) - 1u;
+    atomicAnd(&words[w], ~(mask << s));
+    atomicOr(&words[w], v << s);
+    if (s + nbits > 32) {
+        const int r = 32 - s;
+        atomicAnd(&words[w + 1], ~(mask >> r));
+        atomicOr(&words[w + 1], v >> r);
+    }
+}
+
+// One quantised row -> its token slot in the tiled KV store (tiled_layout.cuh).  Lane l holds the codes
+// of dims l + 32 q.  Called by all 32 lanes with the same `slot`.
+template <int NQ>
+__device__ __forceinline__ void tiled_store_row(const QuantArgs& a, int64_t slot, const uint32_t (&code)[NQ],
+                                                float nrm, int lane, int dim) {
+    uint8_t* rec = a.packed + (slot >> 4) * (int64_t)tl_record_bytes(dim, a.kb, a.vb);
+    const int r = (int)(slot & 15);
+    const int ksec = tl_key_section(dim, a.kb), vsec = tl_val_section(dim, a.vb);
+#pragma unroll
+    for (int q = 0; q < NQ; q++) {
+        const int d = lane + 32 * q;
+        const uint32_t partner = __shfl_down_sync(0xffffffffu, code[q], 1);
+        if (d >= dim) continue;
+        int base, bit;
+        if (a.tiled == 1) {
+            tl_key_slot(dim, a.kb, r, d, base, bit);
+            if (a.kb == 4) {   // a field is one whole byte owned by this token: plain store from the even lane
+                if ((lane & 1) == 0) rec[base + (bit >> 3)] = (uint8_t)(code[q] | (partner << 4));
+            } else {
+                tl_atomic_write(reinterpret_cast<uint32_t*>(rec), base * 8 + bit, a.kb, code[q]);
+            }
+        } else {
+            tl_val_slot(dim, a.vb, r, d, base, bit);
+            tl_atomic_write(reinterpret_cast<uint32_t*>(rec + ksec), base * 8 + bit, a.vb, code[q]);
+        }
+    }
+    if (lane == 0) reinterpret_cast<float*>(rec + ksec + vsec)[(a.tiled == 1 ? 0 : 16) + r] = nrm;
+}
 
 // Store one bit-plane group: lane (p * NQ + q) holds the 4 bytes at row offset p * bpp + 4 q.
 template <int NQ>
@@ -147,6 +193,14 @@ __global__ void __launch_bounds__(256) quantize_kernel(QuantArgs a0, QuantArgs a
                     ub[(lane + 32 * q) * RW + i] = e;
                 }
             }
+            if (PROD) rn[i] = sqrtf(warp_sum(ee));
+            if (!PROD && a.tiled) {
+                if (r < a.n) {
+                    const int64_t slot = a.map(r);
+                    if (slot >= 0) tiled_store_row<NQ>(a, slot, code, nrm[i], lane, dim);
+                }
+                continue;
+            }
             uint32_t mine = 0;
             for (int p = 0; p < a.mse_bits; p++)
 #pragma unroll
@@ -154,7 +208,6 @@ __global__ void __launch_bounds__(256) quantize_kernel(QuantArgs a0, QuantArgs a
                     const uint32_t w = ballot_to_plane_word(__ballot_sync(0xffffffffu, (code[q] >> p) & 1u));
                     if (lane == p * NQ + q) mine = w;
                 }
-            if (PROD) rn[i] = sqrtf(warp_sum(ee));
             if (r < a.n) {
                 const int64_t orow = a.map(r);
                 if (orow >= 0) {
@@ -263,20 +316,21 @@ extern "C" int tqb_quantize_mse(const void* x, int dtype, int64_t n, int dim, in
 
 extern "C" int tqb_kv_append(const void* key, const void* value, int dtype, int64_t n, int dim,
                              int64_t x_stride, const float* rot_k, const float* bnd_k, int kbits,
-                             const float* rot_v, const float* bnd_v, int vbits, uint8_t* k_packed,
-                             float* k_norms, uint8_t* v_packed, float* v_norms, const tqb_rowmap* map,
-                             void* stream) {
-    if (int e = tqb::check_common("kv_append", n, dim, kbits, 1, 4)) return e;
-    if (int e = tqb::check_common("kv_append", n, dim, vbits, 1, 4)) return e;
+                             const float* rot_v, const float* bnd_v, int vbits, uint8_t* store,
+                             const tqb_rowmap* map, void* stream) {
+    TQB_REQUIRE(n >= 0, "kv_append: negative row count");
+    if (dim != 64 && dim != 128) return tqb::fail(TQB_ERR_UNSUPPORTED, "kv_append: head_dim must be 64 or 128, got %d", dim);
+    if (kbits < 2 || kbits > 4 || vbits < 2 || vbits > 4)
+        return tqb::fail(TQB_ERR_UNSUPPORTED, "kv_append: key/value bits must be 2..4, got %d/%d", kbits, vbits);
     if (n == 0) return TQB_OK;
-    TQB_REQUIRE(key && value && rot_k && rot_v && bnd_k && bnd_v && k_packed && k_norms && v_packed && v_norms,
-                "kv_append: null pointer");
+    TQB_REQUIRE(key && value && rot_k && rot_v && bnd_k && bnd_v && store, "kv_append: null pointer");
     TQB_REQUIRE(x_stride >= dim, "kv_append: row stride %lld < dim %d", (long long)x_stride, dim);
+    TQB_REQUIRE((uintptr_t)store % 16 == 0, "kv_append: the record store must be 16-byte aligned");
     tqb::QuantArgs a{}, b{};
     a.x = key; a.n = n; a.x_stride = x_stride; a.rot = rot_k; a.bnd = bnd_k; a.mse_bits = kbits;
-    a.packed = k_packed; a.norms = k_norms; a.map = tqb::make_rowmap(map);
+    a.packed = store; a.norms = nullptr; a.map = tqb::make_rowmap(map); a.tiled = 1; a.kb = kbits; a.vb = vbits;
     b = a;
-    b.x = value; b.rot = rot_v; b.bnd = bnd_v; b.mse_bits = vbits; b.packed = v_packed; b.norms = v_norms;
+    b.x = value; b.rot = rot_v; b.bnd = bnd_v; b.mse_bits = vbits; b.tiled = 2;
     return tqb::dispatch_dtype<false>(dtype, a, b, 2, dim, (cudaStream_t)stream);
 }
 

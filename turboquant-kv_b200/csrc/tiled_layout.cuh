@@ -1,0 +1,109 @@
+// tiled_layout.cuh -- the fragment-major storage layout of the packed KV cache.
+//
+// The upstream layout (bit planes per token, reference.py:206-224) costs ~1.4 integer instructions per
+// code to turn into tensor-core operands, and the decode kernel is bound by instruction issue, not
+// by HBM.  The cache is therefore stored in a layout from which operands fall out of one shared-memory
+// load and a table lookup per TWO codes.  It holds exactly the same codes and the same number of
+// bytes per token; tqb_kv_export / tqb_kv_import convert to and from the upstream layout.
+//
+// Tokens are grouped in tiles of 16.  One RECORD holds one tile of one (sequence, KV head):
+//
+//   [ key section : 32 lanes x KL bytes ][ value section : 32 lanes x VL bytes ][ 16 key norms f32 ][ 16 value norms f32 ]
+//      KL = D*KB/16                          VL = D*VB/16                          record = 2*D*(KB+VB) + 128 bytes
+//
+// Lane = 4*g + t is the mma.sync lane that consumes the bytes (g = lane/4, t = lane%4).
+//
+// Key section, lane (g, t): the codes of tokens g (first KL/2 bytes) and g+8 (last KL/2 bytes) for the
+// dims this lane feeds into the score MMA.  A token's half is D/8 FIELDS of 2*KB bits, field e at bit
+// e*2*KB (little endian).  Field e = code[d] | code[d+1] << KB with d = 16*(e/2) + 8*(e%2) + 2*t, i.e.
+// exactly the A-operand elements (k = 2t, 2t+1 | 2t+8, 2t+9) of k-step e/2.
+//
+// Value section, lane (g, t): the codes of tokens {2t, 2t+1, 2t+8, 2t+9} for dims 16*mt + g and
+// 16*mt + g + 8 (mt < D/16): the A-operand of O^T += V^T P^T, whose contraction index is the token.
+//   VB == 2: field f = 2*mt + half (8 bits): bits[1:0] = code(token A, dim 16mt+g), [3:2] = (B, 16mt+g),
+//            [5:4] = (A, 16mt+g+8), [7:6] = (B, 16mt+g+8), with A = 2t + 8*half, B = A + 1.
+//   VB  > 2: field f = 2*(2*mt + half) + s (2*VB bits): code(A, dim) | code(B, dim) << VB, dim = 16mt+g+8s.
+//
+// Everything below is host/device so that tests replay it on the CPU.
+#pragma once
+#include <stdint.h>
+
+#include "decode_bits.cuh"
+
+namespace tqb {
+
+constexpr int TL_TILE = 16;
+
+TQB_HD int tl_key_lane_bytes(int D, int KB) { return D * KB / 16; }
+TQB_HD int tl_val_lane_bytes(int D, int VB) { return D * VB / 16; }
+TQB_HD int tl_record_bytes(int D, int KB, int VB) { return 2 * D * (KB + VB) + 128; }
+TQB_HD int tl_key_section(int D, int KB) { return 32 * tl_key_lane_bytes(D, KB); }
+TQB_HD int tl_val_section(int D, int VB) { return 32 * tl_val_lane_bytes(D, VB); }
+
+// Where the code of (token row r of the tile, dim d) lives in the KEY section:
+// byte offset of the lane's token half and the bit offset inside it.
+TQB_HD void tl_key_slot(int D, int KB, int r, int d, int& byte_base, int& bit) {
+    const int g = r & 7, second = r >> 3;
+    const int ks = d >> 4, half = (d >> 3) & 1, t = (d & 7) >> 1, hi = d & 1;
+    const int e = 2 * ks + half;
+    const int KL = tl_key_lane_bytes(D, KB);
+    byte_base = (4 * g + t) * KL + second * (KL / 2);
+    bit = e * 2 * KB + hi * KB;
+}
+
+// Same for the VALUE section (byte_base = start of the lane's chunk).
+TQB_HD void tl_val_slot(int D, int VB, int r, int d, int& byte_base, int& bit) {
+    const int half = r >> 3, t = (r & 7) >> 1, ab = r & 1;
+    const int mt = d >> 4, g = d & 7, s = (d >> 3) & 1;
+    const int VL = tl_val_lane_bytes(D, VB);
+    byte_base = (4 * g + t) * VL;
+    if (VB == 2) bit = (2 * mt + half) * 8 + 4 * s + 2 * ab;
+    else bit = (2 * (2 * mt + half) + s) * 2 * VB + ab * VB;
+}
+
+// Read `bits` bits at bit offset `bit` of a little-endian byte string (plain memory).
+TQB_HD uint32_t tl_read_bits(const uint8_t* p, int bit, int bits) {
+    uint32_t v = 0;
+    for (int i = 0; i < bits; i++) v |= (uint32_t)((p[(bit + i) >> 3] >> ((bit + i) & 7)) & 1) << i;
+    return v;
+}
+
+// Field extraction from a lane's chunk held in 32-bit registers (w[0] = first 4 bytes).
+template <int NW>
+TQB_HD uint32_t tl_field(const uint32_t (&w)[NW], int bit, int bits) {
+    const int i = bit >> 5, s = bit & 31;
+    uint32_t v = w[i] >> s;
+    if (s + bits > 32 && i + 1 < NW) v |= w[i + 1] << (32 - s);
+    return v & ((1u << bits) - 1u);
+}
+
+// Codes addressed by a key field / a value field (the table builders use these).
+TQB_HD void tl_key_field_codes(uint32_t x, int KB, int& c_lo, int& c_hi) {
+    c_lo = x & ((1 << KB) - 1);
+    c_hi = (x >> KB) & ((1 << KB) - 1);
+}
+TQB_HD void tl_val_quad_codes(uint32_t x, int& a_g, int& b_g, int& a_g8, int& b_g8) {
+    a_g = x & 3; b_g = (x >> 2) & 3; a_g8 = (x >> 4) & 3; b_g8 = (x >> 6) & 3;
+}
+TQB_HD void tl_val_pair_codes(uint32_t x, int VB, int& c_a, int& c_b) {
+    c_a = x & ((1 << VB) - 1);
+    c_b = (x >> VB) & ((1 << VB) - 1);
+}
+
+}  // namespace tqb
+
+// ---- consumer-side field positions (shared by the kernel and the host replay) ---------------------
+namespace tqb {
+
+// Bit offset, inside a lane's KEY chunk, of the field feeding A-operand element pair
+// (k-step ks, half) of token g (second = 0) or g+8 (second = 1).
+TQB_HD int tl_key_field_bit(int D, int KB, int ks, int half, int second) {
+    return second * (tl_key_lane_bytes(D, KB) * 4) + (2 * ks + half) * 2 * KB;
+}
+// Bit offset, inside a lane's VALUE chunk, of the field for m-tile mt, token half, fragment row s.
+// VB == 2: one 8-bit field serves both rows (s ignored).
+TQB_HD int tl_val_field_bit(int VB, int mt, int half, int s) {
+    return VB == 2 ? (2 * mt + half) * 8 : (2 * (2 * mt + half) + s) * 2 * VB;
+}
+
+}  // namespace tqb

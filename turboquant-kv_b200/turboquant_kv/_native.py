@@ -61,13 +61,18 @@ def lib():
                                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         L.tqb_attention_values_packed.argtypes = [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        L.tqb_kv_record_bytes.restype = c_int64
+        L.tqb_kv_record_bytes.argtypes = [c_int, c_int, c_int]
         L.tqb_kv_append.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_void_p,
-                                    c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    ctypes.POINTER(RowMap), c_void_p]
-        L.tqb_decode_attention.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                           c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
-                                           c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                           c_float, c_void_p, c_size_t, c_void_p, c_int, c_void_p]
+                                    c_int, c_void_p, c_void_p, c_int, c_void_p, ctypes.POINTER(RowMap), c_void_p]
+        L.tqb_kv_export.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, ctypes.POINTER(RowMap), c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p]
+        L.tqb_kv_import.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, ctypes.POINTER(RowMap), c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p]
+        L.tqb_decode_attention.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64,
+                                           c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p,
+                                           c_int, c_void_p]
         L.tqb_scan_topk.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                     c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
         L.tqb_topk_merge.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]

@@ -5,6 +5,11 @@ Same constructor and methods as upstream ``turboquant_kv/cache.py:29-381`` (``ap
 ``compression_ratio``).  Storage is written by the fused quantise kernels and read by kernels that
 work on the packed codes; nothing is dequantised to attend.
 
+Storage layout: quantised layers live in the 16-token record layout of ``kvstore.PackedKVStore``
+(same codes, same bytes per token as upstream, ordered for the decode kernel).  The upstream
+attributes ``_key_packed / _key_norms / _val_packed / _val_norms`` are still there, as read-only
+upstream-layout COPIES produced on access; ``load_packed`` writes upstream-layout rows back.
+
 Additions for serving (none changes upstream behaviour):
   * ``batch_size=B`` gives every sequence of a batch its own cache rows (upstream keeps a single
     sequence and silently drops ``key[1:]``, cache.py:157-160 -- still the behaviour when
@@ -26,11 +31,8 @@ import torch
 
 from . import _native as N
 from .config import TurboQuantConfig
+from .kvstore import PackedKVStore, pad16 as _pad16
 from .reference import _make_qjl_matrix, lloyd_max_codebook, make_rotation_matrix
-
-
-def _pad16(n: int) -> int:
-    return (n + 15) // 16 * 16
 
 
 class QuantizedKVCache:
@@ -80,15 +82,12 @@ class QuantizedKVCache:
 
         bpp = (head_dim + 7) // 8
         self._pk, self._pv = config.key_bits * bpp, config.value_bits * bpp
-        B, H, P = self._batch, num_heads, self._pitch
-
-        def codes(width):
-            return [torch.zeros(B, H, P, width, dtype=torch.uint8, device=dev) for _ in range(num_layers)]
-
-        def scalars():
-            return [torch.zeros(B, H, P, dtype=torch.float32, device=dev) for _ in range(num_layers)]
-
-        self._kp, self._kn, self._vp, self._vn = codes(self._pk), scalars(), codes(self._pv), scalars()
+        B, H = self._batch, num_heads
+        self._kv: Optional[PackedKVStore] = None
+        self._store = []
+        if not self._is_prod:
+            self._kv = PackedKVStore(head_dim, config.key_bits, config.value_bits, config.seed, config.rotation, dev)
+            self._store = [self._kv.alloc(B * H, self._pitch) for _ in range(num_layers)]
 
         self._protected = config.protected_layers > 0
         if self._protected:
@@ -96,28 +95,49 @@ class QuantizedKVCache:
                             for _ in range(config.protected_layers)]
             self._val_fp = [torch.zeros(B, H, max_seq_len, head_dim, dtype=torch.float16, device=dev)
                             for _ in range(config.protected_layers)]
-        self._workspace: Optional[torch.Tensor] = None
 
-    # ---- upstream-shaped views of the storage: (num_heads, max_seq_len, ...) when batch_size is None
-    def _view(self, store):
-        out = [t[:, :, : self.max_seq_len] for t in store]
-        return [t[0] for t in out] if self.batch_size is None else out
+    # ---- upstream-shaped copies of the storage: (num_heads, max_seq_len, ...) when batch_size is None
+    def _export(self, layer_id: int, seq: int, keys: bool = True, values: bool = True):
+        """Upstream-layout rows of the first `seq` tokens of every (sequence, head): each (B*H*seq, ...)."""
+        rm = N.RowMap(max(seq, 1), self._pitch, 1, 0, None, 1, None, 1)
+        return self._kv.export_rows(self._store[layer_id], self._batch * self.num_heads * seq, rm, keys, values)
+
+    def _upstream_view(self, which: int):
+        B, H, S = self._batch, self.num_heads, self.max_seq_len
+        out = []
+        for layer in range(self.num_layers):
+            t = self._export(layer, S, keys=which < 2, values=which >= 2)[which]
+            t = t.view(B, H, S, -1) if t.dim() == 2 else t.view(B, H, S)
+            out.append(t[0] if self.batch_size is None else t)
+        return out
 
     @property
     def _key_packed(self):
-        return self._view(self._kp)
+        return self._upstream_view(0)
 
     @property
     def _key_norms(self):
-        return self._view(self._kn)
+        return self._upstream_view(1)
 
     @property
     def _val_packed(self):
-        return self._view(self._vp)
+        return self._upstream_view(2)
 
     @property
     def _val_norms(self):
-        return self._view(self._vn)
+        return self._upstream_view(3)
+
+    def load_packed(self, layer_id: int, k_packed=None, k_norms=None, v_packed=None, v_norms=None) -> None:
+        """Write upstream-layout rows into the cache: tensors shaped ([batch,] heads, seq, ...), the first
+        `seq` tokens of every (sequence, head).  Sets the layer's length to `seq`."""
+        first = next(t for t in (k_norms, v_norms, k_packed, v_packed) if t is not None)
+        seq = first.shape[-1] if first.dtype != torch.uint8 else first.shape[-2]
+        flat = lambda t, last: None if t is None else (t.reshape(-1, t.shape[-1]) if last else t.reshape(-1))
+        rm = N.RowMap(max(seq, 1), self._pitch, 1, 0, None, 1, None, 1)
+        self._kv.import_rows(self._store[layer_id], rm, flat(k_packed, True), flat(k_norms, False),
+                             flat(v_packed, True), flat(v_norms, False))
+        self.seq_lens[layer_id] = seq
+        self._seq_lens_dev[layer_id] = seq
 
     def _is_protected_layer(self, layer_id: int) -> bool:
         return self._protected and layer_id < self.config.protected_layers
@@ -154,20 +174,10 @@ class QuantizedKVCache:
                 "QuantizedKVCache in prod mode: upstream stores key_bits planes per token but quantize_prod "
                 "yields key_bits - 1, so upstream append() fails with a shape error; not supported here either")
         else:
-            k = self._as_rows(key)
-            v = self._as_rows(value)
             # rows are (batch*head, token); the write position is read on the device so that a captured
             # CUDA graph of a decode step keeps appending at the right place when replayed
             rm = N.RowMap(T, self._pitch, 1, 0, N.ptr(self._seq_lens_dev[layer_id]), H, None, 1)
-            cfg = self.config
-            with torch.cuda.device(self.device):
-                N.check(N.lib().tqb_kv_append(
-                    N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), B * H * T, D, D,
-                    N.ptr(self._key_rotation), N.ptr(self._kb_dev[0]), cfg.key_bits,
-                    N.ptr(self._val_rotation), N.ptr(self._vb_dev[0]), cfg.value_bits,
-                    N.ptr(self._kp[layer_id]), N.ptr(self._kn[layer_id]),
-                    N.ptr(self._vp[layer_id]), N.ptr(self._vn[layer_id]),
-                    rm, N.stream_of(k)))
+            self._kv.append(self._store[layer_id], self._as_rows(key), self._as_rows(value), rm)
         self.seq_lens[layer_id] += T
         self._seq_lens_dev[layer_id] += T
 
@@ -178,7 +188,7 @@ class QuantizedKVCache:
         return x.contiguous()
 
     # ------------------------------------------------------------------------------------------
-    def _dequantize(self, layer_id: int, packed, norms, bits, rotation, centroids, fp_store):
+    def _dequantize(self, layer_id: int, which: str, fp_store):
         seq = int(self.seq_lens[layer_id])
         B, H, D = self._batch, self.num_heads, self.head_dim
         if seq == 0:
@@ -186,23 +196,17 @@ class QuantizedKVCache:
         elif self._is_protected_layer(layer_id):
             out = fp_store[layer_id][:, :, :seq].float()
         else:
-            p = packed[layer_id][:, :, :seq].contiguous().view(B * H * seq, -1)
-            n = norms[layer_id][:, :, :seq].contiguous().view(-1)
-            out = torch.empty(B * H * seq, D, dtype=torch.float32, device=self.device)
-            with torch.cuda.device(self.device):
-                N.check(N.lib().tqb_dequantize_mse(N.ptr(p), N.ptr(n), B * H * seq, D, N.ptr(rotation),
-                                                   N.ptr(centroids), bits, N.ptr(out), N.F32, N.stream_of(p)))
+            kp, kn, vp, vn = self._export(layer_id, seq, keys=which == "key", values=which == "value")
+            out = self._kv.dequantize(kp if which == "key" else vp, kn if which == "key" else vn, which)
             out = out.view(B, H, seq, D)
         return out[0] if self.batch_size is None else out
 
     def _dequantize_keys(self, layer_id: int) -> torch.Tensor:
         """Dense keys (num_heads, seq, head_dim) float32 (with a leading batch dim for batched caches)."""
-        return self._dequantize(layer_id, self._kp, self._kn, self.config.key_bits, self._key_rotation,
-                                self._kb_dev[1], getattr(self, "_key_fp", None))
+        return self._dequantize(layer_id, "key", getattr(self, "_key_fp", None))
 
     def _dequantize_values(self, layer_id: int) -> torch.Tensor:
-        return self._dequantize(layer_id, self._vp, self._vn, self.config.value_bits, self._val_rotation,
-                                self._vb_dev[1], getattr(self, "_val_fp", None))
+        return self._dequantize(layer_id, "value", getattr(self, "_val_fp", None))
 
     # ------------------------------------------------------------------------------------------
     def attention_scores(self, layer_id: int, query: torch.Tensor) -> torch.Tensor:
@@ -226,14 +230,14 @@ class QuantizedKVCache:
             logits = torch.matmul(q, keys.transpose(-2, -1).unsqueeze(0)) * scale
         else:
             logits = torch.empty(nb, H, sq, seq, dtype=torch.float32, device=self.device)
+            kp, kn, _, _ = self._export(layer_id, seq, values=False)
+            kp, kn = kp.view(H, seq, -1), kn.view(H, seq)
             with torch.cuda.device(self.device):
                 for h in range(H):
                     qh = q[:, h].reshape(nb * sq, D).contiguous()
                     out = torch.empty(nb * sq, seq, dtype=torch.float32, device=self.device)
-                    pk = self._kp[layer_id][0, h, :seq]
-                    kn = self._kn[layer_id][0, h, :seq]
                     N.check(N.lib().tqb_attention_scores_packed(
-                        N.ptr(qh), nb * sq, D, N.ptr(pk), N.ptr(kn), seq, N.ptr(self._kb_dev[1]),
+                        N.ptr(qh), nb * sq, D, N.ptr(kp[h]), N.ptr(kn[h]), seq, N.ptr(self._kb_dev[1]),
                         N.ptr(self._key_rotation), self.config.key_bits, N.ptr(out), N.stream_of(qh)))
                     logits[:, h] = out.view(nb, sq, seq)
             logits *= scale
@@ -254,14 +258,14 @@ class QuantizedKVCache:
             out = torch.matmul(w, vals.unsqueeze(0))
         else:
             out = torch.empty(nb, H, sq, D, dtype=torch.float32, device=self.device)
+            _, _, vp, vn = self._export(layer_id, seq, keys=False)
+            vp, vn = vp.view(H, seq, -1), vn.view(H, seq)
             with torch.cuda.device(self.device):
                 for h in range(H):
                     wh = w[:, h].reshape(nb * sq, seq).contiguous()
                     oh = torch.empty(nb * sq, D, dtype=torch.float32, device=self.device)
-                    pv = self._vp[layer_id][0, h, :seq]
-                    vn = self._vn[layer_id][0, h, :seq]
                     N.check(N.lib().tqb_attention_values_packed(
-                        N.ptr(wh), nb * sq, seq, D, N.ptr(pv), N.ptr(vn), N.ptr(self._vb_dev[1]),
+                        N.ptr(wh), nb * sq, seq, D, N.ptr(vp[h]), N.ptr(vn[h]), N.ptr(self._vb_dev[1]),
                         N.ptr(self._val_rotation), self.config.value_bits, N.ptr(oh), N.stream_of(wh)))
                     out[:, h] = oh.view(nb, sq, D)
         return out if has_batch else out.squeeze(0)
@@ -278,37 +282,19 @@ class QuantizedKVCache:
         if self._is_protected_layer(layer_id) or self._is_prod:
             raise RuntimeError("decode_attention covers MSE-quantised layers")
         squeeze = query.dim() == 4
-        q = (query[:, :, 0] if squeeze else query).to(self.device)
-        if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
-            q = q.float()
-        q = q.contiguous()
+        q = query[:, :, 0] if squeeze else query
         B, HQ, D = q.shape
         if B != self._batch or D != self.head_dim or HQ % self.num_heads:
             raise RuntimeError(f"query {tuple(query.shape)} does not fit cache (batch {self._batch}, "
                                f"kv heads {self.num_heads}, head_dim {self.head_dim})")
-        if scale is None:
-            scale = 1.0 / math.sqrt(D)
         max_len = self._pitch if torch.cuda.is_current_stream_capturing() else int(self.seq_lens[layer_id])
-        need = max(N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self._pitch),
-                   N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, max_len))
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
-        res = out if out is not None else torch.empty(B, HQ, D, dtype=q.dtype, device=self.device)
-        cfg = self.config
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_decode_attention(
-                N.ptr(q), N.dtype_code(q.dtype), B, HQ, self.num_heads, D,
-                N.ptr(self._kp[layer_id]), N.ptr(self._kn[layer_id]), N.ptr(self._vp[layer_id]),
-                N.ptr(self._vn[layer_id]), self._pitch, N.ptr(self._seq_lens_dev[layer_id]), max_len,
-                None, 0, 0, N.ptr(self._key_rotation), N.ptr(self._kb_dev[1]), cfg.key_bits,
-                N.ptr(self._val_rotation), N.ptr(self._vb_dev[1]), cfg.value_bits, float(scale),
-                N.ptr(self._workspace), self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype),
-                N.stream_of(q)))
+        res = self._kv.decode_attention(self._store[layer_id], q, self.num_heads, self._seq_lens_dev[layer_id],
+                                        max_len, pitch=self._pitch, scale=scale, out=out, reserve_len=self._pitch)
         return res.unsqueeze(2) if squeeze else res
 
     def decode_status(self) -> int:
         """0 when every bounded device-side wait of the last decode_attention completed (synchronises)."""
-        return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
+        return 0 if self._kv is None else self._kv.status()
 
     # ------------------------------------------------------------------------------------------
     def memory_bytes(self) -> int:

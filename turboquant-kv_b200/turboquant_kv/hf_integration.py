@@ -20,7 +20,7 @@ import torch
 
 from . import _native as N
 from .config import TurboQuantConfig
-from .reference import lloyd_max_codebook, make_rotation_matrix
+from .kvstore import PackedKVStore
 
 _TRANSFORMERS_AVAILABLE = False
 _DynamicCache: type = object
@@ -43,16 +43,10 @@ class _LayerQuantStore:
         self.device = torch.device(device)
         self.seq_len = 0
         self.capacity = 0
-        cfg = tq_config
-        self._key_rotation = make_rotation_matrix(head_dim, seed=cfg.seed, method=cfg.rotation).to(device)
-        self._val_rotation = make_rotation_matrix(head_dim, seed=cfg.seed + 1, method=cfg.rotation).to(device)
-        self._key_codebook = tuple(t.to(device) for t in lloyd_max_codebook(cfg.key_bits, head_dim))
-        self._val_codebook = tuple(t.to(device) for t in lloyd_max_codebook(cfg.value_bits, head_dim))
-        bpp = (head_dim + 7) // 8
-        self._pk, self._pv = cfg.key_bits * bpp, cfg.value_bits * bpp
-        self._kp = self._kn = self._vp = self._vn = None
+        self.kv = PackedKVStore(head_dim, tq_config.key_bits, tq_config.value_bits, tq_config.seed,
+                                tq_config.rotation, device)
+        self._store: Optional[torch.Tensor] = None
         self._len_dev = torch.zeros(batch, dtype=torch.int32, device=device)
-        self._workspace: Optional[torch.Tensor] = None
 
     def _reserve(self, need: int) -> None:
         if need <= self.capacity:
@@ -60,75 +54,48 @@ class _LayerQuantStore:
         cap = max(256, self.capacity)
         while cap < need:
             cap *= 2
-        B, H, dev = self.batch, self.num_heads, self.device
-
-        def grown(old, shape, dtype):
-            new = torch.zeros(shape, dtype=dtype, device=dev)
-            if old is not None and self.seq_len:
-                new[:, :, : self.seq_len] = old[:, :, : self.seq_len]
-            return new
-
-        self._kp = grown(self._kp, (B, H, cap, self._pk), torch.uint8)
-        self._vp = grown(self._vp, (B, H, cap, self._pv), torch.uint8)
-        self._kn = grown(self._kn, (B, H, cap), torch.float32)
-        self._vn = grown(self._vn, (B, H, cap), torch.float32)
-        self.capacity = cap
+        new = self.kv.alloc(self.batch * self.num_heads, cap)
+        if self._store is not None:
+            new[:, : self._store.shape[1]] = self._store
+        self._store, self.capacity = new, cap
 
     def append(self, key: torch.Tensor, value: torch.Tensor) -> None:
         """key / value: (batch, heads, new, head_dim)."""
-        B, H, T, D = key.shape
+        T = key.shape[2]
         self._reserve(self.seq_len + T)
-        k = key.contiguous() if key.dtype in (torch.float32, torch.float16, torch.bfloat16) else key.float().contiguous()
-        v = value.to(k.dtype).contiguous()
-        cfg = self.tq_config
         rm = N.RowMap(T, self.capacity, 1, self.seq_len, None, 1, None, 1)
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_kv_append(
-                N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), B * H * T, D, D,
-                N.ptr(self._key_rotation), N.ptr(self._key_codebook[0]), cfg.key_bits,
-                N.ptr(self._val_rotation), N.ptr(self._val_codebook[0]), cfg.value_bits,
-                N.ptr(self._kp), N.ptr(self._kn), N.ptr(self._vp), N.ptr(self._vn), rm, N.stream_of(k)))
+        self.kv.append(self._store, key, value, rm)
         self.seq_len += T
         self._len_dev += T
 
-    def _dense(self, packed, norms, bits, rotation, centroids, dtype) -> torch.Tensor:
+    def _dense(self, which: str, dtype) -> torch.Tensor:
         B, H, S, D = self.batch, self.num_heads, self.seq_len, self.head_dim
         if S == 0:
             return torch.zeros(B, H, 0, D, dtype=dtype, device=self.device)
-        p = packed[:, :, :S].contiguous().view(B * H * S, -1)
-        n = norms[:, :, :S].contiguous().view(-1)
-        out = torch.empty(B * H * S, D, dtype=dtype, device=self.device)
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_dequantize_mse(N.ptr(p), N.ptr(n), B * H * S, D, N.ptr(rotation), N.ptr(centroids),
-                                               bits, N.ptr(out), N.dtype_code(dtype), N.stream_of(p)))
+        rm = N.RowMap(S, self.capacity, 1, 0, None, 1, None, 1)
+        kp, kn, vp, vn = self.kv.export_rows(self._store, B * H * S, rm, keys=which == "key", values=which == "value")
+        out = self.kv.dequantize(kp if which == "key" else vp, kn if which == "key" else vn, which, dtype)
         return out.view(B, H, S, D)
 
     def get_keys(self, dtype=torch.float32) -> torch.Tensor:
-        return self._dense(self._kp, self._kn, self.tq_config.key_bits, self._key_rotation, self._key_codebook[1], dtype)
+        return self._dense("key", dtype)
 
     def get_values(self, dtype=torch.float32) -> torch.Tensor:
-        return self._dense(self._vp, self._vn, self.tq_config.value_bits, self._val_rotation, self._val_codebook[1], dtype)
+        return self._dense("value", dtype)
+
+    def export(self):
+        """Upstream-layout rows of everything stored: k_packed (B, H, S, pk), k_norms (B, H, S), v_packed, v_norms."""
+        B, H, S = self.batch, self.num_heads, self.seq_len
+        rm = N.RowMap(max(S, 1), self.capacity, 1, 0, None, 1, None, 1)
+        kp, kn, vp, vn = self.kv.export_rows(self._store, B * H * S, rm)
+        return kp.view(B, H, S, -1), kn.view(B, H, S), vp.view(B, H, S, -1), vn.view(B, H, S)
 
     def decode_attention(self, query: torch.Tensor, scale: Optional[float]) -> torch.Tensor:
-        q = query.contiguous()
-        B, HQ, D = q.shape
-        need = N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self.capacity)
-        need = max(need, N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, self.seq_len))
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
-        out = torch.empty_like(q)
-        cfg = self.tq_config
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_decode_attention(
-                N.ptr(q), N.dtype_code(q.dtype), B, HQ, self.num_heads, D, N.ptr(self._kp), N.ptr(self._kn),
-                N.ptr(self._vp), N.ptr(self._vn), self.capacity, N.ptr(self._len_dev), self.seq_len, None, 0, 0,
-                N.ptr(self._key_rotation), N.ptr(self._key_codebook[1]), cfg.key_bits, N.ptr(self._val_rotation),
-                N.ptr(self._val_codebook[1]), cfg.value_bits, float(scale if scale is not None else 1.0 / math.sqrt(D)),
-                N.ptr(self._workspace), self._workspace.numel(), N.ptr(out), N.dtype_code(out.dtype), N.stream_of(q)))
-        return out
+        return self.kv.decode_attention(self._store, query, self.num_heads, self._len_dev, self.seq_len,
+                                        pitch=self.capacity, scale=scale, reserve_len=self.capacity)
 
     def packed_bytes(self) -> int:
-        per_token = self._pk + self._pv + 8
+        per_token = self.kv.pk + self.kv.pv + 8
         return self.batch * self.num_heads * self.seq_len * per_token
 
 

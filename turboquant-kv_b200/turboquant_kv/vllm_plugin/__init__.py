@@ -5,8 +5,8 @@ Same names and method signatures (``TurboQuantKVCacheConfig`` :67, ``TurboQuantP
 cache is paged in name only (it wraps one contiguous single-sequence cache and never uses block
 tables or slot mappings, :114-304).  Here the pool really is paged:
 
-    keys    (num_blocks, kv_heads, block_size, key_bits   * head_dim / 8) uint8 + (.., block_size) f32 norms
-    values  (num_blocks, kv_heads, block_size, value_bits * head_dim / 8) uint8 + norms
+    (num_blocks * kv_heads, block_size / 16, record_bytes) uint8: 16-token records of key codes, value
+    codes and both norms per (block, head), in the layout of ``kvstore.PackedKVStore``
 
 ``append_slots`` scatters freshly quantised tokens through a vLLM slot mapping in one launch and
 ``paged_decode_attention`` runs the fused decode kernel through block tables (grouped-query heads,
@@ -27,7 +27,7 @@ import torch
 
 from .. import _native as N
 from ..config import TurboQuantConfig
-from ..reference import lloyd_max_codebook, make_rotation_matrix
+from ..kvstore import PackedKVStore
 
 
 class AttentionBackend:  # stand-ins for vLLM's abstract bases (duck-typed by the engine)
@@ -79,34 +79,25 @@ class TurboQuantPagedKVCache:
             self.device = torch.device("cuda", torch.cuda.current_device())
         self.block_size = config.block_size
         self.tq_config = config.to_turboquant_config()
-        dev = self.device
-        self._key_rotation = make_rotation_matrix(head_dim, seed=config.seed, method=config.rotation).to(dev)
-        self._val_rotation = make_rotation_matrix(head_dim, seed=config.seed + 1, method=config.rotation).to(dev)
-        self._kb = tuple(t.to(dev) for t in lloyd_max_codebook(config.key_bits, head_dim))
-        self._vb = tuple(t.to(dev) for t in lloyd_max_codebook(config.value_bits, head_dim))
-        bpp = (head_dim + 7) // 8
-        self._pk, self._pv = config.key_bits * bpp, config.value_bits * bpp
+        self.kv = PackedKVStore(head_dim, config.key_bits, config.value_bits, config.seed, config.rotation, self.device)
+        self._key_rotation, self._val_rotation = self.kv.key_rotation, self.kv.val_rotation
+        self._kb, self._vb = self.kv.key_codebook, self.kv.val_codebook
+        self._pk, self._pv = self.kv.pk, self.kv.pv
         self._total_blocks = 0
         self._max_tokens = 0
-        self._kp: List[torch.Tensor] = []
+        self._pools: List[torch.Tensor] = []
         self._seq_len = [0] * num_layers          # upstream-style single-sequence fill level per layer
-        self._workspace: Optional[torch.Tensor] = None
         if config.num_gpu_blocks > 0:
             self.allocate(config.num_gpu_blocks, config.num_cpu_blocks)
 
     def allocate(self, num_gpu_blocks: int, num_cpu_blocks: int = 0) -> None:
         """(Re)allocate the pools for `num_gpu_blocks` pages."""
-        nb, H, bs, dev = num_gpu_blocks, self.num_heads, self.block_size, self.device
-        self._total_blocks, self._max_tokens = nb, nb * bs
-        L = self.num_layers
-        self._kp = [torch.zeros(nb, H, bs, self._pk, dtype=torch.uint8, device=dev) for _ in range(L)]
-        self._vp = [torch.zeros(nb, H, bs, self._pv, dtype=torch.uint8, device=dev) for _ in range(L)]
-        self._kn = [torch.zeros(nb, H, bs, dtype=torch.float32, device=dev) for _ in range(L)]
-        self._vn = [torch.zeros(nb, H, bs, dtype=torch.float32, device=dev) for _ in range(L)]
-        self._seq_len = [0] * L
+        self._total_blocks, self._max_tokens = num_gpu_blocks, num_gpu_blocks * self.block_size
+        self._pools = [self.kv.alloc(num_gpu_blocks * self.num_heads, self.block_size) for _ in range(self.num_layers)]
+        self._seq_len = [0] * self.num_layers
 
     def _need_pool(self):
-        if not self._kp:
+        if not self._pools:
             raise RuntimeError("KV cache not allocated: call allocate(num_gpu_blocks) first")
 
     # ---- paged API ---------------------------------------------------------------------------
@@ -115,17 +106,9 @@ class TurboQuantPagedKVCache:
         block * block_size + offset, negative = skip (vLLM padding)."""
         self._need_pool()
         T, H, D = key.shape
-        k = key.to(self.device)
-        k = (k if k.dtype in (torch.float32, torch.float16, torch.bfloat16) else k.float()).contiguous()
-        v = value.to(self.device, k.dtype).contiguous()
         slots = slot_mapping.to(self.device, torch.int64).contiguous()
         rm = N.RowMap(H, 0, 0, 0, None, 1, N.ptr(slots), self.block_size)
-        c = self.config
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_kv_append(
-                N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), T * H, D, D, N.ptr(self._key_rotation), N.ptr(self._kb[0]),
-                c.key_bits, N.ptr(self._val_rotation), N.ptr(self._vb[0]), c.value_bits, N.ptr(self._kp[layer_id]),
-                N.ptr(self._kn[layer_id]), N.ptr(self._vp[layer_id]), N.ptr(self._vn[layer_id]), rm, N.stream_of(k)))
+        self.kv.append(self._pools[layer_id], key, value, rm)
 
     def paged_decode_attention(self, layer_id: int, query: torch.Tensor, block_tables: torch.Tensor,
                                seq_lens: torch.Tensor, max_seq_len: Optional[int] = None,
@@ -133,33 +116,16 @@ class TurboQuantPagedKVCache:
         """query (batch, q_heads, head_dim); block_tables (batch, max_blocks) int32; seq_lens (batch,) int32.
         `max_seq_len` is a host upper bound on seq_lens (defaults to the table capacity: no sync)."""
         self._need_pool()
-        q = query.to(self.device)
-        q = (q if q.dtype in (torch.float32, torch.float16, torch.bfloat16) else q.float()).contiguous()
-        B, HQ, D = q.shape
         bt = block_tables.to(self.device, torch.int32).contiguous()
         sl = seq_lens.to(self.device, torch.int32).contiguous()
-        max_blocks = bt.shape[1]
-        max_len = int(max_seq_len) if max_seq_len is not None else max_blocks * self.block_size
-        need = N.lib().tqb_decode_attention_workspace_bytes(B, HQ, self.num_heads, D, max_len)
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
-        res = out if out is not None else torch.empty_like(q)
-        c = self.config
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_decode_attention(
-                N.ptr(q), N.dtype_code(q.dtype), B, HQ, self.num_heads, D, N.ptr(self._kp[layer_id]),
-                N.ptr(self._kn[layer_id]), N.ptr(self._vp[layer_id]), N.ptr(self._vn[layer_id]), 0, N.ptr(sl), max_len,
-                N.ptr(bt), max_blocks, self.block_size, N.ptr(self._key_rotation), N.ptr(self._kb[1]), c.key_bits,
-                N.ptr(self._val_rotation), N.ptr(self._vb[1]), c.value_bits,
-                float(scale if scale is not None else 1.0 / math.sqrt(D)), N.ptr(self._workspace),
-                self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype), N.stream_of(q)))
-        return res
+        max_len = int(max_seq_len) if max_seq_len is not None else bt.shape[1] * self.block_size
+        return self.kv.decode_attention(self._pools[layer_id], query, self.num_heads, sl, max_len, block_tables=bt,
+                                        block_size=self.block_size, scale=scale, out=out)
 
     # ---- upstream-style single-sequence API ------------------------------------------------------
     def append(self, layer_id: int, key: torch.Tensor, value: torch.Tensor) -> None:
         """key / value: (kv_heads, new, head_dim) (or with a leading batch dim, item 0 is used)."""
-        if not self._kp:
-            raise RuntimeError("KV cache not allocated: call allocate(num_gpu_blocks) first")
+        self._need_pool()
         if key.dim() == 4:
             key, value = key[0], value[0]
         T = key.shape[1]
@@ -170,32 +136,31 @@ class TurboQuantPagedKVCache:
         self.append_slots(layer_id, key.transpose(0, 1), value.transpose(0, 1), slots)
         self._seq_len[layer_id] += T
 
-    def _flat(self, pool: torch.Tensor, layer_id: int) -> torch.Tensor:
-        """(kv_heads, seq, ...) view-copy of the first seq tokens in block order."""
-        seq = self._seq_len[layer_id]
-        nb = (seq + self.block_size - 1) // self.block_size
-        x = pool[:nb].transpose(0, 1)                     # (H, nb, bs, ...)
-        return x.reshape(self.num_heads, nb * self.block_size, *pool.shape[3:])[:, :seq].contiguous()
+    def _rows(self, layer_id: int, keys: bool = True, values: bool = True):
+        """Upstream-layout rows of the single sequence, head-major: each (heads * seq, ...)."""
+        seq, H, bs = self._seq_len[layer_id], self.num_heads, self.block_size
+        tok = torch.arange(seq, device=self.device, dtype=torch.int64)
+        # row (h, t) lives at slot ((t // bs) * H + h) * bs + t % bs
+        slots = ((tok // bs)[None, :] * H + torch.arange(H, device=self.device)[:, None]) * bs + (tok % bs)[None, :]
+        flat = slots.reshape(-1).contiguous()
+        # a dense map over explicit slots: inner = 1 and block_size = 1 make slot -> slot
+        rm = N.RowMap(1, 0, 0, 0, None, 1, N.ptr(flat), 1)
+        out = self.kv.export_rows(self._pools[layer_id], H * seq, rm, keys, values)
+        del flat
+        return out
 
-    def _dense(self, layer_id: int, packed, norms, bits, rot, cent) -> torch.Tensor:
-        seq, H, D = self._seq_len[layer_id] if self._kp else 0, self.num_heads, self.head_dim
+    def _dense(self, layer_id: int, which: str) -> torch.Tensor:
+        seq, H, D = (self._seq_len[layer_id] if self._pools else 0), self.num_heads, self.head_dim
         if seq == 0:
             return torch.zeros(H, 0, D, dtype=torch.float32, device=self.device)
-        p = self._flat(packed[layer_id], layer_id).view(H * seq, -1)
-        n = self._flat(norms[layer_id], layer_id).view(-1)
-        out = torch.empty(H * seq, D, dtype=torch.float32, device=self.device)
-        with torch.cuda.device(self.device):
-            N.check(N.lib().tqb_dequantize_mse(N.ptr(p), N.ptr(n), H * seq, D, N.ptr(rot), N.ptr(cent), bits,
-                                               N.ptr(out), N.F32, N.stream_of(p)))
-        return out.view(H, seq, D)
+        kp, kn, vp, vn = self._rows(layer_id, keys=which == "key", values=which == "value")
+        return self.kv.dequantize(kp if which == "key" else vp, kn if which == "key" else vn, which).view(H, seq, D)
 
     def get_keys(self, layer_id: int) -> torch.Tensor:
-        return self._dense(layer_id, self._kp, getattr(self, "_kn", None), self.config.key_bits,
-                           self._key_rotation, self._kb[1])
+        return self._dense(layer_id, "key")
 
     def get_values(self, layer_id: int) -> torch.Tensor:
-        return self._dense(layer_id, getattr(self, "_vp", None), getattr(self, "_vn", None),
-                           self.config.value_bits, self._val_rotation, self._vb[1])
+        return self._dense(layer_id, "value")
 
     def attention_scores(self, layer_id: int, query: torch.Tensor) -> torch.Tensor:
         """(heads, seq_q, head_dim) -> (heads, seq_q, seq_kv) logits scaled by 1/sqrt(head_dim)."""
@@ -205,7 +170,8 @@ class TurboQuantPagedKVCache:
         q = query.to(self.device).float()
         H, sq, D = q.shape
         seq = self._seq_len[layer_id]
-        kp, kn = self._flat(self._kp[layer_id], layer_id), self._flat(self._kn[layer_id], layer_id)
+        kp, kn, _, _ = self._rows(layer_id, values=False)
+        kp, kn = kp.view(H, seq, -1), kn.view(H, seq)
         out = torch.empty(H, sq, seq, dtype=torch.float32, device=self.device)
         for h in range(H):
             out[h] = attention_scores_packed(q[h].unsqueeze(0), kp[h], kn[h], self._kb[1], self._key_rotation,
@@ -218,7 +184,8 @@ class TurboQuantPagedKVCache:
 
         w = attn_weights.to(self.device).float()
         H, sq, seq = w.shape
-        vp, vn = self._flat(self._vp[layer_id], layer_id), self._flat(self._vn[layer_id], layer_id)
+        _, _, vp, vn = self._rows(layer_id, keys=False)
+        vp, vn = vp.view(H, seq, -1), vn.view(H, seq)
         out = torch.empty(H, sq, self.head_dim, dtype=torch.float32, device=self.device)
         for h in range(H):
             out[h] = attention_values_packed(w[h].unsqueeze(0), vp[h], vn[h], self._vb[1], self._val_rotation,
