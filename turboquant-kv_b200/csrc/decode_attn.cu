@@ -3,8 +3,8 @@
 // Replaces "dequantise every cached key and value, then attend" (upstream
 // turboquant_kv/cache.py:216-339) by three launches that never materialise dense K/V:
 //
-//   1. rotate_query_kernel   q_rot = R_k q per head, normalised to |.| <= 1, written directly as
-//                            mma.sync B fragments (fp16) + one fp32 scale per head.
+//   1. rotate_query_kernel   q_rot = R_k q per head, times scale * log2(e), written directly as
+//                            mma.sync B fragments (fp16).
 //   2. decode_partial_kernel persistent warps stream 16-token tiles of packed K / V codes and norms
 //                            through a per-warp ring of shared-memory stages filled by TMA bulk copies
 //                            (cp.async.bulk + mbarrier).  Per tile: scores = K-codes x q on tensor
@@ -64,7 +64,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -92,15 +92,16 @@ struct DecodeParams {
     int64_t max_seq;                 // token pitch of a unit (contiguous cache), multiple of 16
     int batch, q_heads, kv_heads, group, max_blocks, block_size;
     int chunk, nchunks;              // tokens per (unit, chunk) work item
+    int sets;                        // partials per work item (consumer warps of the streaming kernel)
     const float* cent_k; const float* cent_v;
     // workspace views
-    int* status; const uint32_t* qfrag; const float* qscale;
+    int* status; const uint32_t* qfrag;
     float* part_m; float* part_l; float* part_acc;
 };
 
 // Workspace layout shared by the size query and the launcher.
 struct DecodeWorkspace {
-    size_t off_status, off_qfrag, off_qscale, off_m, off_l, off_acc, total;
+    size_t off_status, off_qfrag, off_m, off_l, off_acc, total;
     int chunk, nchunks;
 };
 
@@ -111,13 +112,11 @@ struct DecodeWorkspace {
 // One CTA (4 warps) per unit.  Fragment element (ks, lane = 4g+t, half) of head g holds the rotated,
 // normalised query coordinates (16ks + 8half + 2t, +1); heads >= group are zero columns.
 template <typename T>
-__global__ void __launch_bounds__(128) rotate_query_kernel(const T* __restrict__ q, int q_heads, int kv_heads,
+__global__ void __launch_bounds__(256) rotate_query_kernel(const T* __restrict__ q, int q_heads, int kv_heads,
                                                            int group, int dim, const float* __restrict__ R,
-                                                           float scale, uint32_t* __restrict__ qfrag,
-                                                           float* __restrict__ qscale, int* status) {
+                                                           float scale, uint32_t* __restrict__ qfrag, int* status) {
     __shared__ float qin[8][128];
     __shared__ float qr[8][128];
-    __shared__ float qmax[8];
     const int u = blockIdx.x, b = u / kv_heads, h = u - b * kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (u == 0 && threadIdx.x == 0) *status = 0;
@@ -126,41 +125,45 @@ __global__ void __launch_bounds__(128) rotate_query_kernel(const T* __restrict__
         qin[n][k] = to_f32<T>(q[((int64_t)b * q_heads + h * group + n) * dim + k]);
     }
     __syncthreads();
+    // each warp takes 4 rows of R per round so that their loads are in flight together
     const int nq = dim >> 5;
-    for (int j = warp; j < dim; j += 4) {
-        float r[4];
-        for (int i = 0; i < nq; i++) r[i] = R[(int64_t)j * dim + lane + 32 * i];
+    for (int j0 = warp * 4; j0 < dim; j0 += 32) {
+        float r[4][4];
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                r[jj][i] = (i < nq) ? R[(int64_t)(j0 + jj) * dim + lane + 32 * i] : 0.0f;
         for (int n = 0; n < group; n++) {
-            float s = 0.0f;
-            for (int i = 0; i < nq; i++) s = fmaf(r[i], qin[n][lane + 32 * i], s);
-            s = warp_sum(s);
-            if (lane == 0) qr[n][j] = s;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float qv = (i < nq) ? qin[n][lane + 32 * i] : 0.0f;
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) acc[jj] = fmaf(r[jj][i], qv, acc[jj]);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const float sum = warp_sum(acc[jj]);
+                if (lane == 0) qr[n][j0 + jj] = sum;
+            }
         }
     }
     __syncthreads();
-    for (int n = warp; n < 8; n += 4) {
-        float mx = 0.0f;
-        if (n < group)
-            for (int k = lane; k < dim; k += 32) mx = fmaxf(mx, fabsf(qr[n][k]));
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) {
-            qmax[n] = mx;
-            qscale[(int64_t)u * 8 + n] = (n < group) ? mx * scale * LOG2E : 0.0f;
-        }
-    }
-    __syncthreads();
+    // Fragments carry q_rot * scale * log2(e): fp16 keeps 11 significant bits whatever the magnitude and
+    // the products stay far inside its range, so no separate per-head factor is needed.
+    const float fold = scale * LOG2E;
     const int ksteps = dim >> 4;
     for (int idx = threadIdx.x; idx < ksteps * 64; idx += blockDim.x) {
         const int ks = idx >> 6, rem = idx & 63, fl = rem >> 1, half = rem & 1;
         const int g = fl >> 2, t = fl & 3;
         float lo = 0.0f, hi = 0.0f;
-        if (g < group && qmax[g] > 0.0f) {
+        if (g < group) {
             const int dlo = 16 * ks + 8 * half + 2 * t, dhi = dlo + 1;   // k index = dimension
-            const float inv = 1.0f / qmax[g];
-            lo = qr[g][dlo] * inv;
-            hi = qr[g][dhi] * inv;
+            lo = qr[g][dlo] * fold;
+            hi = qr[g][dhi] * fold;
         }
-        qfrag[((int64_t)u * ksteps + ks) * 64 + rem] = pack_half2(lo, hi);
+        qfrag[((int64_t)u * ksteps + ks) * 64 + rem] = pack_half2_sat(lo, hi);
     }
 }
 
@@ -173,17 +176,44 @@ struct DecodeCfg {
     static constexpr int KL = D * KB / 16, VL = D * VB / 16;       // bytes per lane
     static constexpr int KSEC = 32 * KL, VSEC = 32 * VL;
     static constexpr int REC = KSEC + VSEC + 128;                   // one 16-token record
+    // Lookup tables.  An entry is replicated for the 32 lanes (bank = lane: no conflicts).
+    // BYTE tables (8-bit fields): entries 256 bytes apart in a 64 KB table that starts on a 64 KB boundary
+    // of the shared window, so that ONE byte-permute assembles the complete shared address of an entry:
+    // byte 0 = lane offset, byte 1 = the field, bytes 2-3 = table base.  Other tables: 128 bytes apart,
+    // address = base + (field << 7) + lane offset.
+    static constexpr bool KBYTE = (2 * KB == 8);
+    static constexpr bool VQUAD = (VB == 2);                        // 2 dims x 2 tokens per 8-bit field
+    static constexpr bool VBYTE = VQUAD || (2 * VB == 8);
     static constexpr int LUTK_ENTRIES = 1 << (2 * KB);
-    static constexpr int LUTV_ENTRIES = VB == 2 ? 256 : (1 << (2 * VB));
-    static constexpr int LUTV_WORDS = VB == 2 ? 2 : 1;             // 8-byte entries for 2-bit values
-    static constexpr int LUTK_BYTES = LUTK_ENTRIES * 32 * 4;
-    static constexpr int LUTV_BYTES = LUTV_ENTRIES * 32 * 4 * LUTV_WORDS;
+    static constexpr int LUTV_ENTRIES = VQUAD ? 256 : (1 << (2 * VB));
+    static constexpr int LUTV_WORDS = VQUAD ? 2 : 1;               // 8-byte entries for 2-bit values
+    // When both tables are BYTE tables they share ONE 64 KB region: the 256 bytes of entry x hold the key
+    // entry in [0,128) (32 lanes x 4 B) and the value entry in [128,256) (32 lanes x 4 B, or 16 lane slots
+    // x 8 B: a 64-bit shared load is served half a warp at a time, so lanes l and l+16 can share a slot).
+    static constexpr int NALIGNED = (KBYTE || VBYTE) ? 1 : 0;
+    static constexpr int SMALL_K = KBYTE ? 0 : LUTK_ENTRIES * 128;  // tables that need no alignment
+    static constexpr int SMALL_V = VBYTE ? 0 : LUTV_ENTRIES * 128;
     static constexpr int MT = D / 16;                               // m-tiles of O^T / k-steps of the scores
-    static constexpr int WARPS = D == 64 ? 16 : 8;
-    static constexpr int RPS = D == 64 ? 4 : 2;                     // records per pipeline stage
-    static constexpr int NS = D == 64 ? 2 : 4;                      // stages per warp
-    static constexpr int STAGE = RPS * REC;
-    static constexpr size_t SMEM = (size_t)LUTK_BYTES + LUTV_BYTES + (size_t)WARPS * NS * STAGE + WARPS * NS * 8 + 128;
+    static constexpr int WARPS = D == 64 ? 16 : 8;                  // consumer warps
+    static constexpr int GROUPS = 2;                                // consumer warp groups; stage n goes to group n % GROUPS
+    static constexpr int WPG = WARPS / GROUPS;
+    static constexpr int RPW = 4;                                   // records per warp per stage
+    static constexpr int SR = WPG * RPW;                            // records per stage (one bulk copy)
+    static constexpr int STAGE = SR * REC;
+    static constexpr int STAGE_TOKENS = SR * 16;
+    static constexpr int THREADS = (WARPS + 1) * 32;                // consumer warps + one producer warp
+    // Shared-memory plan (dynamic, the whole opt-in maximum):  [ring A | aligned tables | misc | ring B]
+    static constexpr int DYN = 227 * 1024;
+    static constexpr int LENS_MAX = 512;
+    static constexpr int MISC = SMALL_K + SMALL_V + 256 /*centroids*/ + 8 * (8 + 8 + 16) /*barriers, stage headers*/
+                                + LENS_MAX * 4;
+    static constexpr int BASE_MAX = 4096;                           // assumed upper bound of the window offset
+    static constexpr int SLOTS_A = NALIGNED ? (65536 - BASE_MAX) / STAGE : 0;
+    static constexpr int TAIL = NALIGNED ? DYN - 2 * 65536 : DYN - BASE_MAX;
+    static constexpr int SLOTS_B = (TAIL - MISC) / STAGE;
+    static constexpr int NS_FIT = SLOTS_A + SLOTS_B;
+    static constexpr int NS = NS_FIT > 8 ? 8 : NS_FIT;              // stages in the ring
+    static_assert(NS >= 2, "shared memory: the ring needs at least two stages");
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -191,31 +221,47 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Loads from the pipeline stages use explicit shared-space instructions on 32-bit shared addresses (the
+// stage lives wherever the carve-up put it, so the compiler could not prove the address space itself).
+// They are volatile so that they stay behind the mbarrier wait that makes the stage readable.
+__device__ __forceinline__ uint32_t lds32v(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t addr) { return __uint_as_float(lds32v(addr)); }
 
 // A lane's chunk of NB bytes -> 32-bit registers, with the widest loads the chunk's alignment allows.
 template <int NB>
-__device__ __forceinline__ void load_chunk(const uint8_t* p, uint32_t (&w)[NB / 4]) {
+__device__ __forceinline__ void load_chunk(uint32_t addr, uint32_t (&w)[NB / 4]) {
     if (NB % 16 == 0) {
 #pragma unroll
-        for (int i = 0; i < NB / 16; i++) {
-            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
+        for (int i = 0; i < NB / 16; i++)
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
     } else if (NB % 8 == 0) {
 #pragma unroll
-        for (int i = 0; i < NB / 8; i++) {
-            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
-            w[2 * i] = v.x; w[2 * i + 1] = v.y;
-        }
+        for (int i = 0; i < NB / 8; i++)
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i));
     } else {
 #pragma unroll
-        for (int i = 0; i < NB / 4; i++) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+        for (int i = 0; i < NB / 4; i++) w[i] = lds32v(addr + 4 * i);
     }
 }
 
-// Byte offset of a table entry: (field value) << SHIFT, taken straight out of the chunk registers.
-// `bit` and `bits` are compile-time constants after unrolling, so this is one shift and one mask
-// (a funnel shift when the field straddles two registers).
+// (field value) << SHIFT taken straight out of the chunk registers; `bit` and `bits` are compile-time
+// constants after unrolling: one shift and one mask (a funnel shift when the field straddles registers).
 template <int NW, int SHIFT>
 __device__ __forceinline__ uint32_t lut_offset(const uint32_t (&w)[NW], int bit, int bits) {
     const int i = bit >> 5, s = bit & 31;
@@ -225,301 +271,474 @@ __device__ __forceinline__ uint32_t lut_offset(const uint32_t (&w)[NW], int bit,
     return v & (((1u << bits) - 1u) << SHIFT);
 }
 
-// Position of a warp in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to
-// warps; an item is cut into blocks of RPS records.
-template <int RPS>
+// Shared address of the table entry selected by the field at `bit` of chunk registers w.
+//   BYTE table: tab = (table base, 64 KB aligned) | lane offset  -> one byte permute
+//   otherwise:  tab = table base + lane offset                   -> shift, mask, add
+template <bool BYTE, int NW>
+__device__ __forceinline__ uint32_t entry_addr(const uint32_t (&w)[NW], int bit, int bits, uint32_t tab) {
+    if (BYTE) return __byte_perm(w[bit >> 5], tab, 0x7604u | (((bit >> 3) & 3) << 4));
+    return lut_offset<NW, 7>(w, bit, bits) + tab;
+}
+
+// Position of a CTA in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to CTAs;
+// an item is streamed in stages of up to SR records, which the consumer warps share (RPW records each).
+template <int SR, int GROUPS>
 struct StageCursor {
-    int64_t item, total_items, stride;
-    int blk, nblk, ntiles;
-    int unit, b, h, chunk_idx, tok0, tok_end;
+    int item, total_items, stride;     // (the host checks that the item count fits 31 bits)
+    int tiles_left, tile0;              // tiles of the item not yet taken; index of the next one in its unit
+    int unit, b, h, chunk_idx, tok_end;
+    int stage_idx, stages;              // position in the item; an item takes at least GROUPS stages (empty ones
+                                        // if need be) so that every consumer group sees its start and its end
     __device__ __forceinline__ bool valid() const { return item < total_items; }
-    __device__ __forceinline__ int tiles_here() const { return min(RPS, ntiles - blk * RPS); }
-    __device__ __forceinline__ void open(const DecodeParams& p) {
+    __device__ __forceinline__ int tiles_here() const { return min(SR, tiles_left); }
+    // `lens`: the sequence lengths (a shared-memory copy when the batch fits, else the global array)
+    __device__ __forceinline__ void open(const DecodeParams& p, const int32_t* lens) {
         while (item < total_items) {
-            unit = (int)(item / p.nchunks);
-            chunk_idx = (int)(item - (int64_t)unit * p.nchunks);
+            unit = item / p.nchunks;
+            chunk_idx = item - unit * p.nchunks;
             b = unit / p.kv_heads;
             h = unit - b * p.kv_heads;
-            const int S = p.seq_lens[b];
-            tok0 = chunk_idx * p.chunk;
+            const int S = lens[b];
+            const int tok0 = chunk_idx * p.chunk;
             tok_end = min(S, tok0 + p.chunk);
             if (tok0 < tok_end) {
-                ntiles = (tok_end - tok0 + TILE - 1) / TILE;
-                nblk = (ntiles + RPS - 1) / RPS;
-                blk = 0;
+                tiles_left = (tok_end - tok0 + TILE - 1) / TILE;
+                tile0 = tok0 / TILE;
+                stage_idx = 0;
+                stages = max(GROUPS, (tiles_left + SR - 1) / SR);
                 return;
             }
             item += stride;
         }
     }
-    __device__ __forceinline__ void next(const DecodeParams& p) {
-        if (++blk == nblk) { item += stride; open(p); }
+    __device__ __forceinline__ void next(const DecodeParams& p, const int32_t* lens) {
+        const int n = tiles_here();
+        tiles_left -= n; tile0 += n; stage_idx++;
+        if (stage_idx == stages) { item += stride; open(p, lens); }
     }
 };
 
-template <int D, int KB, int VB, bool PAGED>
-__global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::WARPS * 32, 1) decode_partial_kernel(const DecodeParams p) {
+// Per-warp softmax state of the item being processed.
+template <int MT>
+struct WarpState {
+    float m0, m1, l0, l1;      // running maximum (log2 domain; 0 before the first token) and row sums
+    float thr;                 // rescale when a shifted score exceeds this: -inf before the first token, then the slack
+    float O[MT][4];
+    uint32_t qf[MT][2];
+};
+
+// NT (1, 2 or 4) 16-token records at once: scores, online softmax, accumulation.  Both records go through
+// every phase together so that their independent instruction chains interleave.  MASKED handles the
+// partial last tile of an item (tokens >= valid contribute nothing).
+template <int D, int KB, int VB, int NT, bool MASKED>
+__device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t rec0, uint32_t tabK, uint32_t tabV,
+                                               int lane, int g, int valid) {
     using C = DecodeCfg<D, KB, VB>;
-    constexpr int WARPS = C::WARPS, NS = C::NS, RPS = C::RPS;
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t* lutK_b = smem_raw;
-    uint8_t* lutV_b = smem_raw + C::LUTK_BYTES;
-    uint8_t* ring_all = lutV_b + C::LUTV_BYTES;
-    uint64_t* bars_all = reinterpret_cast<uint64_t*>(ring_all + (size_t)WARPS * NS * C::STAGE);
-    float* s_c = reinterpret_cast<float*>(bars_all + WARPS * NS);   // 16 key + 16 value centroids
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    uint8_t* ring = ring_all + (size_t)warp * NS * C::STAGE;
-    const uint32_t bar0 = smem_u32(bars_all + warp * NS);
-
-    if (threadIdx.x < 16) {
-        s_c[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
-        s_c[16 + threadIdx.x] = threadIdx.x < (1 << VB) ? p.cent_v[threadIdx.x] : 0.0f;
-    }
-    if (lane == 0)
-        for (int s = 0; s < NS; s++) mbar_init(bar0 + 8 * s, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
-
-    // ---- lookup tables: entry x replicated for the 32 lanes at word x*32 + lane (no bank conflicts)
+    float sc[NT][4];
+    // ---- scores: 16 tokens x 8 heads per record ----
     {
-        uint32_t* lutK = reinterpret_cast<uint32_t*>(lutK_b);
-        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS) {
-            int clo, chi;
-            tl_key_field_codes((uint32_t)x, KB, clo, chi);
-            lutK[x * 32 + lane] = pack_half2(s_c[clo], s_c[chi]);
+        uint32_t kw[NT][C::KL / 4];
+#pragma unroll
+        for (int i = 0; i < NT; i++) {
+            load_chunk<C::KL>(rec0 + i * C::REC + lane * C::KL, kw[i]);
+            sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
         }
-        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS) {
-            if (VB == 2) {
-                int ag, bg, ag8, bg8;
-                tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
-                reinterpret_cast<uint2*>(lutV_b)[x * 32 + lane] =
-                    make_uint2(pack_half2(s_c[16 + ag], s_c[16 + bg]), pack_half2(s_c[16 + ag8], s_c[16 + bg8]));
-            } else {
-                int ca, cb;
-                tl_val_pair_codes((uint32_t)x, VB, ca, cb);
-                reinterpret_cast<uint32_t*>(lutV_b)[x * 32 + lane] = pack_half2(s_c[16 + ca], s_c[16 + cb]);
-            }
+#pragma unroll
+        for (int ks = 0; ks < C::MT; ks++) {
+            uint32_t a[NT][4];
+#pragma unroll
+            for (int i = 0; i < NT; i++)
+#pragma unroll
+                for (int half = 0; half < 2; half++)
+#pragma unroll
+                    for (int second = 0; second < 2; second++)
+                        a[i][2 * half + second] = lds32(entry_addr<C::KBYTE>(kw[i], tl_key_field_bit(D, KB, ks, half, second), 2 * KB, tabK));
+#pragma unroll
+            for (int i = 0; i < NT; i++) mma_f16(sc[i], a[i], st.qf[ks][0], st.qf[ks][1]);
         }
     }
-    __syncthreads();
-    const uint8_t* lutK_lane = lutK_b + lane * 4;
-    const uint8_t* lutV_lane = lutV_b + lane * 4 * C::LUTV_WORDS;
-
-    StageCursor<RPS> pc, cc;   // producer / consumer cursors over the same stream
-    pc.item = (int64_t)blockIdx.x * WARPS + warp;
-    pc.total_items = (int64_t)p.batch * p.kv_heads * p.nchunks;
-    pc.stride = (int64_t)gridDim.x * WARPS;
-    pc.blk = pc.nblk = pc.ntiles = 0;
-    pc.open(p);
-    cc = pc;
-
-    // lane 0 issues the bulk copies of one stage: a run of records of one unit (contiguous cache) or
-    // record by record through the block table (paged cache)
-    auto issue = [&](const StageCursor<RPS>& cur, int s) {
-        if (lane == 0) {
-            const int nt = cur.tiles_here();
-            const int tile0 = cur.tok0 / TILE + cur.blk * RPS;
-            const uint32_t dst = smem_u32(ring + (size_t)s * C::STAGE);
-            const uint32_t bar = bar0 + 8 * s;
-            // order this warp's earlier generic-proxy reads of the stage before the async-proxy overwrite
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, (uint32_t)(nt * C::REC));
-            if (PAGED) {
-                const int rpb = p.block_size / TILE;   // records per page
-                for (int i = 0; i < nt; i++) {
-                    const int tile = tile0 + i;
-                    const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
-                    const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
-                    bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, bar);
-                }
-            } else {
-                const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + tile0;
-                bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), bar);
-            }
+    // shifted scores s' = score * key_norm - m  (one FFMA each); the running maximum m is lazy: it only
+    // moves when some s' exceeds the slack, so most tiles skip the cross-lane reduction and the rescale
+    float s[NT][4], nvg[NT], nvg8[NT];
+    float tm0 = NEG_INF, tm1 = NEG_INF;
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+        const uint32_t nk = rec0 + i * C::REC + C::KSEC + C::VSEC + 4 * g;   // key norms, then 16 value norms
+        const bool val_g = !MASKED || 16 * i + g < valid, val_g8 = !MASKED || 16 * i + g + 8 < valid;
+        float nkg = ldsf(nk), nkg8 = ldsf(nk + 32);
+        nvg[i] = ldsf(nk + 64);
+        nvg8[i] = ldsf(nk + 96);
+        if (MASKED) {
+            if (!val_g) { nkg = 0.0f; nvg[i] = 0.0f; }
+            if (!val_g8) { nkg8 = 0.0f; nvg8[i] = 0.0f; }
         }
-    };
-
-    uint32_t issued = 0, consumed = 0;
-    while (issued < NS && pc.valid()) { issue(pc, issued % NS); pc.next(p); issued++; }
-
-    float m0 = NEG_INF, m1 = NEG_INF, l0 = 0.0f, l1 = 0.0f, qs0 = 0.0f, qs1 = 0.0f;
-    float O[C::MT][4];
-    uint32_t qf[C::MT][2];
-    bool failed = false;
-
-    while (cc.valid()) {
-        if (cc.blk == 0) {
-            m0 = m1 = NEG_INF; l0 = l1 = 0.0f;
-#pragma unroll
-            for (int mt = 0; mt < C::MT; mt++) { O[mt][0] = O[mt][1] = O[mt][2] = O[mt][3] = 0.0f; }
-            const uint2* qsrc = reinterpret_cast<const uint2*>(p.qfrag) + ((int64_t)cc.unit * C::MT) * 32 + lane;
-#pragma unroll
-            for (int ks = 0; ks < C::MT; ks++) { const uint2 v = qsrc[ks * 32]; qf[ks][0] = v.x; qf[ks][1] = v.y; }
-            qs0 = p.qscale[(int64_t)cc.unit * 8 + 2 * t];
-            qs1 = p.qscale[(int64_t)cc.unit * 8 + 2 * t + 1];
+        s[i][0] = fmaf(sc[i][0], nkg, -st.m0); s[i][1] = fmaf(sc[i][1], nkg, -st.m1);
+        s[i][2] = fmaf(sc[i][2], nkg8, -st.m0); s[i][3] = fmaf(sc[i][3], nkg8, -st.m1);
+        if (MASKED) {
+            if (!val_g) { s[i][0] = NEG_INF; s[i][1] = NEG_INF; }
+            if (!val_g8) { s[i][2] = NEG_INF; s[i][3] = NEG_INF; }
         }
-        const int s = consumed % NS;
-        if (!mbar_wait(bar0 + 8 * s, (consumed / NS) & 1)) failed = true;
-        if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
-        const int nt = cc.tiles_here();
-        const int tok_blk = cc.tok0 + cc.blk * RPS * TILE;
-
-#pragma unroll 1
-        for (int i = 0; i < nt; i++) {
-            const uint8_t* rec = ring + (size_t)s * C::STAGE + i * C::REC;
-            const float* nk = reinterpret_cast<const float*>(rec + C::KSEC + C::VSEC);
-            const float* nv = nk + TILE;
-            const int tokb = tok_blk + i * TILE;
-            const bool val_g = tokb + g < cc.tok_end, val_g8 = tokb + g + 8 < cc.tok_end;
-
-            // ---- scores: 16 tokens x 8 heads ----
-            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            {
-                uint32_t kw[C::KL / 4];
-                load_chunk<C::KL>(rec + lane * C::KL, kw);
+        tm0 = fmaxf(tm0, fmaxf(s[i][0], s[i][2]));
+        tm1 = fmaxf(tm1, fmaxf(s[i][1], s[i][3]));
+    }
+    if (__any_sync(0xffffffffu, fmaxf(tm0, tm1) > st.thr)) {
 #pragma unroll
-                for (int ks = 0; ks < C::MT; ks++) {
-                    uint32_t a[4];
+        for (int o = 4; o < 32; o <<= 1) {
+            tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
+            tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
+        }
+        // move each maximum up by d = max(tm, 0) (never down); everything accumulated so far shrinks by 2^-d
+        // (the very first tile of an item sets the maximum outright: nothing has been accumulated yet)
+        const bool fresh = st.thr == NEG_INF;
+        const float d0 = (tm0 == NEG_INF) ? 0.0f : (fresh ? tm0 : fmaxf(tm0, 0.0f));
+        const float d1 = (tm1 == NEG_INF) ? 0.0f : (fresh ? tm1 : fmaxf(tm1, 0.0f));
+        const float f0 = fresh ? 1.0f : ex2_approx(-d0), f1 = fresh ? 1.0f : ex2_approx(-d1);
+        st.m0 += d0; st.m1 += d1;
+        st.l0 *= f0; st.l1 *= f1;
+#pragma unroll
+        for (int mt = 0; mt < C::MT; mt++) { st.O[mt][0] *= f0; st.O[mt][2] *= f0; st.O[mt][1] *= f1; st.O[mt][3] *= f1; }
+#pragma unroll
+        for (int i = 0; i < NT; i++) { s[i][0] -= d0; s[i][2] -= d0; s[i][1] -= d1; s[i][3] -= d1; }
+        st.thr = RESCALE_SLACK;
+    }
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+        const float p0 = ex2_approx(s[i][0]), p1 = ex2_approx(s[i][1]);
+        const float p2 = ex2_approx(s[i][2]), p3 = ex2_approx(s[i][3]);
+        st.l0 += p0 + p2; st.l1 += p1 + p3;
+        // P^T as B operand: (k = tokens, col = head) through two 8x8 transposes
+        pb[i][0] = movmatrix_trans(pack_half2_sat(p0 * nvg[i], p1 * nvg[i]));
+        pb[i][1] = movmatrix_trans(pack_half2_sat(p2 * nvg8[i], p3 * nvg8[i]));
+    }
+
+    // ---- O^T += V^T P^T : (dims x tokens) x (tokens x heads) ----
+    {
+        uint32_t vw[NT][C::VL / 4];
+#pragma unroll
+        for (int i = 0; i < NT; i++) load_chunk<C::VL>(rec0 + i * C::REC + C::KSEC + lane * C::VL, vw[i]);
+#pragma unroll
+        for (int mt = 0; mt < C::MT; mt++) {
+            uint32_t a[NT][4];
+#pragma unroll
+            for (int i = 0; i < NT; i++) {
+                if (C::VQUAD) {
+                    const uint2 e0 = lds64(entry_addr<true>(vw[i], tl_val_field_bit(VB, mt, 0, 0), 8, tabV));
+                    const uint2 e1 = lds64(entry_addr<true>(vw[i], tl_val_field_bit(VB, mt, 1, 0), 8, tabV));
+                    a[i][0] = e0.x; a[i][1] = e0.y; a[i][2] = e1.x; a[i][3] = e1.y;
+                } else {
 #pragma unroll
                     for (int half = 0; half < 2; half++)
 #pragma unroll
-                        for (int second = 0; second < 2; second++) {
-                            const uint32_t off = lut_offset<C::KL / 4, 7>(kw, tl_key_field_bit(D, KB, ks, half, second), 2 * KB);
-                            a[2 * half + second] = *reinterpret_cast<const uint32_t*>(lutK_lane + off);
-                        }
-                    mma_f16(sc, a, qf[ks][0], qf[ks][1]);
+                        for (int rs = 0; rs < 2; rs++)
+                            a[i][2 * half + rs] = lds32(entry_addr<C::VBYTE>(vw[i], tl_val_field_bit(VB, mt, half, rs), 2 * VB, tabV));
                 }
             }
-            const float nkg = val_g ? nk[g] : 0.0f, nkg8 = val_g8 ? nk[g + 8] : 0.0f;
-            const float s0 = val_g ? sc[0] * (nkg * qs0) : NEG_INF, s1 = val_g ? sc[1] * (nkg * qs1) : NEG_INF;
-            const float s2 = val_g8 ? sc[2] * (nkg8 * qs0) : NEG_INF, s3 = val_g8 ? sc[3] * (nkg8 * qs1) : NEG_INF;
+#pragma unroll
+            for (int i = 0; i < NT; i++) mma_f16(st.O[mt], a[i], pb[i][0], pb[i][1]);
+        }
+    }
+}
 
-            // ---- online softmax, lazy maximum ----
-            float tm0 = fmaxf(s0, s2), tm1 = fmaxf(s1, s3);
-            if (__any_sync(0xffffffffu, (tm0 > m0 + RESCALE_SLACK) || (tm1 > m1 + RESCALE_SLACK))) {
-#pragma unroll
-                for (int o = 4; o < 32; o <<= 1) {
-                    tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
-                    tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
-                }
-                const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
-                const float f0 = (mn0 == NEG_INF) ? 1.0f : ex2_approx(m0 - mn0);
-                const float f1 = (mn1 == NEG_INF) ? 1.0f : ex2_approx(m1 - mn1);
-                l0 *= f0; l1 *= f1;
-#pragma unroll
-                for (int mt = 0; mt < C::MT; mt++) { O[mt][0] *= f0; O[mt][2] *= f0; O[mt][1] *= f1; O[mt][3] *= f1; }
-                m0 = mn0; m1 = mn1;
+template <int D, int KB, int VB, bool PAGED>
+__global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_partial_kernel(const DecodeParams p) {
+    using C = DecodeCfg<D, KB, VB>;
+    constexpr int WARPS = C::WARPS, NS = C::NS, SR = C::SR, RPW = C::RPW, GROUPS = C::GROUPS, WPG = C::WPG;
+    constexpr uint32_t F_FIRST = 1u << 16, F_LAST = 1u << 17, F_END = 1u << 18;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    // ---- carve the shared window (see DecodeCfg): all positions are 32-bit shared addresses ----
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t end = base + C::DYN;
+    uint32_t tabK_base, tabV_base, misc, ringA = base, ringB;
+    int slotsA;
+    if (C::NALIGNED) {
+        const uint32_t al = (base + 65535u) & ~65535u;
+        slotsA = (int)((al - base) / C::STAGE);
+        tabK_base = C::KBYTE ? al : 0;
+        tabV_base = C::VBYTE ? al + (C::KBYTE ? 128u : 0u) : 0;   // second half of every 256-byte entry block
+        misc = al + 65536u;
+    } else {
+        slotsA = 0; tabK_base = tabV_base = 0; misc = base;
+    }
+    if (!C::KBYTE) { tabK_base = misc; misc += C::SMALL_K; }
+    if (!C::VBYTE) { tabV_base = misc; misc += C::SMALL_V; }
+    const uint32_t cent_addr = misc;                 // 32 floats
+    const uint32_t full_addr = misc + 256;           // full[s]: the stage's bytes have landed
+    const uint32_t empty_addr = full_addr + 8 * 8;   // empty[s]: every warp of the stage's group has finished with it
+    const uint32_t meta_addr = empty_addr + 8 * 8;   // one uint4 per stage: {unit, chunk, tiles | flags, valid tokens}
+    const uint32_t lens_addr = meta_addr + 8 * 16;   // sequence lengths of up to LENS_MAX sequences
+    ringB = (lens_addr + C::LENS_MAX * 4 + 127u) & ~127u;
+    const int slotsB = (int)((end - ringB) / C::STAGE);
+    if (slotsA + slotsB < NS) {                      // cannot happen unless the window offset is unusually large
+        if (threadIdx.x == 0) atomicExch(p.status, 2);
+        return;
+    }
+    auto slot_addr = [&](int slot) -> uint32_t {
+        return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
+    };
+    uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
+
+    const bool lens_in_smem = p.batch <= C::LENS_MAX;
+    if (lens_in_smem)
+        for (int i = threadIdx.x; i < p.batch; i += blockDim.x)
+            reinterpret_cast<int32_t*>(smem_gen + lens_addr)[i] = p.seq_lens[i];
+    const int32_t* lens = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + lens_addr) : p.seq_lens;
+    if (threadIdx.x < 16) {
+        float* cf = reinterpret_cast<float*>(smem_gen + cent_addr);
+        cf[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
+        cf[16 + threadIdx.x] = threadIdx.x < (1 << VB) ? p.cent_v[threadIdx.x] : 0.0f;
+    }
+    if (threadIdx.x < NS) {
+        mbar_init(full_addr + threadIdx.x * 8, 1);
+        mbar_init(empty_addr + threadIdx.x * 8, WPG);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    // ---- lookup tables ----
+    {
+        const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
+        constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
+        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS + 1) {
+            int clo, chi;
+            tl_key_field_codes((uint32_t)x, KB, clo, chi);
+            *reinterpret_cast<uint32_t*>(smem_gen + tabK_base + x * KSTR + lane * 4) = pack_half2(cf[clo], cf[chi]);
+        }
+        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS + 1) {
+            if (C::VQUAD) {
+                int ag, bg, ag8, bg8;
+                tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
+                *reinterpret_cast<uint2*>(smem_gen + tabV_base + x * VSTR + (lane & 15) * 8) =
+                    make_uint2(pack_half2(cf[16 + ag], cf[16 + bg]), pack_half2(cf[16 + ag8], cf[16 + bg8]));
+            } else {
+                int ca, cb;
+                tl_val_pair_codes((uint32_t)x, VB, ca, cb);
+                *reinterpret_cast<uint32_t*>(smem_gen + tabV_base + x * VSTR + lane * 4) = pack_half2(cf[16 + ca], cf[16 + cb]);
             }
-            const float mu0 = (m0 == NEG_INF) ? 0.0f : m0, mu1 = (m1 == NEG_INF) ? 0.0f : m1;
-            const float p0 = ex2_approx(s0 - mu0), p1 = ex2_approx(s1 - mu1);
-            const float p2 = ex2_approx(s2 - mu0), p3 = ex2_approx(s3 - mu1);
-            l0 += p0 + p2; l1 += p1 + p3;
-            const float nvg = val_g ? nv[g] : 0.0f, nvg8 = val_g8 ? nv[g + 8] : 0.0f;
-            // P^T as B operand: (k = tokens, col = head) through two 8x8 transposes
-            const uint32_t pb0 = movmatrix_trans(pack_half2_sat(p0 * nvg, p1 * nvg));
-            const uint32_t pb1 = movmatrix_trans(pack_half2_sat(p2 * nvg8, p3 * nvg8));
+        }
+    }
+    __syncthreads();
+    const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
+    const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
 
-            // ---- O^T += V^T P^T : (dims x tokens) x (tokens x heads) ----
-            {
-                uint32_t vw[C::VL / 4];
-                load_chunk<C::VL>(rec + C::KSEC + lane * C::VL, vw);
-#pragma unroll
-                for (int mt = 0; mt < C::MT; mt++) {
-                    uint32_t a[4];
-                    if (VB == 2) {
-                        const uint2 e0 = *reinterpret_cast<const uint2*>(
-                            lutV_lane + lut_offset<C::VL / 4, 8>(vw, tl_val_field_bit(VB, mt, 0, 0), 8));
-                        const uint2 e1 = *reinterpret_cast<const uint2*>(
-                            lutV_lane + lut_offset<C::VL / 4, 8>(vw, tl_val_field_bit(VB, mt, 1, 0), 8));
-                        a[0] = e0.x; a[1] = e0.y; a[2] = e1.x; a[3] = e1.y;
-                    } else {
-#pragma unroll
-                        for (int half = 0; half < 2; half++)
-#pragma unroll
-                            for (int rs = 0; rs < 2; rs++)
-                                a[2 * half + rs] = *reinterpret_cast<const uint32_t*>(
-                                    lutV_lane + lut_offset<C::VL / 4, 7>(vw, tl_val_field_bit(VB, mt, half, rs), 2 * VB));
+    // ---- producer: one lane streams the CTA's items, one bulk copy per stage of a contiguous cache ----
+    if (warp == WARPS) {
+        if (lane == 0) {
+            StageCursor<SR, GROUPS> cur;
+            cur.item = blockIdx.x;
+            cur.total_items = p.batch * p.kv_heads * p.nchunks;
+            cur.stride = gridDim.x;
+            cur.tiles_left = 0;
+            cur.open(p, lens);
+            bool ok = true;
+            int end_marks = 0;
+            uint32_t n = 0;
+            for (;; n++) {
+                const int s = n % NS;
+                if (n >= NS) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
+                if (!ok) break;
+                uint4* meta = reinterpret_cast<uint4*>(smem_gen + meta_addr + s * 16);
+                if (!cur.valid()) {                     // end of stream: one marker stage per consumer group
+                    *meta = make_uint4(0, 0, F_END, 0);
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_addr + 8 * s) : "memory");
+                    if (++end_marks == GROUPS) break;
+                    continue;
+                }
+                const int nt = cur.tiles_here();
+                const int left = cur.tok_end - cur.tile0 * TILE;
+                *meta = make_uint4((uint32_t)cur.unit, (uint32_t)cur.chunk_idx,
+                                   (uint32_t)nt | (cur.stage_idx < GROUPS ? F_FIRST : 0u) |
+                                       (cur.stage_idx >= cur.stages - GROUPS ? F_LAST : 0u),
+                                   (uint32_t)left);
+                if (nt == 0) {                          // padding stage of a short item: flags only
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_addr + 8 * s) : "memory");
+                    cur.next(p, lens);
+                    continue;
+                }
+                const uint32_t dst = slot_addr(s);
+                // (the consumers' reads of this slot are ordered before this write by the empty barrier)
+                mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
+                if (PAGED) {
+                    const int rpb = p.block_size / TILE;   // records per page
+                    for (int i = 0; i < nt; i++) {
+                        const int tile = cur.tile0 + i;
+                        const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
+                        const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
+                        bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, full_addr + 8 * s);
                     }
-                    mma_f16(O[mt], a, pb0, pb1);
+                } else {
+                    const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + cur.tile0;
+                    bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), full_addr + 8 * s);
+                }
+                cur.next(p, lens);
+            }
+            if (!ok) {
+                // The consumers stopped releasing stages.  Record it and give the copies still in flight a
+                // bounded chance to land before this CTA's shared memory is released.
+                atomicExch(p.status, 1);
+                for (uint32_t i = (n > (uint32_t)NS ? n - NS : 0); i < n; i++)
+                    (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);   // (padding stages complete at once)
+            }
+        }
+        return;
+    }
+
+    // ---- consumers: group (warp / WPG) takes every GROUPS-th stage; its warp i takes records RPW*i .. RPW*i+RPW-1 ----
+    WarpState<C::MT> st;
+    int unit = 0, chunk_idx = 0;
+    st.m0 = st.m1 = st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
+    const int r0 = RPW * (warp % WPG);
+    for (uint32_t n = warp / WPG;; n += GROUPS) {
+        const int s = n % NS;
+        const bool ok = mbar_wait(full_addr + 8 * s, (n / NS) & 1);
+        if (!__all_sync(0xffffffffu, ok)) {           // a copy never arrived: flag it and stop
+            if (lane == 0) atomicExch(p.status, 1);
+            break;
+        }
+        uint4 meta;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(meta.x), "=r"(meta.y), "=r"(meta.z), "=r"(meta.w) : "r"(meta_addr + s * 16));
+        if (meta.z & F_END) break;                    // end of the stream
+        const int nt = meta.z & 0xffff;
+        if (meta.z & F_FIRST) {                       // this group's first stage of an item
+            unit = (int)meta.x; chunk_idx = (int)meta.y;
+            st.m0 = st.m1 = 0.0f; st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
+#pragma unroll
+            for (int mt = 0; mt < C::MT; mt++) { st.O[mt][0] = st.O[mt][1] = st.O[mt][2] = st.O[mt][3] = 0.0f; }
+            const uint2* qsrc = reinterpret_cast<const uint2*>(p.qfrag) + ((int64_t)unit * C::MT) * 32 + lane;
+#pragma unroll
+            for (int ks = 0; ks < C::MT; ks++) { const uint2 v = qsrc[ks * 32]; st.qf[ks][0] = v.x; st.qf[ks][1] = v.y; }
+        }
+        if (r0 < nt) {
+            const uint32_t rec = slot_addr(s) + r0 * C::REC;
+            const int lv = (int)meta.w - r0 * TILE;   // valid tokens from this warp's first record on
+            const int mine = min(RPW, nt - r0);
+            if (mine == 4 && lv >= 4 * TILE) {
+                process_tiles<D, KB, VB, 4, false>(st, rec, tabK, tabV, lane, g, 4 * TILE);
+            } else {
+                for (int i0 = 0; i0 < mine; i0 += 2) {
+                    const uint32_t r = rec + i0 * C::REC;
+                    const int v = lv - i0 * TILE;
+                    if (mine - i0 >= 2) {
+                        if (v >= 2 * TILE) process_tiles<D, KB, VB, 2, false>(st, r, tabK, tabV, lane, g, 2 * TILE);
+                        else process_tiles<D, KB, VB, 2, true>(st, r, tabK, tabV, lane, g, v);
+                    } else {
+                        process_tiles<D, KB, VB, 1, true>(st, r, tabK, tabV, lane, g, v);
+                    }
                 }
             }
         }
-
-        // ---- stage is free: refill it with the stage NS ahead ----
         __syncwarp();
-        if (pc.valid()) { issue(pc, s); pc.next(p); issued++; }
-        consumed++;
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
 
-        // ---- end of item: write the partial (rotated space, unnormalised) ----
-        if (cc.blk + 1 == cc.nblk) {
+        if (meta.z & F_LAST) {                        // this group's last stage of the item: the warp's partial
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
-                l0 += __shfl_xor_sync(0xffffffffu, l0, o);
-                l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+                st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, o);
+                st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, o);
             }
-            const int64_t pbase = ((int64_t)cc.unit * p.nchunks + cc.chunk_idx) * p.group;
+            const bool none = st.thr == NEG_INF;      // this warp saw no token of the item
+            const int64_t pbase = (((int64_t)unit * p.nchunks + chunk_idx) * WARPS + warp) * p.group;
             const int h0 = 2 * t, h1 = 2 * t + 1;
             if (g == 0) {
-                if (h0 < p.group) { p.part_m[pbase + h0] = m0; p.part_l[pbase + h0] = l0; }
-                if (h1 < p.group) { p.part_m[pbase + h1] = m1; p.part_l[pbase + h1] = l1; }
+                if (h0 < p.group) { p.part_m[pbase + h0] = none ? NEG_INF : st.m0; p.part_l[pbase + h0] = st.l0; }
+                if (h1 < p.group) { p.part_m[pbase + h1] = none ? NEG_INF : st.m1; p.part_l[pbase + h1] = st.l1; }
             }
 #pragma unroll
             for (int mt = 0; mt < C::MT; mt++) {
                 const int dg = 16 * mt + g, dg8 = dg + 8;
                 if (h0 < p.group) {
-                    p.part_acc[(pbase + h0) * D + dg] = O[mt][0];
-                    p.part_acc[(pbase + h0) * D + dg8] = O[mt][2];
+                    p.part_acc[(pbase + h0) * D + dg] = st.O[mt][0];
+                    p.part_acc[(pbase + h0) * D + dg8] = st.O[mt][2];
                 }
                 if (h1 < p.group) {
-                    p.part_acc[(pbase + h1) * D + dg] = O[mt][1];
-                    p.part_acc[(pbase + h1) * D + dg8] = O[mt][3];
+                    p.part_acc[(pbase + h1) * D + dg] = st.O[mt][1];
+                    p.part_acc[(pbase + h1) * D + dg8] = st.O[mt][3];
                 }
             }
         }
-        cc.next(p);
-    }
-
-    if (failed) {
-        // A copy never arrived.  Record it; give the copies still in flight a bounded chance to land
-        // before this CTA's shared memory is released.
-        if (lane == 0) atomicExch(p.status, 1);
-        for (uint32_t i = consumed; i < issued; i++) (void)mbar_wait(bar0 + 8 * (i % NS), (i / NS) & 1);
     }
 }
 
 // =================================================================================================
 // 3. merge of the chunks + inverse value rotation
 // =================================================================================================
-// One CTA of D threads per (unit, query head of the group).
+// One CTA per (unit, query head of the group).  Threads are (chunk group cg) x (dimension j).  Every
+// global load that does not depend on another one is issued up front (chunk maxima and sums, the first
+// eight accumulator rows of the thread, its rows of R_v), so the kernel costs about one memory round
+// trip; the chunk weights 2^(m_c - M) are then recomputed by every thread from shared memory.
+constexpr int MERGE_THREADS = 512;
+constexpr int MERGE_MAX_CHUNKS = 1024;
+constexpr int MERGE_BATCH = 8;
+
 template <typename OutT>
-__global__ void decode_merge_kernel(const DecodeParams p, int dim, const float* __restrict__ Rv,
-                                    OutT* __restrict__ out) {
+__global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const DecodeParams p, int dim,
+                                                                     const float* __restrict__ Rv,
+                                                                     OutT* __restrict__ out) {
+    __shared__ float sm_m[MERGE_MAX_CHUNKS];
+    __shared__ float sm_l[MERGE_MAX_CHUNKS];
+    __shared__ float red[MERGE_THREADS];
     __shared__ float y[128];
-    __shared__ float red[2];
     const int u = blockIdx.x / p.group, n = blockIdx.x - u * p.group;
     const int b = u / p.kv_heads, h = u - b * p.kv_heads;
     const int S = p.seq_lens[b];
-    const int nch = (S + p.chunk - 1) / p.chunk;
-    const int j = threadIdx.x;
-    const int64_t pbase = (int64_t)u * p.nchunks * p.group + n;
-    float M = NEG_INF;
-    for (int c = 0; c < nch; c++) M = fmaxf(M, p.part_m[pbase + (int64_t)c * p.group]);
-    float acc = 0.0f, L = 0.0f;
-    for (int c = 0; c < nch; c++) {
-        const int64_t pi = pbase + (int64_t)c * p.group;
-        const float mc = p.part_m[pi];
-        const float w = (mc == NEG_INF) ? 0.0f : exp2f(mc - M);
-        L = fmaf(w, p.part_l[pi], L);
-        acc = fmaf(w, p.part_acc[pi * dim + j], acc);
+    // every chunk contributes one partial per consumer warp of the streaming kernel
+    const int nch = min(((S + p.chunk - 1) / p.chunk) * p.sets, MERGE_MAX_CHUNKS);
+    const int tid = threadIdx.x, groups = MERGE_THREADS / dim, cg = tid / dim, j = tid - cg * dim;
+    const int64_t pbase = (int64_t)u * p.nchunks * p.sets * p.group + n;
+    const int rows = dim / groups;                       // rows of R_v per thread (8 or 32)
+
+    for (int c = tid; c < nch; c += MERGE_THREADS) {
+        sm_m[c] = p.part_m[pbase + (int64_t)c * p.group];
+        sm_l[c] = p.part_l[pbase + (int64_t)c * p.group];
     }
-    y[j] = (L > 0.0f) ? acc / L : 0.0f;
-    (void)red;
+    float raw[MERGE_BATCH];
+#pragma unroll
+    for (int k = 0; k < MERGE_BATCH; k++) {
+        const int c = cg + k * groups;
+        raw[k] = c < nch ? p.part_acc[(pbase + (int64_t)c * p.group) * dim + j] : 0.0f;
+    }
+    float rv[8];                                         // first 8 of this thread's R_v rows
+#pragma unroll
+    for (int k = 0; k < 8; k++) rv[k] = Rv[(int64_t)(cg + k * groups) * dim + j];
     __syncthreads();
+
+    float M = NEG_INF;
+    for (int c = 0; c < nch; c++) M = fmaxf(M, sm_m[c]);
+    float L = 0.0f;
+    for (int c = 0; c < nch; c++) L = fmaf(exp2f(sm_m[c] - M), sm_l[c], L);
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MERGE_BATCH; k++) {
+        const int c = cg + k * groups;
+        if (c < nch) acc = fmaf(exp2f(sm_m[c] - M), raw[k], acc);
+    }
+    for (int c = cg + MERGE_BATCH * groups; c < nch; c += groups)     // very long contexts only
+        acc = fmaf(exp2f(sm_m[c] - M), p.part_acc[(pbase + (int64_t)c * p.group) * dim + j], acc);
+    red[tid] = acc;
+    __syncthreads();
+    if (tid < dim) {
+        float a = 0.0f;
+        for (int gg = 0; gg < groups; gg++) a += red[gg * dim + tid];
+        y[tid] = (nch > 0 && L > 0.0f) ? a / L : 0.0f;
+    }
+    __syncthreads();
+    // out_k = sum_j y_j Rv[j][k]: this thread takes rows cg, cg + groups, ...
     float o = 0.0f;
-    for (int jj = 0; jj < dim; jj++) o = fmaf(y[jj], Rv[(int64_t)jj * dim + j], o);
-    out[((int64_t)b * p.q_heads + h * p.group + n) * dim + j] = from_f32<OutT>(o);
+#pragma unroll
+    for (int k = 0; k < 8; k++) o = fmaf(y[cg + k * groups], rv[k], o);
+    for (int k = 8; k < rows; k++) o = fmaf(y[cg + k * groups], Rv[(int64_t)(cg + k * groups) * dim + j], o);
+    __syncthreads();
+    red[tid] = o;
+    __syncthreads();
+    if (tid < dim) {
+        float a = 0.0f;
+        for (int gg = 0; gg < groups; gg++) a += red[gg * dim + tid];
+        out[((int64_t)b * p.q_heads + h * p.group + n) * dim + tid] = from_f32<OutT>(a);
+    }
 }
 
 // ---- host side -------------------------------------------------------------------------------------
@@ -528,15 +747,20 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 
 // Tokens per work item: small enough that every warp of the grid gets several items, large enough
 // that the per-item partial (group x (D+2) floats) stays a few percent of the streamed bytes.
-static int choose_chunk(int64_t units, int64_t max_len, int64_t total_warps) {
-    int best = 64;
+// Tokens per (unit, chunk) work item of the streaming kernel.  Work items are dealt round-robin to the
+// CTAs (one per SM); every item yields one partial per consumer warp, so the chunk count per unit is
+// bounded by what the merge kernel keeps in shared memory.
+static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets) {
+    int best = 0;
     double best_cost = 1e300;
-    for (int L = 64; L <= 4096; L *= 2) {
+    for (int64_t L = stage_tokens; L <= (int64_t)1 << 24; L *= 2) {
         const int64_t nch = (max_len + L - 1) / L;
-        const int64_t rounds = (units * nch + total_warps - 1) / total_warps;
-        const double cost = (double)rounds * ((double)std::min<int64_t>(L, max_len) + 24.0);
-        if (cost <= best_cost) { best_cost = cost; best = L; }
-        if (L >= max_len) break;
+        if (nch * sets <= 1024) {
+            const int64_t rounds = (units * nch + ctas - 1) / ctas;
+            const double cost = (double)rounds * ((double)std::min<int64_t>(L, max_len) + stage_tokens);
+            if (cost <= best_cost) { best_cost = cost; best = (int)L; }
+        }
+        if (L >= max_len && best) break;
     }
     return best;
 }
@@ -545,13 +769,13 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     DecodeWorkspace w{};
     const int64_t units = (int64_t)batch * kv_heads;
     const int group = q_heads / kv_heads;
-    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), (int64_t)sm_count() * (dim == 64 ? 16 : 8));
+    const int sets = dim == 64 ? 16 : 8;
+    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), sm_count(), sets * 32, sets);
     w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
     size_t off = 0;
     w.off_status = off; off = align_up(off + 256, 256);
     w.off_qfrag = off;  off = align_up(off + (size_t)units * dim * 16, 256);   // (dim/16) x 64 words
-    w.off_qscale = off; off = align_up(off + (size_t)units * 8 * 4, 256);
-    const size_t parts = (size_t)units * w.nchunks * group;
+    const size_t parts = (size_t)units * w.nchunks * sets * group;
     w.off_m = off;   off = align_up(off + parts * 4, 256);
     w.off_l = off;   off = align_up(off + parts * 4, 256);
     w.off_acc = off; off = align_up(off + parts * dim * 4, 256);
@@ -563,10 +787,12 @@ template <int D, int KB, int VB, bool PAGED>
 static int launch_partial(const DecodeParams& p, cudaStream_t st) {
     using C = DecodeCfg<D, KB, VB>;
     auto kern = decode_partial_kernel<D, KB, VB, PAGED>;
-    TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
     const int64_t items = (int64_t)p.batch * p.kv_heads * p.nchunks;
-    const int grid = (int)std::min<int64_t>(sm_count(), ceil_div(items, C::WARPS));
-    kern<<<grid, C::WARPS * 32, C::SMEM, st>>>(p);
+    if (items + sm_count() >= 0x7fffffff)
+        return fail(TQB_ERR_UNSUPPORTED, "decode_attention: too many (sequence, head, chunk) work items");
+    const int grid = (int)std::min<int64_t>(sm_count(), items);
+    kern<<<grid, C::THREADS, C::DYN, st>>>(p);
     return check_launch("decode_partial");
 }
 
@@ -623,15 +849,14 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
 
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     DecodeParams p{};
-    p.store = store;
+    p.store = store; p.sets = dim == 64 ? 16 : 8;
     p.seq_lens = seq_lens; p.block_tables = block_tables; p.max_seq = max_seq;
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = group;
     p.max_blocks = max_blocks; p.block_size = block_size; p.chunk = w.chunk; p.nchunks = w.nchunks;
     p.cent_k = cent_k; p.cent_v = cent_v;
     p.status = reinterpret_cast<int*>(ws + w.off_status);
     uint32_t* qfrag = reinterpret_cast<uint32_t*>(ws + w.off_qfrag);
-    float* qscale = reinterpret_cast<float*>(ws + w.off_qscale);
-    p.qfrag = qfrag; p.qscale = qscale;
+    p.qfrag = qfrag;
     p.part_m = reinterpret_cast<float*>(ws + w.off_m);
     p.part_l = reinterpret_cast<float*>(ws + w.off_l);
     p.part_acc = reinterpret_cast<float*>(ws + w.off_acc);
@@ -639,9 +864,9 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
     const int units = batch * kv_heads;
 
     switch (q_dtype) {
-        case TQB_F32: rotate_query_kernel<float><<<units, 128, 0, st>>>((const float*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, qscale, p.status); break;
-        case TQB_F16: rotate_query_kernel<__half><<<units, 128, 0, st>>>((const __half*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, qscale, p.status); break;
-        case TQB_BF16: rotate_query_kernel<__nv_bfloat16><<<units, 128, 0, st>>>((const __nv_bfloat16*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, qscale, p.status); break;
+        case TQB_F32: rotate_query_kernel<float><<<units, 256, 0, st>>>((const float*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
+        case TQB_F16: rotate_query_kernel<__half><<<units, 256, 0, st>>>((const __half*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
+        case TQB_BF16: rotate_query_kernel<__nv_bfloat16><<<units, 256, 0, st>>>((const __nv_bfloat16*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
         default: return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
     }
     if (int e = check_launch("rotate_query")) return e;
@@ -654,9 +879,9 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
     }
 
     switch (out_dtype) {
-        case TQB_F32: decode_merge_kernel<float><<<units * group, dim, 0, st>>>(p, dim, rot_v, (float*)out); break;
-        case TQB_F16: decode_merge_kernel<__half><<<units * group, dim, 0, st>>>(p, dim, rot_v, (__half*)out); break;
-        case TQB_BF16: decode_merge_kernel<__nv_bfloat16><<<units * group, dim, 0, st>>>(p, dim, rot_v, (__nv_bfloat16*)out); break;
+        case TQB_F32: decode_merge_kernel<float><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (float*)out); break;
+        case TQB_F16: decode_merge_kernel<__half><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (__half*)out); break;
+        case TQB_BF16: decode_merge_kernel<__nv_bfloat16><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (__nv_bfloat16*)out); break;
         default: return fail(TQB_ERR_INVALID, "decode_attention: unknown output dtype %d", out_dtype);
     }
     return check_launch("decode_merge");

@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(DequantArgs a, int dim)
 template <int NQ, typename OutT, bool PROD>
 static int launch_dequantize(const DequantArgs& a, int dim, cudaStream_t st) {
     constexpr int DP = NQ * 32;
-    const int warps = a.n <= 256 ? 2 : (a.n <= 4096 ? 4 : 8);
+    const int warps = 8;
     const int kc_max = dim < KC ? dim : KC;
     const int nchunks = (dim + KC - 1) / KC;
     const int mats = (PROD && nchunks == 1) ? 2 : 1;

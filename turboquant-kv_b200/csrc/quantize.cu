@@ -258,7 +258,7 @@ template <int NQ, typename T, bool PROD>
 static int launch_quantize(const QuantArgs& a0, const QuantArgs& a1, int ntensors, int dim, cudaStream_t st) {
     constexpr int DP = NQ * 32;
     const int64_t n = a0.n;
-    const int warps = n <= 256 ? 2 : (n <= 4096 ? 4 : 8);
+    const int warps = 8;
     const int kc_max = dim < KC ? dim : KC;
     const int nchunks = (dim + KC - 1) / KC;
     const int mats = (PROD && nchunks == 1) ? 2 : 1;

@@ -10,13 +10,27 @@ namespace tqb {
 constexpr int RW = 8;           // rows per warp
 constexpr int KC = 128;         // k-chunk of the transposed matrix kept in shared memory
 // T[kk][j] = M[j][c0 + kk] for kk < kc, j < DP (zero beyond dim).  Row pitch DP + 1 keeps both the
-// transposing stores and the row reads free of bank conflicts.
+// transposing stores and the row reads free of bank conflicts.  Eight loads are issued before the
+// first store so that their latencies overlap (this runs once per CTA and, for the few rows of a
+// decode-step append, is most of the kernel).
 template <int DP>
 __device__ __forceinline__ void load_transposed_chunk(float* T, const float* __restrict__ M, int dim,
                                                       int c0, int kc) {
-    for (int idx = threadIdx.x; idx < DP * kc; idx += blockDim.x) {
-        const int j = idx / kc, kk = idx - j * kc;
-        T[kk * (DP + 1) + j] = (j < dim) ? M[(int64_t)j * dim + c0 + kk] : 0.0f;
+    const int total = DP * kc;
+    const int step = blockDim.x;
+    for (int base = threadIdx.x; base < total; base += step * 8) {
+        float v[8];
+        int dst[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = base + u * step;
+            const int j = idx / kc, kk = idx - j * kc;
+            dst[u] = idx < total ? kk * (DP + 1) + j : -1;
+            v[u] = (idx < total && j < dim) ? M[(int64_t)j * dim + c0 + kk] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (dst[u] >= 0) T[dst[u]] = v[u];
     }
 }
 
@@ -44,9 +58,21 @@ __device__ __forceinline__ void accumulate_chunk(float (&acc)[RW][NQ], const flo
 template <int DP>
 __device__ __forceinline__ void load_direct_chunk(float* T, const float* __restrict__ M, int dim,
                                                   int c0, int kc) {
-    for (int idx = threadIdx.x; idx < DP * kc; idx += blockDim.x) {
-        const int kk = idx / DP, j = idx - kk * DP;
-        T[kk * (DP + 1) + j] = (j < dim) ? M[(int64_t)(c0 + kk) * dim + j] : 0.0f;
+    const int total = DP * kc;
+    const int step = blockDim.x;
+    for (int base = threadIdx.x; base < total; base += step * 8) {
+        float v[8];
+        int dst[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = base + u * step;
+            const int kk = idx / DP, j = idx - kk * DP;
+            dst[u] = idx < total ? kk * (DP + 1) + j : -1;
+            v[u] = (idx < total && j < dim) ? M[(int64_t)(c0 + kk) * dim + j] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (dst[u] >= 0) T[dst[u]] = v[u];
     }
 }
 
