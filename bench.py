@@ -9,20 +9,21 @@ Workload (synthetic stand-in with the shapes of a Llama-3.2-1B decode step): 16 
 8 KV heads, head_dim 64, keys 4 bits / values 2 bits, batch 32, context 16,384 tokens already in the
 cache, one new token per sequence per step.  K entries ~ N(0,1) with 4 outlier channels per
 (layer, KV head) scaled x20, V entries ~ N(0,1), bf16.  One step = for every layer: quantise and append
-the new K/V token, then attend over the whole packed cache (grouped-query heads).
+the new K/V token, then attend over the whole packed cache (grouped-query heads) -- the fused
+decode_step call: three launches per layer.
 
 N > 1: KV heads are sharded over the ranks (8/N per rank, with their 4 query heads each); there is no
 collective on the path, total work is fixed ("strong" scaling), value = batch / max-over-ranks step time.
 
 One JSON line is printed by rank 0:
   value     tokens/s with everything resident in HBM: the step is captured once in a CUDA graph
-            (launch-bound otherwise: 48 small launches per step) and K replays are timed with CUDA events
+            (launch-bound otherwise: 48 launches per step) and K replays are timed with CUDA events
   e2e       the same step fed from pinned host buffers: H2D of q/k/v of all layers, the step, D2H of the
             attention output, every step
   roofline  HBM roofline of the dominant kernel (decode_partial_kernel); bytes per launch are the packed
             K/V rows and norms of one layer; its duration is measured with CUDA events in an extra pass
-            of the same steps launched eagerly (events cannot be read inside a captured graph); the
-            event pair brackets the three launches of one decode_attention call
+            of the same steps launched eagerly, launch by launch (events cannot be read inside a captured
+            graph), with one event pair around the streaming kernel alone
   cpu_baseline  the CPU checker (oracle/, an OpenMP port of the upstream dequantise-then-attend path)
             timed on this machine's cores on a sample of the same workload
   extra     secondary figures: shorter contexts, and the 4-bit index scan (QPS and HBM GB/s)
@@ -250,15 +251,32 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     out = torch.empty(LAYERS, BATCH, qh, HEAD_DIM, device=device, dtype=torch.bfloat16)
 
     def step_eager(events=None):
+        """One decode step: per layer, append the new token and attend (the fused three-launch call).
+        With `events`, every call is split into its launches so that the streaming kernel alone sits
+        between an event pair (a whole-call pair is recorded as well)."""
         for layer in range(LAYERS):
-            cache.append(layer, k_in[layer], v_in[layer])
-            if events is not None:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-            cache.decode_attention(layer, q_in[layer], out=out[layer])
-            if events is not None:
-                b.record()
-                events.append((a, b))
+            if events is None:
+                cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
+                continue
+            if layer == 0:
+                torch.cuda._sleep(20_000_000)      # ~10 ms: the launches below queue up behind it, so no
+                                                   # event pair contains a wait for the host
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            lib = _native.lib()
+            ev[0].record()
+            lib.tqb_debug_decode_phases(1)
+            cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
+            cache.seq_lens[layer] -= 1             # the length advances in the merge launch
+            ev[1].record()
+            lib.tqb_debug_decode_phases(2)
+            cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
+            cache.seq_lens[layer] -= 1
+            ev[2].record()
+            lib.tqb_debug_decode_phases(4)
+            cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
+            ev[3].record()
+            lib.tqb_debug_decode_phases(7)
+            events.append(ev)
 
     for _ in range(2):            # allocations, attribute settings, first-touch effects
         step_eager()
@@ -328,16 +346,20 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     for _ in range(K):
         step_eager(events)
     barrier()
-    per_call_ms = sum(a.elapsed_time(b) for a, b in events) / len(events)
+    per_call_ms = sum(ev[0].elapsed_time(ev[3]) for ev in events) / len(events)
+    kernel_ms = sum(ev[1].elapsed_time(ev[2]) for ev in events) / len(events)
     assert cache.decode_status() == 0, "a bounded device-side wait expired"
     seq_now = int(cache.seq_lens[0])
     bytes_per_launch = BATCH * kvh * seq_now * BYTES_PER_TOKEN_HEAD
     peaks = measured_peaks()
-    achieved = bytes_per_launch / (per_call_ms * 1e-3) / 1e9
+    achieved = bytes_per_launch / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "decode_partial_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                "traffic": None, "bytes_per_launch": bytes_per_launch, "ms_per_launch": per_call_ms,
-                "note": "duration covers the 3 launches of one decode_attention call (query rotation, partial, merge)"}
+                "traffic": None, "bytes_per_launch": bytes_per_launch, "ms_per_launch": kernel_ms,
+                "ms_per_call_all_launches": per_call_ms,
+                "note": "ms_per_launch: the streaming kernel alone between an event pair; ms_per_call_all_launches: "
+                        "the three launches of one decode_step call (append + query rotation, streaming kernel, "
+                        "merge) launched one by one"}
 
     line = {"metric": METRIC, "value": BATCH / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -412,8 +434,7 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
 
         def step():
             for layer in range(LAYERS):
-                cache.append(layer, kn[layer], kn[layer])
-                cache.decode_attention(layer, q[layer], out=o[layer])
+                cache.decode_step(layer, q[layer], kn[layer], kn[layer], out=o[layer])
 
         step()
         torch.cuda.synchronize()

@@ -186,6 +186,30 @@ int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads,
                          void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                          void* stream);
 
+/* One whole decode step of a layer in three launches: the new token's key and value of every
+ * (sequence, KV head) are quantised and stored at position seq_lens[b] of their unit (what
+ * QuantizedKVCache.append, turboquant_kv/cache.py:116-184, does for one token), the queries are
+ * rotated in the same launch, attention runs over seq_lens[b] + 1 tokens, and seq_lens[b] is advanced
+ * by one at the end (device side, so a captured CUDA graph of the step can be replayed).
+ * query (batch, q_heads, dim), key / value (batch, kv_heads, dim) with kv_stride elements between
+ * (sequence, head) rows, all of `dtype`; contiguous caches only (unit pitch max_seq); max_len (host) >=
+ * every seq_lens[b] + 1.  The stored codes equal those tqb_kv_append stores.  A unit that is already
+ * full (seq_lens[b] == max_seq) stores nothing and sets the status word to 3.
+ * Workspace as for tqb_decode_attention (same size query, with max_len counting the new token). */
+int tqb_decode_step(const void* query, const void* key, const void* value, int dtype, int64_t kv_stride,
+                    int batch, int q_heads, int kv_heads, int dim, uint8_t* store, int64_t max_seq,
+                    int32_t* seq_lens, int64_t max_len, const float* rot_k, const float* bnd_k,
+                    const float* cent_k, int kbits, const float* rot_v, const float* bnd_v,
+                    const float* cent_v, int vbits, float scale, void* workspace, size_t workspace_bytes,
+                    void* out, int out_dtype, void* stream);
+
+/* Measurement aid (no upstream counterpart): restricts the following tqb_decode_attention /
+ * tqb_decode_step calls of this process to a subset of their three launches (bit 0: preparation,
+ * bit 1: the streaming kernel, bit 2: the merge), so that a benchmark can bracket one kernel with
+ * events.  A call made with a subset reuses the workspace contents of the previous launches.  7 restores
+ * normal operation. */
+void tqb_debug_decode_phases(int mask);
+
 /* ---- packed-code inner-product scan with top-k ------------------------------------------------
  * Replaces turboquant::search_packed (csrc/core/turboquant_core.cpp:407-514) as bound by
  * turboquant_kv._core.Index.search (csrc/core/bindings.cpp:100-135) and

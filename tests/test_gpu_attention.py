@@ -167,6 +167,81 @@ def test_decode_appends_token_by_token(orc):
         attention_close(out[:, :, 0].cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("dim,kb,vb,kv_heads,group,dtype", [
+    (64, 4, 2, 8, 4, torch.bfloat16),
+    (64, 3, 3, 2, 8, torch.float32),
+    (64, 2, 4, 1, 2, torch.float16),
+    (128, 4, 3, 4, 4, torch.bfloat16),
+    (128, 2, 2, 2, 1, torch.float32),
+])
+def test_fused_step_equals_append_then_attend(dim, kb, vb, kv_heads, group, dtype):
+    """decode_step stores the same bytes and returns the same attention as append + decode_attention."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    batch, pre, steps = 3, 29, 6
+    k, v = _fill(batch, kv_heads, pre + steps, dim, seed=11)
+    k, v = k.cuda().to(dtype), v.cuda().to(dtype)
+    cfg = TurboQuantConfig(key_bits=kb, value_bits=vb, seed=42)
+    two = QuantizedKVCache(cfg, 1, 48, kv_heads, dim, device="cuda", batch_size=batch)
+    one = QuantizedKVCache(cfg, 1, 48, kv_heads, dim, device="cuda", batch_size=batch)
+    for c in (two, one):
+        c.append(0, k[:, :, :pre], v[:, :, :pre])
+    gen = torch.Generator().manual_seed(5)
+    for step in range(pre, pre + steps):
+        q = torch.randn(batch, kv_heads * group, dim, generator=gen).cuda().to(dtype)
+        two.append(0, k[:, :, step:step + 1], v[:, :, step:step + 1])
+        ref = two.decode_attention(0, q)
+        out = one.decode_step(0, q, k[:, :, step], v[:, :, step])
+        assert one.decode_status() == 0
+        assert int(one.seq_lens[0]) == step + 1
+        assert torch.equal(one._seq_lens_dev[0], two._seq_lens_dev[0])
+        assert torch.equal(one._store[0], two._store[0]), "fused step stored different record bytes"
+        assert torch.equal(out, ref)
+    with pytest.raises(RuntimeError, match="overflow"):
+        for _ in range(48):
+            one.decode_step(0, q, k[:, :, 0], v[:, :, 0])
+
+
+def test_fused_step_replays_in_a_cuda_graph(orc):
+    """A captured step keeps appending at the device-side position when the graph is replayed."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    batch, kv_heads, group, dim, pre = 2, 2, 4, 64, 20
+    k, v = _fill(batch, kv_heads, pre + 8, dim, seed=13)
+    cache = QuantizedKVCache(TurboQuantConfig(seed=42), 1, 64, kv_heads, dim, device="cuda", batch_size=batch)
+    cache.append(0, k[:, :, :pre].cuda(), v[:, :, :pre].cuda())
+    qs, ks, vs = (torch.zeros(batch, kv_heads * group, dim, device="cuda"),
+                  torch.zeros(batch, kv_heads, dim, device="cuda"), torch.zeros(batch, kv_heads, dim, device="cuda"))
+    out = torch.empty_like(qs)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        cache.decode_step(0, qs, ks, vs, out=out)           # warm-up outside capture (sets kernel attributes)
+    torch.cuda.current_stream().wait_stream(side)
+    cache.seq_lens[0] -= 1
+    cache._seq_lens_dev[0] -= 1
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        cache.decode_step(0, qs, ks, vs, out=out)
+    cache.seq_lens[0] -= 1                                   # capture does not run the kernels
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(4, dim)
+    _, cv = orc.lloyd_max_codebook(2, dim)
+    gen = torch.Generator().manual_seed(17)
+    for step in range(pre, pre + 8):
+        q = torch.randn(batch, kv_heads * group, dim, generator=gen)
+        qs.copy_(q.cuda()); ks.copy_(k[:, :, step].cuda()); vs.copy_(v[:, :, step].cuda())
+        graph.replay()
+        cache.seq_lens[0] += 1
+        torch.cuda.synchronize()
+        assert cache._seq_lens_dev[0].tolist() == [step + 1] * batch
+        kp, kn, vp, vn = exported(cache, 0, step + 1)
+        ref = orc.decode_attention(q.numpy(), kp, kn, vp, vn, np.full(batch, step + 1, np.int32),
+                                   rk, ck, 4, rv, cv, 2)
+        attention_close(out.cpu().numpy(), ref)
+    assert cache.decode_status() == 0
+
+
 def test_paged_decode_with_ragged_lengths(orc):
     """vLLM-style pools, permuted block tables, different length per sequence, K4/V3 at head_dim 128."""
     from turboquant_kv.vllm_plugin import TurboQuantAttentionImpl, TurboQuantKVCacheConfig, TurboQuantPagedKVCache

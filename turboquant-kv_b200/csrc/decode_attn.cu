@@ -3,24 +3,27 @@
 // Replaces "dequantise every cached key and value, then attend" (upstream
 // turboquant_kv/cache.py:216-339) by three launches that never materialise dense K/V:
 //
-//   1. rotate_query_kernel   q_rot = R_k q per head, times scale * log2(e), written directly as
-//                            mma.sync B fragments (fp16).
-//   2. decode_partial_kernel persistent warps stream 16-token tiles of packed K / V codes and norms
-//                            through a per-warp ring of shared-memory stages filled by TMA bulk copies
-//                            (cp.async.bulk + mbarrier).  Per tile: scores = K-codes x q on tensor
-//                            cores (codes -> fp16 centroids through a 256-entry shared-memory table
-//                            indexed by one byte = 2 codes), online softmax in the log2 domain with a
-//                            lazy running maximum, P^T via movmatrix, O^T += V^T-codes x P^T on tensor
-//                            cores, all in ROTATED space.  One (m, l, acc) partial per (unit, chunk).
-//   3. decode_merge_kernel   combines the chunks of a (sequence, query head), divides by l and applies
-//                            the inverse value rotation acc @ R_v (reference.py:362).
+//   1. decode_prepare_kernel q_rot = R_k q per head, times scale * log2(e), written directly as
+//                            mma.sync B fragments (fp16); for a fused step it also quantises and
+//                            stores the new token's key and value.
+//   2. decode_partial_kernel one persistent CTA per SM.  A producer warp streams the 16-token records
+//                            of the CTA's work items into a ring of shared-memory stages, one TMA bulk
+//                            copy (cp.async.bulk + mbarrier) of up to 28 KB per stage; two groups of
+//                            consumer warps take alternate stages, four records per warp.  Per record:
+//                            scores = K-codes x q on tensor cores (codes -> fp16 centroids through a
+//                            256-entry shared-memory table indexed by one byte = 2 codes), online
+//                            softmax in the log2 domain with a lazy running maximum, P^T via movmatrix,
+//                            O^T += V^T-codes x P^T on tensor cores, all in ROTATED space.  One
+//                            (m, l, acc) partial per (unit, chunk, consumer warp).
+//   3. decode_merge_kernel   combines the partials of a (sequence, query head), divides by l and
+//                            applies the inverse value rotation acc @ R_v (reference.py:362).
 //
 // A unit is one (sequence, KV head); its `group` query heads ride along as the N dimension of the
 // MMA (grouped-query attention: decode cost is paid once per KV head).  HBM traffic per token and
 // KV head is the packed K row + packed V row + two float norms; everything else lives in L2/SMEM.
 //
 // Every wait is bounded: a warp that gives up records it in the status word at the start of the
-// workspace, drains nothing further and returns, so a lost copy cannot hang the device.
+// workspace and returns, so a lost copy cannot hang the device.
 #include "common.cuh"
 #include "tiled_layout.cuh"
 
@@ -101,7 +104,7 @@ struct DecodeParams {
 
 // Workspace layout shared by the size query and the launcher.
 struct DecodeWorkspace {
-    size_t off_status, off_qfrag, off_m, off_l, off_acc, total;
+    size_t off_status, off_lens, off_qfrag, off_m, off_l, off_acc, total;
     int chunk, nchunks;
 };
 
@@ -109,49 +112,10 @@ struct DecodeWorkspace {
 // =================================================================================================
 // 1. query rotation -> B fragments
 // =================================================================================================
-// One CTA (4 warps) per unit.  Fragment element (ks, lane = 4g+t, half) of head g holds the rotated,
-// normalised query coordinates (16ks + 8half + 2t, +1); heads >= group are zero columns.
-template <typename T>
-__global__ void __launch_bounds__(256) rotate_query_kernel(const T* __restrict__ q, int q_heads, int kv_heads,
-                                                           int group, int dim, const float* __restrict__ R,
-                                                           float scale, uint32_t* __restrict__ qfrag, int* status) {
-    __shared__ float qin[8][128];
-    __shared__ float qr[8][128];
-    const int u = blockIdx.x, b = u / kv_heads, h = u - b * kv_heads;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (u == 0 && threadIdx.x == 0) *status = 0;
-    for (int idx = threadIdx.x; idx < group * dim; idx += blockDim.x) {
-        const int n = idx / dim, k = idx - n * dim;
-        qin[n][k] = to_f32<T>(q[((int64_t)b * q_heads + h * group + n) * dim + k]);
-    }
-    __syncthreads();
-    // each warp takes 4 rows of R per round so that their loads are in flight together
-    const int nq = dim >> 5;
-    for (int j0 = warp * 4; j0 < dim; j0 += 32) {
-        float r[4][4];
-#pragma unroll
-        for (int jj = 0; jj < 4; jj++)
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                r[jj][i] = (i < nq) ? R[(int64_t)(j0 + jj) * dim + lane + 32 * i] : 0.0f;
-        for (int n = 0; n < group; n++) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float qv = (i < nq) ? qin[n][lane + 32 * i] : 0.0f;
-#pragma unroll
-                for (int jj = 0; jj < 4; jj++) acc[jj] = fmaf(r[jj][i], qv, acc[jj]);
-            }
-#pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-                const float sum = warp_sum(acc[jj]);
-                if (lane == 0) qr[n][j0 + jj] = sum;
-            }
-        }
-    }
-    __syncthreads();
-    // Fragments carry q_rot * scale * log2(e): fp16 keeps 11 significant bits whatever the magnitude and
-    // the products stay far inside its range, so no separate per-head factor is needed.
+// Fragments carry q_rot * scale * log2(e): fp16 keeps 11 significant bits whatever the magnitude and
+// the products stay far inside its range, so no separate per-head factor is needed.
+__device__ __forceinline__ void write_query_fragments(const float (*qr)[128], int u, int group, int dim,
+                                                      float scale, uint32_t* __restrict__ qfrag) {
     const float fold = scale * LOG2E;
     const int ksteps = dim >> 4;
     for (int idx = threadIdx.x; idx < ksteps * 64; idx += blockDim.x) {
@@ -165,6 +129,100 @@ __global__ void __launch_bounds__(256) rotate_query_kernel(const T* __restrict__
         }
         qfrag[((int64_t)u * ksteps + ks) * 64 + rem] = pack_half2_sat(lo, hi);
     }
+}
+
+// -------------------------------------------------------------------------------------------------
+// One CTA (8 warps) per unit rotates the unit's queries into B fragments: element (ks, lane = 4g+t, half)
+// of head g holds the rotated query coordinates (16ks + 8half + 2t, +1); heads >= group are zero columns.
+// With key != nullptr it is one decode step's whole preparation: it also quantises and stores the new
+// token's key and value of the unit.
+//
+// The code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums and a
+// butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
+// code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
+// The token goes to position lens_in[b] of its unit; lens_now[b] = lens_in[b] + 1 is what the
+// attention kernels of this step read.  A full unit (position >= max_seq) stores nothing, raises
+// status 3 and attends to the tokens it has.
+template <typename T, int NQ>
+__global__ void __launch_bounds__(256) decode_prepare_kernel(
+    const T* __restrict__ q, const T* __restrict__ key, const T* __restrict__ value, int64_t kv_stride,
+    int q_heads, int kv_heads, int group, int dim, const float* __restrict__ Rk, const float* __restrict__ Rv,
+    const float* __restrict__ bnd_k, const float* __restrict__ bnd_v, int kbits, int vbits, float scale,
+    uint8_t* __restrict__ store, int64_t max_seq, const int32_t* __restrict__ lens_in,
+    int32_t* __restrict__ lens_now, uint32_t* __restrict__ qfrag, int* status) {
+    __shared__ float vec[10][128];            // rows 0..group-1: queries; 8: unit key; 9: unit value
+    __shared__ float qr[8][128];
+    __shared__ float bnd[2][16];
+    __shared__ float nrm[2];
+    __shared__ uint32_t codes[2][128];
+    const int u = blockIdx.x, b = u / kv_heads, h = u - b * kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (u == 0 && threadIdx.x == 0) *status = 0;
+    const bool step = key != nullptr;
+    const int pos = step ? lens_in[b] : 0;
+    const bool room = step && pos < max_seq;
+    if (step && h == 0 && threadIdx.x == 0) lens_now[b] = room ? pos + 1 : pos;
+    if (step && !room && threadIdx.x == 0) atomicExch(status, 3);
+    if (step && threadIdx.x < 32) {            // (the boundary tables are null without a new token)
+        const int which = threadIdx.x >> 4, i = threadIdx.x & 15;
+        const int nb = (1 << (which ? vbits : kbits)) - 1;
+        bnd[which][i] = i < nb ? (which ? bnd_v : bnd_k)[i] : __int_as_float(0x7f800000);
+    }
+    for (int idx = threadIdx.x; idx < group * dim; idx += blockDim.x) {
+        const int n = idx / dim, k = idx - n * dim;
+        vec[n][k] = to_f32<T>(q[((int64_t)b * q_heads + h * group + n) * dim + k]);
+    }
+    if (step && warp >= 6) {                   // warps 6, 7: norm and unit vector of the key, the value
+        const int which = warp - 6;
+        const T* x = (which ? value : key) + (int64_t)u * kv_stride;
+        float v[NQ], ss = 0.0f;
+#pragma unroll
+        for (int qq = 0; qq < NQ; qq++) {
+            const int j = lane + 32 * qq;
+            v[qq] = j < dim ? to_f32<T>(x[j]) : 0.0f;
+            ss = fmaf(v[qq], v[qq], ss);
+        }
+        const float n = sqrtf(warp_sum(ss));
+        const float den = fmaxf(n, 1e-10f);
+#pragma unroll
+        for (int qq = 0; qq < NQ; qq++)
+            if (lane + 32 * qq < dim) vec[8 + which][lane + 32 * qq] = v[qq] / den;
+        if (lane == 0) nrm[which] = n;
+    }
+    __syncthreads();
+    // one thread per output coordinate of (group + 2) vectors
+    const int total = (group + (step ? 2 : 0)) * dim;
+    for (int o = threadIdx.x; o < total; o += blockDim.x) {
+        const int vi = o / dim, j = o - vi * dim;
+        const float* src = vec[vi < group ? vi : 8 + (vi - group)];
+        const float4* row = reinterpret_cast<const float4*>((vi <= group ? Rk : Rv) + (int64_t)j * dim);
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int k4 = 0; k4 < dim / 4; k4++) {
+            const float4 r = __ldg(row + k4);
+            acc = fmaf(src[4 * k4], r.x, acc);
+            acc = fmaf(src[4 * k4 + 1], r.y, acc);
+            acc = fmaf(src[4 * k4 + 2], r.z, acc);
+            acc = fmaf(src[4 * k4 + 3], r.w, acc);
+        }
+        if (vi < group) {
+            qr[vi][j] = acc;
+        } else {
+            const int which = vi - group;
+            uint32_t c = 0;
+            for (int step = 1 << ((which ? vbits : kbits) - 1); step > 0; step >>= 1)
+                if (bnd[which][c + step - 1] < acc) c += step;
+            codes[which][j] = c;
+        }
+    }
+    __syncthreads();
+    if (warp < 2 && room) {                    // warp 0 stores the key, warp 1 the value
+        uint32_t code[NQ];
+#pragma unroll
+        for (int qq = 0; qq < NQ; qq++) code[qq] = lane + 32 * qq < dim ? codes[warp][lane + 32 * qq] : 0u;
+        tiled_store_row<NQ>(store, warp + 1, kbits, vbits, (int64_t)u * max_seq + pos, code, nrm[warp], lane, dim);
+    }
+    write_query_fragments(qr, u, group, dim, scale, qfrag);
 }
 
 
@@ -670,14 +728,15 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
 // global load that does not depend on another one is issued up front (chunk maxima and sums, the first
 // eight accumulator rows of the thread, its rows of R_v), so the kernel costs about one memory round
 // trip; the chunk weights 2^(m_c - M) are then recomputed by every thread from shared memory.
-constexpr int MERGE_THREADS = 512;
+// 256 threads for head_dim 64 (all CTAs of the benchmark shape are then resident at once), else 512.
 constexpr int MERGE_MAX_CHUNKS = 1024;
-constexpr int MERGE_BATCH = 8;
+constexpr int MERGE_BATCH = 16;
 
-template <typename OutT>
+template <typename OutT, int MERGE_THREADS>
 __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const DecodeParams p, int dim,
                                                                      const float* __restrict__ Rv,
-                                                                     OutT* __restrict__ out) {
+                                                                     OutT* __restrict__ out,
+                                                                     int32_t* __restrict__ advance) {
     __shared__ float sm_m[MERGE_MAX_CHUNKS];
     __shared__ float sm_l[MERGE_MAX_CHUNKS];
     __shared__ float red[MERGE_THREADS];
@@ -685,6 +744,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
     const int u = blockIdx.x / p.group, n = blockIdx.x - u * p.group;
     const int b = u / p.kv_heads, h = u - b * p.kv_heads;
     const int S = p.seq_lens[b];
+    // a fused step publishes the new length once nothing of this call reads the caller's array any more
+    if (advance && h == 0 && n == 0 && threadIdx.x == 0) advance[b] = S;
     // every chunk contributes one partial per consumer warp of the streaming kernel
     const int nch = min(((S + p.chunk - 1) / p.chunk) * p.sets, MERGE_MAX_CHUNKS);
     const int tid = threadIdx.x, groups = MERGE_THREADS / dim, cg = tid / dim, j = tid - cg * dim;
@@ -701,9 +762,10 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
         const int c = cg + k * groups;
         raw[k] = c < nch ? p.part_acc[(pbase + (int64_t)c * p.group) * dim + j] : 0.0f;
     }
-    float rv[8];                                         // first 8 of this thread's R_v rows
+    constexpr int RVN = MERGE_THREADS == 256 ? 16 : 8;
+    float rv[RVN];                                       // first RVN of this thread's R_v rows
 #pragma unroll
-    for (int k = 0; k < 8; k++) rv[k] = Rv[(int64_t)(cg + k * groups) * dim + j];
+    for (int k = 0; k < RVN; k++) rv[k] = k < rows ? Rv[(int64_t)(cg + k * groups) * dim + j] : 0.0f;
     __syncthreads();
 
     float M = NEG_INF;
@@ -729,8 +791,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
     // out_k = sum_j y_j Rv[j][k]: this thread takes rows cg, cg + groups, ...
     float o = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; k++) o = fmaf(y[cg + k * groups], rv[k], o);
-    for (int k = 8; k < rows; k++) o = fmaf(y[cg + k * groups], Rv[(int64_t)(cg + k * groups) * dim + j], o);
+    for (int k = 0; k < RVN; k++) if (k < rows) o = fmaf(y[cg + k * groups], rv[k], o);
+    for (int k = RVN; k < rows; k++) o = fmaf(y[cg + k * groups], Rv[(int64_t)(cg + k * groups) * dim + j], o);
     __syncthreads();
     red[tid] = o;
     __syncthreads();
@@ -774,6 +836,7 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
     size_t off = 0;
     w.off_status = off; off = align_up(off + 256, 256);
+    w.off_lens = off;   off = align_up(off + (size_t)batch * 4, 256);    // sequence lengths of a fused step
     w.off_qfrag = off;  off = align_up(off + (size_t)units * dim * 16, 256);   // (dim/16) x 64 words
     const size_t parts = (size_t)units * w.nchunks * sets * group;
     w.off_m = off;   off = align_up(off + parts * 4, 256);
@@ -814,7 +877,14 @@ extern "C" size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, i
     return tqb::plan_workspace(batch, q_heads, kv_heads, dim, max_len).total;
 }
 
-extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
+namespace tqb {
+static int g_phases = 7;   // launches a decode call makes: 1 = preparation, 2 = streaming kernel, 4 = merge
+
+// Shared by tqb_decode_attention (key == nullptr) and tqb_decode_step (key, value: the new token of every
+// unit; lens_mut: the caller's sequence lengths, advanced by one at the end of the call).
+static int decode_common(const void* query, int q_dtype, const void* key, const void* value, int64_t kv_stride,
+                         const float* bnd_k, const float* bnd_v, int32_t* lens_mut,
+                         int batch, int q_heads, int kv_heads,
                                     int dim, const uint8_t* store, int64_t max_seq,
                                     const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
                                     int max_blocks, int block_size, const float* rot_k, const float* cent_k,
@@ -863,26 +933,68 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
     cudaStream_t st = (cudaStream_t)stream;
     const int units = batch * kv_heads;
 
-    switch (q_dtype) {
-        case TQB_F32: rotate_query_kernel<float><<<units, 256, 0, st>>>((const float*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
-        case TQB_F16: rotate_query_kernel<__half><<<units, 256, 0, st>>>((const __half*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
-        case TQB_BF16: rotate_query_kernel<__nv_bfloat16><<<units, 256, 0, st>>>((const __nv_bfloat16*)query, q_heads, kv_heads, group, dim, rot_k, scale, qfrag, p.status); break;
-        default: return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
+    int32_t* lens_now = reinterpret_cast<int32_t*>(ws + w.off_lens);
+    if (key) p.seq_lens = lens_now;
+    if (g_phases & 1) {
+#define TQB_PREP(T, NQ) decode_prepare_kernel<T, NQ><<<units, 256, 0, st>>>(                                       \
+        (const T*)query, (const T*)key, (const T*)value, kv_stride, q_heads, kv_heads, group, dim, rot_k, rot_v, \
+        bnd_k, bnd_v, kbits, vbits, scale, const_cast<uint8_t*>(store), max_seq, seq_lens, lens_now, qfrag, p.status)
+        switch (q_dtype) {
+            case TQB_F32: if (dim == 64) TQB_PREP(float, 2); else TQB_PREP(float, 4); break;
+            case TQB_F16: if (dim == 64) TQB_PREP(__half, 2); else TQB_PREP(__half, 4); break;
+            case TQB_BF16: if (dim == 64) TQB_PREP(__nv_bfloat16, 2); else TQB_PREP(__nv_bfloat16, 4); break;
+            default: return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
+        }
+#undef TQB_PREP
+        if (int e = check_launch("decode_prepare")) return e;
     }
-    if (int e = check_launch("rotate_query")) return e;
 
-    if (max_len > 0) {
+    if (max_len > 0 && (g_phases & 2)) {
         int e;
         if (dim == 64) e = paged ? dispatch_bits<64, true>(kbits, vbits, p, st) : dispatch_bits<64, false>(kbits, vbits, p, st);
         else e = paged ? dispatch_bits<128, true>(kbits, vbits, p, st) : dispatch_bits<128, false>(kbits, vbits, p, st);
         if (e) return e;
     }
 
+    if (!(g_phases & 4)) return TQB_OK;
+#define TQB_MERGE(T, TH) decode_merge_kernel<T, TH><<<units * group, TH, 0, st>>>(p, dim, rot_v, (T*)out, lens_mut)
     switch (out_dtype) {
-        case TQB_F32: decode_merge_kernel<float><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (float*)out); break;
-        case TQB_F16: decode_merge_kernel<__half><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (__half*)out); break;
-        case TQB_BF16: decode_merge_kernel<__nv_bfloat16><<<units * group, MERGE_THREADS, 0, st>>>(p, dim, rot_v, (__nv_bfloat16*)out); break;
+        case TQB_F32: if (dim == 64) TQB_MERGE(float, 256); else TQB_MERGE(float, 512); break;
+        case TQB_F16: if (dim == 64) TQB_MERGE(__half, 256); else TQB_MERGE(__half, 512); break;
+        case TQB_BF16: if (dim == 64) TQB_MERGE(__nv_bfloat16, 256); else TQB_MERGE(__nv_bfloat16, 512); break;
         default: return fail(TQB_ERR_INVALID, "decode_attention: unknown output dtype %d", out_dtype);
     }
+#undef TQB_MERGE
     return check_launch("decode_merge");
+}
+}  // namespace tqb
+
+extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
+                                    int dim, const uint8_t* store, int64_t max_seq,
+                                    const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
+                                    int max_blocks, int block_size, const float* rot_k, const float* cent_k,
+                                    int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,
+                                    void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                                    void* stream) {
+    return tqb::decode_common(query, q_dtype, nullptr, nullptr, 0, nullptr, nullptr, nullptr, batch, q_heads,
+                              kv_heads, dim, store, max_seq, seq_lens, max_len, block_tables, max_blocks,
+                              block_size, rot_k, cent_k, kbits, rot_v, cent_v, vbits, scale, workspace,
+                              workspace_bytes, out, out_dtype, stream);
+}
+
+extern "C" void tqb_debug_decode_phases(int mask) { tqb::g_phases = mask & 7; }
+
+extern "C" int tqb_decode_step(const void* query, const void* key, const void* value, int dtype,
+                               int64_t kv_stride, int batch, int q_heads, int kv_heads, int dim, uint8_t* store,
+                               int64_t max_seq, int32_t* seq_lens, int64_t max_len, const float* rot_k,
+                               const float* bnd_k, const float* cent_k, int kbits, const float* rot_v,
+                               const float* bnd_v, const float* cent_v, int vbits, float scale, void* workspace,
+                               size_t workspace_bytes, void* out, int out_dtype, void* stream) {
+    TQB_REQUIRE(batch == 0 || (key && value && bnd_k && bnd_v), "decode_step: null pointer");
+    TQB_REQUIRE(kv_stride >= dim, "decode_step: kv_stride (%lld) smaller than head_dim", (long long)kv_stride);
+    TQB_REQUIRE(max_len >= 1, "decode_step: max_len counts the new token, so it is at least 1");
+    return tqb::decode_common(query, dtype, key, value, kv_stride, bnd_k, bnd_v, seq_lens, batch, q_heads,
+                              kv_heads, dim, store, max_seq, seq_lens, max_len, nullptr, 0, 0, rot_k, cent_k,
+                              kbits, rot_v, cent_v, vbits, scale, workspace, workspace_bytes, out, out_dtype,
+                              stream);
 }

@@ -34,49 +34,6 @@ struct QuantArgs {
     int kb, vb;                 // tiled store geometry (bits of keys and values)
 };
 
-// Clear-then-set of a bit field in 32-bit words; safe against concurrent writers of OTHER bits of
-// the same word (two tokens of a pair share value bytes, 3-bit fields straddle bytes).
-__device__ __forceinline__ void tl_atomic_write(uint32_t* words, int absbit, int nbits, uint32_t v) {
-    const int w = absbit >> 5, s = absbit & 31;
-    const uint32_t mask = (1u << nbits) - 1u;
-    atomicAnd(&words[w], ~(mask << s));
-    atomicOr(&words[w], v << s);
-    if (s + nbits > 32) {
-        const int r = 32 - s;
-        atomicAnd(&words[w + 1], ~(mask >> r));
-        atomicOr(&words[w + 1], v >> r);
-    }
-}
-
-// One quantised row -> its token slot in the tiled KV store (tiled_layout.cuh).  Lane l holds the codes
-// of dims l + 32 q.  Called by all 32 lanes with the same `slot`.
-template <int NQ>
-__device__ __forceinline__ void tiled_store_row(const QuantArgs& a, int64_t slot, const uint32_t (&code)[NQ],
-                                                float nrm, int lane, int dim) {
-    uint8_t* rec = a.packed + (slot >> 4) * (int64_t)tl_record_bytes(dim, a.kb, a.vb);
-    const int r = (int)(slot & 15);
-    const int ksec = tl_key_section(dim, a.kb), vsec = tl_val_section(dim, a.vb);
-#pragma unroll
-    for (int q = 0; q < NQ; q++) {
-        const int d = lane + 32 * q;
-        const uint32_t partner = __shfl_down_sync(0xffffffffu, code[q], 1);
-        if (d >= dim) continue;
-        int base, bit;
-        if (a.tiled == 1) {
-            tl_key_slot(dim, a.kb, r, d, base, bit);
-            if (a.kb == 4) {   // a field is one whole byte owned by this token: plain store from the even lane
-                if ((lane & 1) == 0) rec[base + (bit >> 3)] = (uint8_t)(code[q] | (partner << 4));
-            } else {
-                tl_atomic_write(reinterpret_cast<uint32_t*>(rec), base * 8 + bit, a.kb, code[q]);
-            }
-        } else {
-            tl_val_slot(dim, a.vb, r, d, base, bit);
-            tl_atomic_write(reinterpret_cast<uint32_t*>(rec + ksec), base * 8 + bit, a.vb, code[q]);
-        }
-    }
-    if (lane == 0) reinterpret_cast<float*>(rec + ksec + vsec)[(a.tiled == 1 ? 0 : 16) + r] = nrm;
-}
-
 // Store one bit-plane group: lane (p * NQ + q) holds the 4 bytes at row offset p * bpp + 4 q.
 template <int NQ>
 __device__ __forceinline__ void store_planes(uint8_t* row, uint32_t word, int planes, int bpp, int lane) {
@@ -197,7 +154,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(QuantArgs a0, QuantArgs a
             if (!PROD && a.tiled) {
                 if (r < a.n) {
                     const int64_t slot = a.map(r);
-                    if (slot >= 0) tiled_store_row<NQ>(a, slot, code, nrm[i], lane, dim);
+                    if (slot >= 0) tiled_store_row<NQ>(a.packed, a.tiled, a.kb, a.vb, slot, code, nrm[i], lane, dim);
                 }
                 continue;
             }

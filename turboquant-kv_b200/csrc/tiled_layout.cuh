@@ -106,4 +106,50 @@ TQB_HD int tl_val_field_bit(int VB, int mt, int half, int s) {
     return VB == 2 ? (2 * mt + half) * 8 : (2 * (2 * mt + half) + s) * 2 * VB;
 }
 
+#ifdef __CUDACC__
+// Clear-then-set of a bit field in 32-bit words; safe against concurrent writers of OTHER bits of
+// the same word (two tokens of a pair share value bytes, 3-bit fields straddle bytes).
+__device__ __forceinline__ void tl_atomic_write(uint32_t* words, int absbit, int nbits, uint32_t v) {
+    const int w = absbit >> 5, s = absbit & 31;
+    const uint32_t mask = (1u << nbits) - 1u;
+    atomicAnd(&words[w], ~(mask << s));
+    atomicOr(&words[w], v << s);
+    if (s + nbits > 32) {
+        const int r = 32 - s;
+        atomicAnd(&words[w + 1], ~(mask >> r));
+        atomicOr(&words[w + 1], v >> r);
+    }
+}
+
+// One quantised row -> its token slot in the tiled KV store (tiled_layout.cuh).  Lane l holds the codes
+// of dims l + 32 q.  Called by all 32 lanes with the same `slot`.
+// `which`: 1 = key section, 2 = value section.
+template <int NQ>
+__device__ __forceinline__ void tiled_store_row(uint8_t* store, int which, int kb, int vb, int64_t slot,
+                                                const uint32_t (&code)[NQ], float nrm, int lane, int dim) {
+    uint8_t* rec = store + (slot >> 4) * (int64_t)tl_record_bytes(dim, kb, vb);
+    const int r = (int)(slot & 15);
+    const int ksec = tl_key_section(dim, kb), vsec = tl_val_section(dim, vb);
+#pragma unroll
+    for (int q = 0; q < NQ; q++) {
+        const int d = lane + 32 * q;
+        const uint32_t partner = __shfl_down_sync(0xffffffffu, code[q], 1);
+        if (d >= dim) continue;
+        int base, bit;
+        if (which == 1) {
+            tl_key_slot(dim, kb, r, d, base, bit);
+            if (kb == 4) {   // a field is one whole byte owned by this token: plain store from the even lane
+                if ((lane & 1) == 0) rec[base + (bit >> 3)] = (uint8_t)(code[q] | (partner << 4));
+            } else {
+                tl_atomic_write(reinterpret_cast<uint32_t*>(rec), base * 8 + bit, kb, code[q]);
+            }
+        } else {
+            tl_val_slot(dim, vb, r, d, base, bit);
+            tl_atomic_write(reinterpret_cast<uint32_t*>(rec + ksec), base * 8 + bit, vb, code[q]);
+        }
+    }
+    if (lane == 0) reinterpret_cast<float*>(rec + ksec + vsec)[(which == 1 ? 0 : 16) + r] = nrm;
+}
+#endif  // __CUDACC__
+
 }  // namespace tqb

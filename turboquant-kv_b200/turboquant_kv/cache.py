@@ -292,6 +292,32 @@ class QuantizedKVCache:
                                         max_len, pitch=self._pitch, scale=scale, out=out, reserve_len=self._pitch)
         return res.unsqueeze(2) if squeeze else res
 
+    def decode_step(self, layer_id: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                    scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``append`` of one token per sequence followed by ``decode_attention``, in three launches.
+
+        query: (batch, q_heads, head_dim); key / value: (batch, num_heads, head_dim) or
+        (batch, num_heads, 1, head_dim).  Same result as the two separate calls."""
+        if self._is_protected_layer(layer_id) or self._is_prod:
+            raise RuntimeError("decode_step covers MSE-quantised layers")
+        if key.dim() == 4:
+            key, value = key[:, :, 0], value[:, :, 0]
+        squeeze = query.dim() == 4
+        q = query[:, :, 0] if squeeze else query
+        B, HQ, D = q.shape
+        if B != self._batch or D != self.head_dim or HQ % self.num_heads:
+            raise RuntimeError(f"query {tuple(query.shape)} does not fit cache (batch {self._batch}, "
+                               f"kv heads {self.num_heads}, head_dim {self.head_dim})")
+        pos = int(self.seq_lens[layer_id])
+        if pos + 1 > self.max_seq_len:
+            raise RuntimeError(f"cache overflow: {pos} + 1 > max_seq_len {self.max_seq_len}")
+        max_len = self._pitch if torch.cuda.is_current_stream_capturing() else pos + 1
+        res = self._kv.decode_step(self._store[layer_id], q, key, value, self.num_heads,
+                                   self._seq_lens_dev[layer_id], max_len, self._pitch, scale=scale, out=out,
+                                   reserve_len=self._pitch)
+        self.seq_lens[layer_id] += 1
+        return res.unsqueeze(2) if squeeze else res
+
     def decode_status(self) -> int:
         """0 when every bounded device-side wait of the last decode_attention completed (synchronises)."""
         return 0 if self._kv is None else self._kv.status()

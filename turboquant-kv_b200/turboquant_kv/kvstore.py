@@ -127,6 +127,41 @@ class PackedKVStore:
                 N.ptr(self._workspace), self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype), N.stream_of(q)))
         return res
 
+    def decode_step(self, store: torch.Tensor, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                    kv_heads: int, seq_lens: torch.Tensor, max_len: int, pitch: int, scale: Optional[float] = None,
+                    out: Optional[torch.Tensor] = None, reserve_len: int = 0) -> torch.Tensor:
+        """Append one token per sequence and attend to it and everything before it, fused.
+
+        query (batch, q_heads, head_dim); key / value (batch, kv_heads, head_dim), same dtype as the query.
+        ``seq_lens`` (device int32) gives the write position and is advanced by one on the device;
+        ``max_len`` bounds the new lengths."""
+        q = query.to(self.device)
+        if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            q = q.float()
+        q = q.contiguous()
+        k = key.to(device=self.device, dtype=q.dtype).contiguous()
+        v = value.to(device=self.device, dtype=q.dtype).contiguous()
+        B, HQ, D = q.shape
+        if k.shape != (B, kv_heads, D) or v.shape != k.shape:
+            raise RuntimeError(f"decode_step: key/value must be ({B}, {kv_heads}, {D}), got {tuple(k.shape)}")
+        L = N.lib()
+        need = max(L.tqb_decode_attention_workspace_bytes(B, HQ, kv_heads, D, max_len),
+                   L.tqb_decode_attention_workspace_bytes(B, HQ, kv_heads, D, max(reserve_len, max_len)))
+        if need == 0:
+            raise RuntimeError(f"decode_step: {HQ} query heads do not fit {kv_heads} KV heads")
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        res = out if out is not None else torch.empty_like(q)
+        with torch.cuda.device(self.device):
+            N.check(L.tqb_decode_step(
+                N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), D, B, HQ, kv_heads, D, N.ptr(store), pitch,
+                N.ptr(seq_lens), max_len,
+                N.ptr(self.key_rotation), N.ptr(self.key_codebook[0]), N.ptr(self.key_codebook[1]), self.key_bits,
+                N.ptr(self.val_rotation), N.ptr(self.val_codebook[0]), N.ptr(self.val_codebook[1]), self.value_bits,
+                float(scale if scale is not None else 1.0 / math.sqrt(D)),
+                N.ptr(self._workspace), self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype), N.stream_of(q)))
+        return res
+
     def status(self) -> int:
         """0 when every bounded device-side wait of the last decode completed (synchronises)."""
         return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
