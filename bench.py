@@ -50,6 +50,11 @@ LAYERS, Q_HEADS, KV_HEADS, HEAD_DIM, BATCH = 16, 32, 8, 64, 32
 KEY_BITS, VALUE_BITS = 4, 2
 BYTES_PER_TOKEN_HEAD = KEY_BITS * HEAD_DIM // 8 + 4 + VALUE_BITS * HEAD_DIM // 8 + 4   # 56
 METRIC, UNIT = "decode_attention_tokens_per_s", "tokens/s"
+# DRAM traffic of one decode_partial_kernel launch from an ncu capture of a full-size launch of this
+# workload (dram__bytes_read.sum 235.18 MB + dram__bytes_write.sum 14.09 MB against 234.88 MB of
+# algorithmic bytes); traffic grows in proportion to the tokens, so other sizes are scaled by the ratio.
+NCU_TRAFFIC_RATIO = (235.18 + 14.09) / 234.88
+NCU_TRAFFIC_SOURCE = "profiles/decode_partial_kernel_c4_ctx16384.md (ncu dram__bytes_read.sum + dram__bytes_write.sum)"
 
 
 def workload_config(ctx: int, world: int) -> dict:
@@ -355,7 +360,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     achieved = bytes_per_launch / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "decode_partial_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                "traffic": None, "bytes_per_launch": bytes_per_launch, "ms_per_launch": kernel_ms,
+                "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO, "traffic_source": NCU_TRAFFIC_SOURCE,
+                "bytes_per_launch": bytes_per_launch, "ms_per_launch": kernel_ms,
                 "ms_per_call_all_launches": per_call_ms,
                 "note": "ms_per_launch: the streaming kernel alone between an event pair; ms_per_call_all_launches: "
                         "the three launches of one decode_step call (append + query rotation, streaming kernel, "

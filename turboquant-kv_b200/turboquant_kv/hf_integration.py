@@ -5,9 +5,9 @@ Same constructor and ``DynamicCache`` surface as upstream ``turboquant_kv/hf_int
 ``from_config``, ``seen_tokens``, ``memory_bytes``, ``__len__/__getitem__/__iter__``).
 
 ``update`` keeps upstream's contract -- it returns dense tensors: every OLD token dequantised, the NEW
-tokens exact (hf_integration.py:383-390) -- but all sequences of a batch share one packed store
-(batch, heads, capacity, packed_dim) that the fused kernels write and read; the per-head, per-batch
-Python loops of upstream are gone.  ``decode_attention`` is the fast path that skips the dense
+tokens exact (hf_integration.py:383-390) -- but all sequences of a batch share one record store
+(batch * heads units of 16-token records, see csrc/tiled_layout.cuh) that the fused kernels write and
+read; the per-head, per-batch Python loops of upstream are gone.  ``decode_attention`` is the fast path that skips the dense
 round trip altogether for one-token steps.
 """
 from __future__ import annotations
