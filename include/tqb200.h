@@ -225,6 +225,22 @@ int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed, const flo
                   int k, int64_t id_offset, void* workspace, size_t workspace_bytes,
                   float* out_scores, int64_t* out_ids, void* stream);
 
+/* The same scan for callers that cannot allocate a workspace (no counterpart in the reference): the
+ * scratch is a fixed 4 MiB array inside the library's device image, so the call reaches no allocating
+ * routine.  Meant for hosts that have already handed all free device memory to pools of their own,
+ * where an allocation fails or shrinks a pool, and for latency-critical loops in which a device
+ * allocation would stall every stream of the process.  Calls that need more scratch than
+ * tqb_scan_topk_static_capacity() bytes (tqb_scan_topk_workspace_bytes tells; e.g. more than 16 queries
+ * at k = 10) are rejected with TQB_ERR_WORKSPACE and a message; use tqb_scan_topk for those.
+ * The first call on a device resolves the array's address (cudaGetSymbolAddress, with that device
+ * current): make it early, before any stream capture is begun.  All calls on a device share the array:
+ * the status word at its start is cleared on `stream` by every call, the rest is rewritten before it
+ * is read; calls that may overlap on the device race on it and must be serialised by the caller. */
+size_t tqb_scan_topk_static_capacity(void);
+int tqb_scan_topk_static(const float* queries, int nq, const uint8_t* packed, const float* norms,
+                         int64_t n, int dim, int bits, const float* rotation, const float* centroids,
+                         int k, int64_t id_offset, float* out_scores, int64_t* out_ids, void* stream);
+
 /* Merge `parts` sorted candidate lists per query (the row-sharded search: one list per shard,
  * gathered over NCCL) into the global top-k with the same ordering rule.
  * scores (nq, parts, k) float32, ids (nq, parts, k) int64 -> out (nq, k). */

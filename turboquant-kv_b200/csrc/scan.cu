@@ -24,6 +24,8 @@
 #include "common.cuh"
 #include "decode_bits.cuh"
 
+#include <mutex>
+
 namespace tqb {
 
 constexpr int SCAN_TILE = 16;
@@ -639,4 +641,69 @@ extern "C" int tqb_topk_merge(const float* scores, const int64_t* ids, int nq, i
     TQB_REQUIRE(scores && ids && out_scores && out_ids, "topk_merge: null pointer");
     tqb::topk_merge_kernel<<<nq, 128, 0, (cudaStream_t)stream>>>(scores, ids, parts, k, out_scores, out_ids);
     return tqb::check_launch("topk_merge");
+}
+
+// ---- scan with built-in scratch ------------------------------------------------------------------
+// Same computation as tqb_scan_topk, for callers that cannot hand over a workspace because they cannot
+// allocate one: a host that has already given every free byte of device memory to its own pools (an
+// allocation there fails or forces the pool to shrink), or a latency-critical loop in which a device
+// allocation would stall all streams of the process while the driver maps memory.  The scratch is a
+// fixed array in the module's device image, so this entry point never calls an allocating routine.
+//
+// Set-up: the first call on each device looks up the array's address with cudaGetSymbolAddress while
+// that device is current (this may load the module on that device).  Make that first call early, on
+// every device that will be used, before any stream capture is begun.
+//
+// Sharing: all calls on one device use the same array.  The status word at its start is cleared on the
+// caller's stream at the beginning of each call; candidate lists and query fragments are rewritten by
+// every call before they are read.  Calls that may overlap on the device (different streams, different
+// host threads) race on the array and must be serialised by the caller; calls on one stream are safe.
+namespace tqb {
+constexpr size_t SCAN_STATIC_BYTES = (size_t)4 << 20;          // 4 MiB: e.g. up to 16 queries per call at k = 10
+constexpr int SCAN_STATIC_MAX_DEVICES = 64;
+static __device__ __align__(256) unsigned char g_scan_scratch[SCAN_STATIC_BYTES];
+static void* g_scan_scratch_ptr[SCAN_STATIC_MAX_DEVICES] = {};
+static std::mutex g_scan_scratch_mutex;
+
+static int scan_static_scratch(void** out) {
+    int dev = -1;
+    TQB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= SCAN_STATIC_MAX_DEVICES)
+        return fail(TQB_ERR_UNSUPPORTED, "scan_topk_static: device ordinal %d not supported (limit %d)", dev,
+                    SCAN_STATIC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_scan_scratch_mutex);
+    if (!g_scan_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_scan_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(TQB_ERR_CUDA, "scan_topk_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                        cudaGetErrorString(e));
+        g_scan_scratch_ptr[dev] = ptr;
+    }
+    *out = g_scan_scratch_ptr[dev];
+    return TQB_OK;
+}
+}  // namespace tqb
+
+extern "C" size_t tqb_scan_topk_static_capacity(void) { return tqb::SCAN_STATIC_BYTES; }
+
+extern "C" int tqb_scan_topk_static(const float* queries, int nq, const uint8_t* packed, const float* norms,
+                                    int64_t n, int dim, int bits, const float* rotation, const float* centroids,
+                                    int k, int64_t id_offset, float* out_scores, int64_t* out_ids, void* stream) {
+    using namespace tqb;
+    TQB_REQUIRE(nq >= 0 && n >= 0, "scan_topk_static: negative size");
+    if (nq == 0) return TQB_OK;
+    TQB_REQUIRE(dim > 0 && k >= 1 && k <= TQB_SCAN_MAX_K, "scan_topk_static: dim must be positive and k in 1..%d, got dim %d, k %d",
+                TQB_SCAN_MAX_K, dim, k);
+    const size_t need = tqb_scan_topk_workspace_bytes(nq, n, dim, bits, k);
+    if (need == 0 || need > SCAN_STATIC_BYTES)
+        return fail(TQB_ERR_WORKSPACE,
+                    "scan_topk_static: this call needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                    "use fewer queries per call or tqb_scan_topk with a workspace of your own", need,
+                    SCAN_STATIC_BYTES);
+    void* scratch = nullptr;
+    if (int e = scan_static_scratch(&scratch)) return e;
+    TQB_CUDA(cudaMemsetAsync(scratch, 0, 256, (cudaStream_t)stream));   // the status word starts at zero
+    return tqb_scan_topk(queries, nq, packed, norms, n, dim, bits, rotation, centroids, k, id_offset, scratch,
+                         SCAN_STATIC_BYTES, out_scores, out_ids, stream);
 }
