@@ -134,7 +134,12 @@ int tqb_attention_values_packed(const float* weights, int64_t bh, int64_t seq, i
  * the same codes and the same bytes per token as upstream.  A token SLOT is a flat index
  * slot = unit * pitch + position (pitch a multiple of 16); its record is slot / 16.  Contiguous cache:
  * unit = sequence * kv_heads + head, pitch = padded max_seq.  Paged cache: unit = block * kv_heads +
- * head, pitch = block_size.  tqb_kv_export / tqb_kv_import convert slots to and from upstream rows. */
+ * head, pitch = block_size.  tqb_kv_export / tqb_kv_import convert slots to and from upstream rows.
+ *
+ * vbits == 0 selects KEY-ONLY records, [32 lanes x dim*kbits/16 bytes of codes][16 norms f32] =
+ * 2*dim*kbits + 64 bytes: the storage of the search index (16 database rows per record, row i in slot
+ * i; 68 bytes per row at dim 128, 4 bits, as upstream).  tqb_kv_append (value = NULL), tqb_kv_export and
+ * tqb_kv_import (value outputs / inputs NULL) accept them; the decode entry points do not. */
 int64_t tqb_kv_record_bytes(int dim, int kbits, int vbits);
 
 /* ---- KV-cache append ---------------------------------------------------------------------
@@ -224,6 +229,18 @@ int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed, const flo
                   int64_t n, int dim, int bits, const float* rotation, const float* centroids,
                   int k, int64_t id_offset, void* workspace, size_t workspace_bytes,
                   float* out_scores, int64_t* out_ids, void* stream);
+
+/* The scan over an index stored as key-only records (see "storage layout" above; filled by
+ * tqb_kv_append with vbits = 0 or tqb_kv_import): same results as tqb_scan_topk on the same rows --
+ * scores bit-identical to upstream search_packed, ids identical except among exactly tied scores -- at a
+ * third of the instructions per row, because the codes arrive in the order the MMA lanes consume them.
+ * This is what TurboQuantIndex.search (turboquant_kv/search.py:206-227) runs on for dim 64 / 128 and
+ * 2-4 bits.  records: ceil(n / 16) records, 16-byte aligned; rows n..16*ceil(n/16)-1 are ignored. */
+size_t tqb_scan_records_workspace_bytes(int nq, int dim, int bits, int k);
+int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, int64_t n, int dim, int bits,
+                          const float* rotation, const float* centroids, int k, int64_t id_offset,
+                          void* workspace, size_t workspace_bytes, float* out_scores, int64_t* out_ids,
+                          void* stream);
 
 /* The same scan for callers that cannot allocate a workspace (no counterpart in the reference): the
  * scratch is a fixed 4 MiB array inside the library's device image, so the call reaches no allocating

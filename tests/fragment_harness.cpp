@@ -160,8 +160,12 @@ void tiled_key_tile(int D, int KB, int VB, const uint8_t* rec, const float* cent
         Frag f{};
         for (int lane = 0; lane < 32; lane++) {
             const int g = lane >> 2, t = lane & 3;
-            uint32_t kw[8];
-            load_words(rec + lane * KL, kw, KL);
+            uint32_t kw[8] = {};
+            {
+                const int pieces = tl_key_pieces(D, KB), pb = KL / pieces;
+                for (int pc = 0; pc < pieces; pc++)
+                    std::memcpy(reinterpret_cast<uint8_t*>(kw) + pc * pb, rec + tl_key_piece_offset(D, KB, lane, pc), pb);
+            }
             for (int half = 0; half < 2; half++) {
                 for (int second = 0; second < 2; second++) {
                     const uint32_t x = tl_field(kw, tl_key_field_bit(D, KB, ks, half, second), 2 * KB);

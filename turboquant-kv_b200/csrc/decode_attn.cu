@@ -25,6 +25,7 @@
 // Every wait is bounded: a warp that gives up records it in the status word at the start of the
 // workspace and returns, so a lost copy cannot hang the device.
 #include "common.cuh"
+#include "pipe.cuh"
 #include "tiled_layout.cuh"
 
 namespace tqb {
@@ -33,60 +34,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_INF = -__builtin_huge_valf();
 constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score exceeds m + 4 (log2)
 constexpr int TILE = 16;                // tokens per MMA tile
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
-
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// TMA bulk copy global -> this CTA's shared memory, completion counted on an mbarrier.
-// Both addresses 16-byte aligned, size a multiple of 16.  No multicast.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-    uint32_t y;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
-}
-// half2 {lo, hi} with saturation to the largest finite fp16 instead of infinity.
-__device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // ---- launch parameters --------------------------------------------------------------------------
 struct DecodeParams {
@@ -279,65 +226,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-
-// Loads from the pipeline stages use explicit shared-space instructions on 32-bit shared addresses (the
-// stage lives wherever the carve-up put it, so the compiler could not prove the address space itself).
-// They are volatile so that they stay behind the mbarrier wait that makes the stage readable.
-__device__ __forceinline__ uint32_t lds32v(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ float ldsf(uint32_t addr) { return __uint_as_float(lds32v(addr)); }
-
-// A lane's chunk of NB bytes -> 32-bit registers, with the widest loads the chunk's alignment allows.
-template <int NB>
-__device__ __forceinline__ void load_chunk(uint32_t addr, uint32_t (&w)[NB / 4]) {
-    if (NB % 16 == 0) {
-#pragma unroll
-        for (int i = 0; i < NB / 16; i++)
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
-    } else if (NB % 8 == 0) {
-#pragma unroll
-        for (int i = 0; i < NB / 8; i++)
-            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i));
-    } else {
-#pragma unroll
-        for (int i = 0; i < NB / 4; i++) w[i] = lds32v(addr + 4 * i);
-    }
-}
-
-// (field value) << SHIFT taken straight out of the chunk registers; `bit` and `bits` are compile-time
-// constants after unrolling: one shift and one mask (a funnel shift when the field straddles registers).
-template <int NW, int SHIFT>
-__device__ __forceinline__ uint32_t lut_offset(const uint32_t (&w)[NW], int bit, int bits) {
-    const int i = bit >> 5, s = bit & 31;
-    uint32_t v;
-    if (s + bits <= 32) v = (s >= SHIFT) ? (w[i] >> (s - SHIFT)) : (w[i] << (SHIFT - s));
-    else v = __funnelshift_r(w[i], w[(i + 1) < NW ? (i + 1) : i], s) << SHIFT;
-    return v & (((1u << bits) - 1u) << SHIFT);
-}
-
-// Shared address of the table entry selected by the field at `bit` of chunk registers w.
-//   BYTE table: tab = (table base, 64 KB aligned) | lane offset  -> one byte permute
-//   otherwise:  tab = table base + lane offset                   -> shift, mask, add
-template <bool BYTE, int NW>
-__device__ __forceinline__ uint32_t entry_addr(const uint32_t (&w)[NW], int bit, int bits, uint32_t tab) {
-    if (BYTE) return __byte_perm(w[bit >> 5], tab, 0x7604u | (((bit >> 3) & 3) << 4));
-    return lut_offset<NW, 7>(w, bit, bits) + tab;
-}
-
 // Position of a CTA in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to CTAs;
 // an item is streamed in stages of up to SR records, which the consumer warps share (RPW records each).
 template <int SR, int GROUPS>
@@ -398,7 +286,7 @@ __device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t re
         uint32_t kw[NT][C::KL / 4];
 #pragma unroll
         for (int i = 0; i < NT; i++) {
-            load_chunk<C::KL>(rec0 + i * C::REC + lane * C::KL, kw[i]);
+            load_key_chunk<C::KL>(rec0 + i * C::REC, lane, kw[i]);
             sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
         }
 #pragma unroll

@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) kv_convert_kernel(const StoreArgs a) {
         uint8_t* rec = a.store + (slot >> 4) * (int64_t)recb;
         const int r = (int)(slot & 15);
         float* nrm = reinterpret_cast<float*>(rec + ksec + vsec);
-        for (int which = 0; which < 2; which++) {          // 0 = keys, 1 = values
+        for (int which = 0; which < (a.vb ? 2 : 1); which++) {   // 0 = keys, 1 = values
             const int bits = which ? a.vb : a.kb;
             uint8_t* packed = which ? a.v_packed : a.k_packed;
             float* norms = which ? a.v_norms : a.k_norms;
@@ -78,8 +78,9 @@ __global__ void __launch_bounds__(256) kv_convert_kernel(const StoreArgs a) {
 
 static int check_geometry(const char* who, int dim, int kb, int vb) {
     if (dim != 64 && dim != 128) return fail(TQB_ERR_UNSUPPORTED, "%s: head_dim must be 64 or 128, got %d", who, dim);
-    if (kb < 2 || kb > 4 || vb < 2 || vb > 4)
-        return fail(TQB_ERR_UNSUPPORTED, "%s: key/value bits must be 2..4, got %d/%d", who, kb, vb);
+    if (kb < 2 || kb > 4 || (vb != 0 && (vb < 2 || vb > 4)))
+        return fail(TQB_ERR_UNSUPPORTED, "%s: key bits must be 2..4 and value bits 2..4 (or 0: key-only records), got %d/%d",
+                    who, kb, vb);
     return TQB_OK;
 }
 
@@ -92,6 +93,7 @@ static int launch_convert(const char* who, uint8_t* store, int64_t n, int dim, i
     TQB_REQUIRE(store, "%s: null store", who);
     TQB_REQUIRE((uintptr_t)store % 16 == 0, "%s: the record store must be 16-byte aligned", who);
     TQB_REQUIRE(((uintptr_t)kp | (uintptr_t)vp) % 4 == 0, "%s: packed rows must be 4-byte aligned", who);
+    TQB_REQUIRE(vb != 0 || (!vp && !vn), "%s: key-only records have no value rows", who);
     StoreArgs a{};
     a.store = store; a.n = n; a.dim = dim; a.kb = kb; a.vb = vb; a.map = make_rowmap(map);
     a.k_packed = kp; a.k_norms = kn; a.v_packed = vp; a.v_norms = vn;
@@ -103,7 +105,7 @@ static int launch_convert(const char* who, uint8_t* store, int64_t n, int dim, i
 }  // namespace tqb
 
 extern "C" int64_t tqb_kv_record_bytes(int dim, int kbits, int vbits) {
-    if ((dim != 64 && dim != 128) || kbits < 2 || kbits > 4 || vbits < 2 || vbits > 4) return 0;
+    if ((dim != 64 && dim != 128) || kbits < 2 || kbits > 4 || (vbits != 0 && (vbits < 2 || vbits > 4))) return 0;
     return tqb::tl_record_bytes(dim, kbits, vbits);
 }
 

@@ -277,10 +277,12 @@ extern "C" int tqb_kv_append(const void* key, const void* value, int dtype, int6
                              const tqb_rowmap* map, void* stream) {
     TQB_REQUIRE(n >= 0, "kv_append: negative row count");
     if (dim != 64 && dim != 128) return tqb::fail(TQB_ERR_UNSUPPORTED, "kv_append: head_dim must be 64 or 128, got %d", dim);
-    if (kbits < 2 || kbits > 4 || vbits < 2 || vbits > 4)
-        return tqb::fail(TQB_ERR_UNSUPPORTED, "kv_append: key/value bits must be 2..4, got %d/%d", kbits, vbits);
+    if (kbits < 2 || kbits > 4 || (vbits != 0 && (vbits < 2 || vbits > 4)))
+        return tqb::fail(TQB_ERR_UNSUPPORTED, "kv_append: key bits must be 2..4 and value bits 2..4 (or 0: key-only records), got %d/%d",
+                         kbits, vbits);
     if (n == 0) return TQB_OK;
-    TQB_REQUIRE(key && value && rot_k && rot_v && bnd_k && bnd_v && store, "kv_append: null pointer");
+    TQB_REQUIRE(key && rot_k && bnd_k && store, "kv_append: null pointer");
+    TQB_REQUIRE(vbits == 0 || (value && rot_v && bnd_v), "kv_append: null pointer");
     TQB_REQUIRE(x_stride >= dim, "kv_append: row stride %lld < dim %d", (long long)x_stride, dim);
     TQB_REQUIRE((uintptr_t)store % 16 == 0, "kv_append: the record store must be 16-byte aligned");
     tqb::QuantArgs a{}, b{};
@@ -288,7 +290,7 @@ extern "C" int tqb_kv_append(const void* key, const void* value, int dtype, int6
     a.packed = store; a.norms = nullptr; a.map = tqb::make_rowmap(map); a.tiled = 1; a.kb = kbits; a.vb = vbits;
     b = a;
     b.x = value; b.rot = rot_v; b.bnd = bnd_v; b.mse_bits = vbits; b.tiled = 2;
-    return tqb::dispatch_dtype<false>(dtype, a, b, 2, dim, (cudaStream_t)stream);
+    return tqb::dispatch_dtype<false>(dtype, a, b, vbits ? 2 : 1, dim, (cudaStream_t)stream);
 }
 
 extern "C" int tqb_quantize_prod(const void* x, int dtype, int64_t n, int dim, int64_t x_stride,

@@ -23,8 +23,11 @@
 // scan_generic_kernel (one row per lane, float32 table lookups) with the same list and merge code.
 #include "common.cuh"
 #include "decode_bits.cuh"
+#include "pipe.cuh"
+#include "tiled_layout.cuh"
 
 #include <mutex>
+#include <cstdlib>
 
 namespace tqb {
 
@@ -79,6 +82,8 @@ __device__ __forceinline__ bool better(float s, int id, float ts, int tid) {
 
 struct ScanParams {
     const uint8_t* packed; const float* norms; int64_t n;
+    const uint8_t* records;             // non-null: the database as key-only 16-row records (tiled_layout.cuh)
+    int combine;                        // record scan: one merged candidate list per CTA instead of one per warp
     int dim, bits, nq, k, kk;           // kk = k + SCAN_MARGIN candidates kept per list
     const float* rot; const float* cent; const float* queries;
     int64_t id_offset;
@@ -127,26 +132,40 @@ __device__ __forceinline__ void list_insert(float* ls, int* li, int kk, float s,
 // (B1); B2 repeats the hi part in even columns and is zero in odd ones.
 __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, int use_mma) {
     extern __shared__ float sm[];
-    float* qin = sm;                    // dim
-    float* qr = sm + p.dim;             // QG * dim
+    float* qr = sm + p.dim;             // QG * dim (rotated queries); the raw queries follow
     __shared__ float qmax[QG];
     const int grp = blockIdx.x;
     if (grp == 0 && threadIdx.x == 0) *p.status = 0;
-    for (int jq = 0; jq < QG; jq++) {
-        const int q = grp * QG + jq;
-        __syncthreads();
-        if (q < p.nq) {
-            for (int k = threadIdx.x; k < p.dim; k += blockDim.x) qin[k] = p.queries[(int64_t)q * p.dim + k];
-        }
-        __syncthreads();
-        for (int j = threadIdx.x; j < p.dim; j += blockDim.x) {
-            float s = 0.0f;
-            if (q < p.nq) {
-                const float* row = p.rot + (int64_t)j * p.dim;
-                for (int k = 0; k < p.dim; k++) s = __fadd_rn(s, __fmul_rn(qin[k], row[k]));
-                p.qrot[(int64_t)q * p.dim + j] = s;
+    // all QG queries of the group go through one pass over R: row j is read once (128-bit loads), each
+    // query keeps its own sum, accumulated in k order with separate multiply and add
+    float* qin_all = qr + QG * p.dim;        // QG * dim (the caller sizes the shared memory for it)
+    for (int e = threadIdx.x; e < QG * p.dim; e += blockDim.x) {
+        const int jq = e / p.dim, k = e - jq * p.dim, q = grp * QG + jq;
+        qin_all[e] = q < p.nq ? p.queries[(int64_t)q * p.dim + k] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < p.dim; j += blockDim.x) {
+        const float4* row = reinterpret_cast<const float4*>(p.rot + (int64_t)j * p.dim);
+        float s[QG];
+#pragma unroll
+        for (int jq = 0; jq < QG; jq++) s[jq] = 0.0f;
+#pragma unroll 4
+        for (int k4 = 0; k4 < p.dim / 4; k4++) {
+            const float4 r = __ldg(row + k4);
+#pragma unroll
+            for (int jq = 0; jq < QG; jq++) {
+                const float* qv = qin_all + jq * p.dim + 4 * k4;
+                s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[0], r.x));
+                s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[1], r.y));
+                s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[2], r.z));
+                s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[3], r.w));
             }
-            qr[jq * p.dim + j] = s;
+        }
+#pragma unroll
+        for (int jq = 0; jq < QG; jq++) {
+            const int q = grp * QG + jq;
+            if (q < p.nq) p.qrot[(int64_t)q * p.dim + j] = s[jq];
+            qr[jq * p.dim + j] = q < p.nq ? s[jq] : 0.0f;
         }
     }
     __syncthreads();
@@ -171,7 +190,8 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
         uint32_t w[4];
         for (int half = 0; half < 2; half++) {
             int dlo, dhi;
-            pair_dims(p.dim, t, 2 * ks + half, dlo, dhi);
+            if (use_mma == 2) { dlo = 16 * ks + 8 * half + 2 * t; dhi = dlo + 1; }   // record layout: dims in order
+            else pair_dims(p.dim, t, 2 * ks + half, dlo, dhi);
             const float a = qr[jq * p.dim + dlo] * inv, b = qr[jq * p.dim + dhi] * inv;
             const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
             w[half] = part ? s_pack_half2(a - ah, b - bh) : s_pack_half2(ah, bh);
@@ -337,6 +357,363 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
 
 
 // =================================================================================================
+// 2c. record scan: the database stored as key-only 16-row records (tiled_layout.cuh)
+// =================================================================================================
+// Same arithmetic as scan_kernel (two MMAs per 16 dims on fp16 hi / lo parts), but the rows arrive in
+// the order the MMA lanes consume them: one shared-memory load brings a lane's code fields of a record,
+// and each field (two codes) is the index of a 64-bit table entry {hi pair, lo pair}.  For 4-bit codes a
+// field is one byte and a single byte permute forms the entry's shared address (256-byte entries in a
+// 64 KB table on a 64 KB boundary of the shared window).  One persistent CTA per SM and query group: a
+// producer warp streams stages of SR records with one TMA bulk copy each; GROUPS groups of consumer
+// warps take the stages in turn, RPW records per warp.  Every wait is bounded.
+template <int D, int BITS>
+struct RecScanCfg {
+    static constexpr int KL = D * BITS / 16;                 // code bytes per lane and record
+    static constexpr int KSEC = 32 * KL;
+    static constexpr int REC = KSEC + 64;                    // + 16 norms
+    static constexpr bool KBYTE = (2 * BITS == 8);
+    static constexpr int LUT_ENTRIES = 1 << (2 * BITS);
+    static constexpr int LUT_BYTES = LUT_ENTRIES * 256;      // uint2 x 32 lanes per entry
+    static constexpr int KS = D / 16;
+    static constexpr int NT = D == 64 ? 4 : 2;               // records a warp has in flight at once
+    // Two consumer groups share the ring: with 8 stages each group has 4 stages in flight, which covers
+    // the memory latency (a group finishes a stage well within one round trip to HBM).
+    static constexpr int WARPS = 16, GROUPS = 2, WPG = WARPS / GROUPS, RPW = NT, SR = WPG * RPW;
+    static constexpr int STAGE = SR * REC;
+    static constexpr int THREADS = (WARPS + 1) * 32;         // + the producer warp
+    static constexpr int DYN = 227 * 1024;
+    static constexpr int MAX_NS = 8;
+    static constexpr int FIXED = 8 * (8 + 8 + 8) + 64;       // barriers, stage headers, centroids
+};
+
+// NT records at once: acc[i] = this lane's part of the 16 x 8 score tile of record i.
+// Table entry x occupies 256 bytes: [hi pair of every lane: 32 x 4 B][lo pair: 32 x 4 B], so both parts
+// come from one computed address (32-bit loads may land in any register, which keeps the four operand
+// registers of an MMA contiguous without moves).  qf[ks] = B fragment {[q_hi | q_lo] half 0, half 1};
+// the second MMA needs [q_hi | 0]: the same registers with the odd columns (odd lane / 4) cleared.
+template <int D, int BITS, int NT>
+__device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, const uint2 (&qf)[D / 16], uint32_t keep,
+                                               int lane, float (&acc)[NT][4]) {
+    using C = RecScanCfg<D, BITS>;
+    uint32_t kw[NT][C::KL / 4];
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+        load_key_chunk<C::KL>(rec0 + i * C::REC, lane, kw[i]);
+        acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    }
+#pragma unroll
+    for (int ks = 0; ks < C::KS; ks++) {
+        uint32_t ah[NT][4], al[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; i++)
+#pragma unroll
+            for (int half = 0; half < 2; half++)
+#pragma unroll
+                for (int second = 0; second < 2; second++) {
+                    const int bit = tl_key_field_bit(D, BITS, ks, half, second);
+                    const uint32_t addr = C::KBYTE ? entry_addr<true>(kw[i], bit, 8, tab)
+                                                   : lut_offset<C::KL / 4, 8>(kw[i], bit, 2 * BITS) + tab;
+                    ah[i][2 * half + second] = lds32(addr);
+                    al[i][2 * half + second] = lds32(addr + 128);
+                }
+        const uint32_t b0 = qf[ks].x & keep, b1 = qf[ks].y & keep;
+#pragma unroll
+        for (int i = 0; i < NT; i++) mma_f16(acc[i], ah[i], qf[ks].x, qf[ks].y);
+#pragma unroll
+        for (int i = 0; i < NT; i++) mma_f16(acc[i], al[i], b0, b1);
+    }
+}
+
+// Candidate lists of up to 32 entries live in registers: lane e holds entry e (best first) of each of the
+// QG queries.  Insertion of (s, id) into the list of query bq (warp-uniform): the entries better than the
+// candidate form a prefix, everything behind it moves down one lane.
+struct RegLists {
+    float s[QG];
+    int i[QG];
+};
+template <int JQ>
+__device__ __forceinline__ void reg_list_insert(RegLists& L, int kk, float s, int id, int lane) {
+    const uint32_t ahead = __ballot_sync(0xffffffffu, lane < kk && better(L.s[JQ], L.i[JQ], s, id));
+    const int pos = __popc(ahead);
+    const float us = __shfl_up_sync(0xffffffffu, L.s[JQ], 1);
+    const int ui = __shfl_up_sync(0xffffffffu, L.i[JQ], 1);
+    if (lane < kk) {
+        if (lane > pos) { L.s[JQ] = us; L.i[JQ] = ui; }
+        else if (lane == pos) { L.s[JQ] = s; L.i[JQ] = id; }
+    }
+}
+
+// The rare path of the record scan, kept out of line so that the streaming loop stays small enough for
+// the instruction cache: lanes flagged `ok` offer (sc, id) to the list of the query their lane serves
+// (query = lane % 4).  Returns the caller's updated threshold (the tail of its query's list).
+struct ScanThreshold { float s; int i; };
+__device__ __noinline__ ScanThreshold rec_scan_offer(float* ls, int* li, int kk, float sc, int id, bool ok,
+                                                     ScanThreshold thr, int lane) {
+    const int t = lane & 3;
+    uint32_t mask = __ballot_sync(0xffffffffu, ok);
+    while (mask) {
+        const int leader = __ffs(mask) - 1;
+        mask &= mask - 1;
+        const float bs = __shfl_sync(0xffffffffu, sc, leader);
+        const int bid = __shfl_sync(0xffffffffu, id, leader);
+        const int bq = leader & 3;
+        list_insert(ls + bq * kk, li + bq * kk, kk, bs, bid, lane);
+        if (t == bq) { thr.s = ls[bq * kk + kk - 1]; thr.i = li[bq * kk + kk - 1]; }
+    }
+    return thr;
+}
+
+template <int D, int BITS>
+__global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_kernel(const ScanParams p) {
+    using C = RecScanCfg<D, BITS>;
+    constexpr int WARPS = C::WARPS, GROUPS = C::GROUPS, WPG = C::WPG, RPW = C::RPW, SR = C::SR, NT = C::NT;
+    constexpr uint32_t F_END = 1u << 31;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int grp = blockIdx.y;
+
+    // ---- carve the shared window: [ring A | table (64 KB aligned for byte fields) | misc, lists | ring B] ----
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t end = base + C::DYN;
+    uint32_t tab_base, misc, ringA = base;
+    int slotsA = 0;
+    if (C::KBYTE) {
+        tab_base = (base + 65535u) & ~65535u;
+        slotsA = (int)((tab_base - base) / C::STAGE);
+    } else {
+        tab_base = base;
+    }
+    misc = tab_base + C::LUT_BYTES;
+    const uint32_t full_addr = misc, empty_addr = misc + 64, meta_addr = misc + 128, cent_addr = misc + 192;
+    const uint32_t lists_addr = misc + C::FIXED;
+    const uint32_t lists_bytes = (uint32_t)WARPS * QG * p.kk * 8;
+    const uint32_t ringB = (lists_addr + lists_bytes + 127u) & ~127u;
+    const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
+    const int NS = min(C::MAX_NS, slotsA + slotsB);
+    uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
+    float* lists_s = reinterpret_cast<float*>(smem_gen + lists_addr);
+    int* lists_i = reinterpret_cast<int*>(lists_s + WARPS * QG * p.kk);
+    if (NS < 2) {                                    // the host sizes kk so that this cannot happen
+        if (threadIdx.x == 0) atomicExch(p.status, 2);
+        return;
+    }
+    auto slot_addr = [&](int slot) -> uint32_t {
+        return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
+    };
+
+    if (threadIdx.x < 16)
+        reinterpret_cast<float*>(smem_gen + cent_addr)[threadIdx.x] =
+            threadIdx.x < (1 << BITS) ? p.cent[threadIdx.x] * CENT_SCALE : 0.0f;
+    if (threadIdx.x < C::MAX_NS) {
+        mbar_init(full_addr + threadIdx.x * 8, 1);
+        mbar_init(empty_addr + threadIdx.x * 8, WPG);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int e = threadIdx.x; e < WARPS * QG * p.kk; e += blockDim.x) { lists_s[e] = -__builtin_huge_valf(); lists_i[e] = ID_NONE; }
+    __syncthreads();
+    {
+        const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
+        for (int x = warp; x < C::LUT_ENTRIES; x += WARPS + 1) {
+            int clo, chi;
+            tl_key_field_codes((uint32_t)x, BITS, clo, chi);
+            const float a = cf[clo], b = cf[chi];
+            const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
+            *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + lane * 4) = pack_half2(ah, bh);
+            *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + 128 + lane * 4) = pack_half2(a - ah, b - bh);
+        }
+    }
+    __syncthreads();
+
+    const int64_t nrec = p.n / SCAN_TILE;            // full records; the last n % 16 rows belong to the merge kernel
+    const int64_t nstages = (nrec + SR - 1) / SR;
+
+    if (warp == WARPS) {
+        // ---- producer: stage index blockIdx.x, + gridDim.x, ...; one bulk copy per stage ----
+        if (lane == 0) {
+            bool ok = true;
+            int end_marks = 0;
+            uint32_t n = 0;
+            int64_t st = blockIdx.x;
+            int s = 0;                                // slot of stage n and the parity of its previous use
+            uint32_t par = 1;                         // (no division by the run-time ring size in the loop)
+            for (;; n++, s++) {
+                if (s == NS) { s = 0; par ^= 1; }
+                if (n >= (uint32_t)NS) ok = mbar_wait(empty_addr + 8 * s, par);
+                if (!ok) break;
+                uint2* meta = reinterpret_cast<uint2*>(smem_gen + meta_addr + s * 8);
+                if (st >= nstages) {                  // end of stream: one marker per consumer group
+                    *meta = make_uint2(0u, F_END);
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_addr + 8 * s) : "memory");
+                    if (++end_marks == GROUPS) break;
+                    continue;
+                }
+                const int64_t r0 = st * SR;
+                const int nt = (nrec - r0) < SR ? (int)(nrec - r0) : SR;
+                *meta = make_uint2((uint32_t)r0, (uint32_t)nt);
+                mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
+                {
+                    const int parts = max(1, p.combine >> 8);          // experiment: copies per stage
+                    const int per = (nt + parts - 1) / parts;
+                    for (int r = 0; r < nt; r += per) {
+                        const int c = min(per, nt - r);
+                        bulk_g2s(slot_addr(s) + r * C::REC, p.records + (r0 + r) * C::REC, (uint32_t)(c * C::REC),
+                                 full_addr + 8 * s);
+                    }
+                }
+                st += gridDim.x;
+            }
+            if (!ok) {
+                atomicExch(p.status, 1);
+                for (uint32_t i = (n > (uint32_t)NS ? n - NS : 0); i < n; i++)
+                    (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);
+            }
+        }
+    } else {
+        // ---- consumers ----
+        const uint32_t tab = C::KBYTE ? (tab_base | (uint32_t)(lane * 4)) : tab_base + lane * 4;
+        uint2 qf[C::KS];
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
+#pragma unroll
+            for (int ks = 0; ks < C::KS; ks++) { const uint4 v = src[ks * 32]; qf[ks] = make_uint2(v.x, v.y); }
+        }
+        const uint32_t keep = (g & 1) ? 0u : 0xffffffffu;
+        float* ls = lists_s + (size_t)warp * QG * p.kk;
+        int* li = lists_i + (size_t)warp * QG * p.kk;
+        const bool reg_lists = p.kk <= 32;            // else the lists stay in shared memory
+        RegLists RL;
+#pragma unroll
+        for (int jq = 0; jq < QG; jq++) { RL.s[jq] = -__builtin_huge_valf(); RL.i[jq] = ID_NONE; }
+        const int myq = grp * QG + t;                 // the query whose scores this lane receives
+        const float qsc = myq < p.nq ? p.qscale[myq] : 0.0f;
+        ScanThreshold thr{-__builtin_huge_valf(), ID_NONE};
+        const bool live = myq < p.nq && !(p.combine & 2);
+        const int r0w = RPW * (warp % WPG);
+        int s = warp / WPG - GROUPS;                  // slot of this group's current stage and its parity
+        uint32_t par = 0;
+        for (;;) {
+            s += GROUPS;
+            if (s >= NS) { s -= NS; par ^= 1; }
+            const bool ok = mbar_wait(full_addr + 8 * s, par);
+            if (!__all_sync(0xffffffffu, ok)) {
+                if (lane == 0) atomicExch(p.status, 1);
+                break;
+            }
+            uint2 meta;
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(meta.x), "=r"(meta.y) : "r"(meta_addr + s * 8));
+            if (meta.y & F_END) {                     // release the marker's slot too: the producer may need it
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
+                break;
+            }
+            const int nt = (int)meta.y;
+            const int mine = min(RPW, nt - r0w);
+            if (p.combine & 4) { thr.s += ldsf(slot_addr(s) + lane * 4); }
+            else
+            for (int i0 = 0; i0 < mine; i0 += NT) {
+                const uint32_t rec = slot_addr(s) + (r0w + i0) * C::REC;
+                float acc[NT][4];
+                // (records past the stage's end hold stale bytes: computed but never inserted)
+                rec_scan_tiles<D, BITS, NT>(rec, tab, qf, keep, lane, acc);
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    if (i0 + i >= mine) break;
+                    const uint32_t nr = rec + i * C::REC + C::KSEC + 4 * g;
+                    const float sc0 = (acc[i][0] + acc[i][1]) * (ldsf(nr) * qsc);
+                    const float sc1 = (acc[i][2] + acc[i][3]) * (ldsf(nr + 32) * qsc);
+                    const int id0 = (int)(meta.x + r0w + i0 + i) * SCAN_TILE + g, id1 = id0 + 8;
+                    const bool ok0 = live && better(sc0, id0, thr.s, thr.i);
+                    const bool ok1 = live && better(sc1, id1, thr.s, thr.i);
+                    if (__any_sync(0xffffffffu, ok0 || ok1)) {
+                        if (reg_lists) {
+#pragma unroll 1
+                            for (int r = 0; r < 2; r++) {
+                                const float sc = r ? sc1 : sc0;
+                                const int id = r ? id1 : id0;
+                                uint32_t mask = __ballot_sync(0xffffffffu, live && better(sc, id, thr.s, thr.i));
+                                while (mask) {
+                                    const int leader = __ffs(mask) - 1;
+                                    mask &= mask - 1;
+                                    const float bs = __shfl_sync(0xffffffffu, sc, leader);
+                                    const int bid = __shfl_sync(0xffffffffu, id, leader);
+                                    switch (leader & 3) {
+                                        case 0: reg_list_insert<0>(RL, p.kk, bs, bid, lane); break;
+                                        case 1: reg_list_insert<1>(RL, p.kk, bs, bid, lane); break;
+                                        case 2: reg_list_insert<2>(RL, p.kk, bs, bid, lane); break;
+                                        default: reg_list_insert<3>(RL, p.kk, bs, bid, lane); break;
+                                    }
+                                }
+                                // every lane's threshold = the tail of the list of the query it serves
+                                const float t0 = __shfl_sync(0xffffffffu, RL.s[0], p.kk - 1), t1 = __shfl_sync(0xffffffffu, RL.s[1], p.kk - 1);
+                                const float t2 = __shfl_sync(0xffffffffu, RL.s[2], p.kk - 1), t3 = __shfl_sync(0xffffffffu, RL.s[3], p.kk - 1);
+                                const int j0 = __shfl_sync(0xffffffffu, RL.i[0], p.kk - 1), j1 = __shfl_sync(0xffffffffu, RL.i[1], p.kk - 1);
+                                const int j2 = __shfl_sync(0xffffffffu, RL.i[2], p.kk - 1), j3 = __shfl_sync(0xffffffffu, RL.i[3], p.kk - 1);
+                                thr.s = t == 0 ? t0 : t == 1 ? t1 : t == 2 ? t2 : t3;
+                                thr.i = t == 0 ? j0 : t == 1 ? j1 : t == 2 ? j2 : j3;
+                            }
+                        } else {
+                            thr = rec_scan_offer(ls, li, p.kk, sc0, id0, ok0, thr, lane);
+                            thr = rec_scan_offer(ls, li, p.kk, sc1, id1, live && better(sc1, id1, thr.s, thr.i), thr, lane);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
+        }
+        if (reg_lists && lane < p.kk) {
+#pragma unroll
+            for (int jq = 0; jq < QG; jq++) { ls[jq * p.kk + lane] = RL.s[jq]; li[jq * p.kk + lane] = RL.i[jq]; }
+        }
+    }
+
+    // ---- candidates -> global (every thread of the CTA gets here) ----
+    __syncthreads();
+    if (p.combine) {
+        // one list per CTA and query: rank every candidate among the CTA's WARPS * kk by counting
+        const int per_q = WARPS * p.kk;
+        for (int idx = threadIdx.x; idx < QG * p.kk; idx += blockDim.x) {
+            const int jq = idx / p.kk, e = idx - jq * p.kk, q = grp * QG + jq;
+            if (q >= p.nq) continue;
+            const int64_t o = ((int64_t)q * p.lists_per_query + blockIdx.x) * p.kk + e;
+            p.cand_s[o] = -__builtin_huge_valf();
+            p.cand_id[o] = ID_NONE;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < QG * per_q; idx += blockDim.x) {
+            const int jq = idx / per_q, c = idx - jq * per_q, q = grp * QG + jq;
+            if (q >= p.nq) continue;
+            const int w = c / p.kk, e = c - w * p.kk;
+            const float s = lists_s[(w * QG + jq) * p.kk + e];
+            const int id = lists_i[(w * QG + jq) * p.kk + e];
+            if (id == ID_NONE) continue;
+            int rank = 0;
+            for (int w2 = 0; w2 < WARPS; w2++) {
+                const float* s2 = lists_s + (w2 * QG + jq) * p.kk;
+                const int* i2 = lists_i + (w2 * QG + jq) * p.kk;
+                for (int e2 = 0; e2 < p.kk; e2++) rank += better(s2[e2], i2[e2], s, id) ? 1 : 0;
+            }
+            if (rank < p.kk) {
+                const int64_t o = ((int64_t)q * p.lists_per_query + blockIdx.x) * p.kk + rank;
+                p.cand_s[o] = s;
+                p.cand_id[o] = id;
+            }
+        }
+    } else if (warp < WARPS) {
+        const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
+        for (int jq = 0; jq < QG; jq++) {
+            const int q = grp * QG + jq;
+            if (q >= p.nq) break;
+            const int64_t o = ((int64_t)q * p.lists_per_query + wid) * p.kk;
+            for (int e = lane; e < p.kk; e += 32) {
+                p.cand_s[o + e] = lists_s[(warp * QG + jq) * p.kk + e];
+                p.cand_id[o + e] = lists_i[(warp * QG + jq) * p.kk + e];
+            }
+        }
+    }
+}
+
+
+// =================================================================================================
 // 2b. generic scan: any dim (multiple of 8, <= 512), bits 1..4.  One query per blockIdx.y, one row per
 // lane; the float32 table and the summation order are the upstream ones, so these scores are exact.
 // =================================================================================================
@@ -397,8 +774,9 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) scan_generic_kernel(const Sca
 // =================================================================================================
 // 3. merge: best kk candidates per query -> exact float32 re-score -> sort -> top k
 // =================================================================================================
-constexpr int MERGE_THREADS = 128;
+constexpr int MERGE_THREADS = 256;
 constexpr int MERGE_MAX = TQB_SCAN_MAX_K + SCAN_MARGIN + SCAN_TILE;   // selected + tail rows
+constexpr int SURV_MAX = 1024;          // candidates the fast selection path ranks among themselves
 
 __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -416,11 +794,49 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
     const int64_t ncand = (int64_t)p.lists_per_query * p.kk;
     const float* cs = p.cand_s + (int64_t)q * ncand;
     const int* ci = p.cand_id + (int64_t)q * ncand;
-    // ---- selection by the scan's scores: round r takes the best candidate worse than round r-1's ----
+    // ---- selection by the scan's scores ----
+    // Fast path: every list is sorted best-first, so the kk-th best of the list HEADS is a lower bound of
+    // the kk-th best candidate overall; the few candidates not below it are ranked among themselves.
+    __shared__ float sv_s[SURV_MAX];
+    __shared__ int sv_i[SURV_MAX];
+    __shared__ int surv_n;
+    __shared__ float tau_s;
+    __shared__ int tau_i;
+    if (tid == 0) { surv_n = 0; tau_s = -__builtin_huge_valf(); tau_i = ID_NONE; }
+    __syncthreads();
+    const int L = p.lists_per_query;
+    for (int l = tid; l < L; l += blockDim.x) {
+        const float hs = cs[(int64_t)l * p.kk];
+        const int hi = ci[(int64_t)l * p.kk];
+        if (hi == ID_NONE) continue;
+        int rank = 0;
+        for (int l2 = 0; l2 < L; l2++) rank += better(cs[(int64_t)l2 * p.kk], ci[(int64_t)l2 * p.kk], hs, hi) ? 1 : 0;
+        if (rank == p.kk - 1) { tau_s = hs; tau_i = hi; }      // (ranks are distinct: at most one writer)
+    }
+    __syncthreads();
+    for (int64_t e = tid; e < ncand; e += blockDim.x) {
+        const float sc = cs[e];
+        const int id = ci[e];
+        if (id == ID_NONE || better(tau_s, tau_i, sc, id)) continue;
+        const int pos = atomicAdd(&surv_n, 1);
+        if (pos < SURV_MAX) { sv_s[pos] = sc; sv_i[pos] = id; }
+    }
+    __syncthreads();
+    int nsel = 0;
+    const bool fast = surv_n <= SURV_MAX;
+    if (fast) {
+        nsel = min(p.kk, surv_n);
+        for (int e = tid; e < surv_n; e += blockDim.x) {
+            int rank = 0;
+            for (int o = 0; o < surv_n; o++) rank += better(sv_s[o], sv_i[o], sv_s[e], sv_i[e]) ? 1 : 0;
+            if (rank < p.kk) sel_i[rank] = sv_i[e];
+        }
+        __syncthreads();
+    }
+    // General path (more survivors than the buffer holds): round r takes the best candidate worse than round r-1's.
     float prev_s = __builtin_huge_valf();
     int prev_i = -1;
-    int nsel = 0;
-    for (int r = 0; r < p.kk; r++) {
+    for (int r = 0; !fast && r < p.kk; r++) {
         float bs = -__builtin_huge_valf();
         int bi = ID_NONE;
         for (int64_t e = tid; e < ncand; e += blockDim.x) {
@@ -453,22 +869,37 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
     const int total = nsel + tail;
     __syncthreads();
     // ---- exact re-score, upstream order: dims ascending, add table entries, then * norm ----
-    for (int e = tid; e < total; e += blockDim.x) {
+    // A warp per candidate: the lanes look the table entries up in parallel, lane 0 adds them in order.
+    __shared__ float vals[MERGE_THREADS / 32][512];
+    for (int e = warp; e < total; e += MERGE_THREADS / 32) {
         const int id = sel_i[e];
-        const uint8_t* row = p.packed + (int64_t)id * pd;
-        float dot = 0.0f;
-        for (int m = 0; m < bpp; m++) {
-            uint32_t pl[4] = {0, 0, 0, 0};
-            for (int b = 0; b < p.bits; b++) pl[b] = row[b * bpp + m];
-            const int lim = min(8, p.dim - 8 * m);
-            for (int t = 0; t < lim; t++) {
-                const int sh = 7 - t;
-                const uint32_t c = ((pl[0] >> sh) & 1u) | (((pl[1] >> sh) & 1u) << 1) |
-                                   (((pl[2] >> sh) & 1u) << 2) | (((pl[3] >> sh) & 1u) << 3);
-                dot = __fadd_rn(dot, T[(8 * m + t) * levels + c]);
+        float nrm;
+        if (p.records) {
+            const int ksec = tl_key_section(p.dim, p.bits);
+            const uint8_t* rec = p.records + (int64_t)(id >> 4) * tl_record_bytes(p.dim, p.bits, 0);
+            for (int d = lane; d < p.dim; d += 32) {
+                int base, bit;
+                tl_key_slot(p.dim, p.bits, id & 15, d, base, bit);
+                vals[warp][d] = T[d * levels + tl_read_bits(rec + base, bit, p.bits)];
             }
+            nrm = reinterpret_cast<const float*>(rec + ksec)[id & 15];
+        } else {
+            const uint8_t* row = p.packed + (int64_t)id * pd;
+            for (int d = lane; d < p.dim; d += 32) {
+                const int m = d >> 3, sh = 7 - (d & 7);
+                uint32_t c = 0;
+                for (int b = 0; b < p.bits; b++) c |= ((row[b * bpp + m] >> sh) & 1u) << b;
+                vals[warp][d] = T[d * levels + c];
+            }
+            nrm = p.norms[id];
         }
-        sel_s[e] = __fmul_rn(dot, p.norms[id]);
+        __syncwarp();
+        if (lane == 0) {
+            float dot = 0.0f;
+            for (int d = 0; d < p.dim; d++) dot = __fadd_rn(dot, vals[warp][d]);
+            sel_s[e] = __fmul_rn(dot, nrm);
+        }
+        __syncwarp();
     }
     __syncthreads();
     // ---- rank by counting, emit the first k ----
@@ -570,6 +1001,105 @@ static int launch_scan(const ScanParams& p, int ngroups, cudaStream_t st) {
 
 }  // namespace tqb
 
+namespace tqb {
+
+// Record scan: candidate lists are merged per CTA inside the scan kernel while that is cheap
+// (rank by counting among 16 * kk entries); beyond that every consumer warp writes its own list.
+static bool rec_combine(int kk) { return 16 * kk <= 1024; }
+
+static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
+    ScanPlan pl{};
+    pl.mma = true;
+    pl.kk = k + SCAN_MARGIN;
+    pl.lists = sm_count() * (rec_combine(pl.kk) ? 1 : 16);
+    pl.ngroups = (nq + QG - 1) / QG;
+    size_t off = 0;
+    pl.off_status = off; off = s_align(off + 256);
+    pl.off_qrot = off;   off = s_align(off + (size_t)nq * dim * 4);
+    pl.off_qfrag = off;  off = s_align(off + (size_t)pl.ngroups * (dim / 16 + 1) * 32 * 16);
+    pl.off_qscale = off; off = s_align(off + (size_t)nq * 4);
+    const size_t cand = (size_t)nq * pl.lists * pl.kk;
+    pl.off_cs = off; off = s_align(off + cand * 4);
+    pl.off_ci = off; off = s_align(off + cand * 4);
+    pl.total = off;
+    (void)bits;
+    return pl;
+}
+
+template <int D, int BITS>
+static int launch_scan_records(const ScanParams& p, int ngroups, int grid_x, cudaStream_t st) {
+    using C = RecScanCfg<D, BITS>;
+    // at least two stages must fit beside the table and the candidate lists
+    const size_t lists = (size_t)C::WARPS * QG * p.kk * 8;
+    const size_t worst = (C::KBYTE ? 2 * 65536 : C::LUT_BYTES + 4096) + C::FIXED + lists + 256;
+    const size_t tail = worst < (size_t)C::DYN ? (size_t)C::DYN - worst : 0;
+    const size_t stages = tail / C::STAGE + (C::KBYTE ? (65536 - 4096) / C::STAGE : 0);
+    if (stages < 2)
+        return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: k = %d leaves no room for the pipeline in shared memory", p.k);
+    auto kern = scan_records_kernel<D, BITS>;
+    TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
+    dim3 grid(grid_x, ngroups);
+    kern<<<grid, C::THREADS, C::DYN, st>>>(p);
+    return check_launch("scan_records");
+}
+
+}  // namespace tqb
+
+extern "C" size_t tqb_scan_records_workspace_bytes(int nq, int dim, int bits, int k) {
+    if (nq <= 0 || (dim != 64 && dim != 128) || bits < 2 || bits > 4 || k <= 0 || k > TQB_SCAN_MAX_K) return 0;
+    return tqb::plan_scan_records(nq, dim, bits, k).total;
+}
+
+extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, int64_t n, int dim,
+                                     int bits, const float* rotation, const float* centroids, int k,
+                                     int64_t id_offset, void* workspace, size_t workspace_bytes,
+                                     float* out_scores, int64_t* out_ids, void* stream) {
+    using namespace tqb;
+    TQB_REQUIRE(nq >= 0 && n >= 0, "scan_records_topk: negative size");
+    if (dim != 64 && dim != 128) return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: dim must be 64 or 128, got %d", dim);
+    if (bits < 2 || bits > 4) return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: bit_width must be 2-4, got %d", bits);
+    TQB_REQUIRE(k >= 1, "scan_records_topk: k must be positive, got %d", k);
+    if (k > TQB_SCAN_MAX_K) return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: k = %d exceeds the limit %d", k, TQB_SCAN_MAX_K);
+    if (n >= 0x7fffffff - 16) return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: at most 2^31-18 rows per call (shard the index)");
+    if (nq == 0) return TQB_OK;
+    TQB_REQUIRE(queries && rotation && centroids && workspace && out_scores && out_ids, "scan_records_topk: null pointer");
+    TQB_REQUIRE(n == 0 || records, "scan_records_topk: null database");
+    TQB_REQUIRE((uintptr_t)records % 16 == 0, "scan_records_topk: the record store must be 16-byte aligned");
+    TQB_REQUIRE((uintptr_t)workspace % 256 == 0, "scan_records_topk: workspace must be 256-byte aligned");
+    const ScanPlan pl = plan_scan_records(nq, dim, bits, k);
+    if (workspace_bytes < pl.total)
+        return fail(TQB_ERR_WORKSPACE, "scan_records_topk: workspace %zu bytes < required %zu", workspace_bytes, pl.total);
+
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    ScanParams p{};
+    p.records = records; p.n = n; p.dim = dim; p.bits = bits; p.nq = nq; p.k = k; p.kk = pl.kk;
+    p.rot = rotation; p.cent = centroids; p.queries = queries; p.id_offset = id_offset;
+    p.status = reinterpret_cast<int*>(ws + pl.off_status);
+    p.qrot = reinterpret_cast<float*>(ws + pl.off_qrot);
+    p.qfrag = reinterpret_cast<uint32_t*>(ws + pl.off_qfrag);
+    p.qscale = reinterpret_cast<float*>(ws + pl.off_qscale);
+    p.cand_s = reinterpret_cast<float*>(ws + pl.off_cs);
+    p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
+    p.out_scores = out_scores; p.out_ids = out_ids;
+    p.combine = (rec_combine(pl.kk) ? 1 : 0) | (getenv("TQB_NOOFFER") ? 2 : 0) | (getenv("TQB_PROBE") ? 4 : 0) |
+                (getenv("TQB_SPLIT") ? atoi(getenv("TQB_SPLIT")) << 8 : 0);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid_x = sm_count();
+    p.lists_per_query = grid_x * (p.combine ? 1 : 16);
+
+    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, 2);
+    if (int e = check_launch("scan_prepare")) return e;
+    int e = TQB_ERR_UNSUPPORTED;
+#define TQB_CASE(d, b) if (dim == d && bits == b) e = launch_scan_records<d, b>(p, pl.ngroups, grid_x, st);
+    TQB_CASE(64, 2) TQB_CASE(64, 3) TQB_CASE(64, 4) TQB_CASE(128, 2) TQB_CASE(128, 3) TQB_CASE(128, 4)
+#undef TQB_CASE
+    if (e) return e;
+    const size_t msmem = sizeof(float) * (size_t)dim * (1 << bits);
+    TQB_CUDA(cudaFuncSetAttribute(scan_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(msmem, 48 * 1024)));
+    scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
+    return check_launch("scan_merge");
+}
+
 extern "C" size_t tqb_scan_topk_workspace_bytes(int nq, int64_t n, int dim, int bits, int k) {
     if (nq <= 0 || dim <= 0 || k <= 0 || k > TQB_SCAN_MAX_K) return 0;
     return tqb::plan_scan(nq, n, dim, bits, k).total;
@@ -613,7 +1143,7 @@ extern "C" int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed
     const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(sm_count(), ceil_div(ntiles, SCAN_WARPS)));
     p.lists_per_query = gx * SCAN_WARPS;
 
-    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + QG) * dim, st>>>(p, pl.mma ? 1 : 0);
+    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, pl.mma ? 1 : 0);
     if (int e = check_launch("scan_prepare")) return e;
 
     if (pl.mma) {
@@ -630,6 +1160,7 @@ extern "C" int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed
         if (int e = check_launch("scan_generic")) return e;
     }
     const size_t msmem = sizeof(float) * (size_t)dim * (1 << bits);
+    TQB_CUDA(cudaFuncSetAttribute(scan_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(msmem, 48 * 1024)));
     scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
     return check_launch("scan_merge");
 }

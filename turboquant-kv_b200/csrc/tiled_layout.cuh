@@ -11,9 +11,13 @@
 //   [ key section : 32 lanes x KL bytes ][ value section : 32 lanes x VL bytes ][ 16 key norms f32 ][ 16 value norms f32 ]
 //      KL = D*KB/16                          VL = D*VB/16                          record = 2*D*(KB+VB) + 128 bytes
 //
+// The search index uses the same records without the value half (VB = 0): 16 database rows per record,
+// [ key section ][ 16 norms ], record = 2*D*KB + 64 bytes -- the upstream 68 bytes per row at D = 128, 4 bits.
+//
 // Lane = 4*g + t is the mma.sync lane that consumes the bytes (g = lane/4, t = lane%4).
 //
-// Key section, lane (g, t): the codes of tokens g (first KL/2 bytes) and g+8 (last KL/2 bytes) for the
+// Key section, lane (g, t) [stored contiguously per lane, or as two planes when KL = 32, see
+// tl_key_piece_offset]: the codes of tokens g (first KL/2 bytes) and g+8 (last KL/2 bytes) for the
 // dims this lane feeds into the score MMA.  A token's half is D/8 FIELDS of 2*KB bits, field e at bit
 // e*2*KB (little endian).  Field e = code[d] | code[d+1] << KB with d = 16*(e/2) + 8*(e%2) + 2*t, i.e.
 // exactly the A-operand elements (k = 2t, 2t+1 | 2t+8, 2t+9) of k-step e/2.
@@ -36,9 +40,19 @@ constexpr int TL_TILE = 16;
 
 TQB_HD int tl_key_lane_bytes(int D, int KB) { return D * KB / 16; }
 TQB_HD int tl_val_lane_bytes(int D, int VB) { return D * VB / 16; }
-TQB_HD int tl_record_bytes(int D, int KB, int VB) { return 2 * D * (KB + VB) + 128; }
+// VB == 0: key-only records (the search index: rows instead of tokens) carry the 16 key norms only.
+TQB_HD int tl_record_bytes(int D, int KB, int VB) { return 2 * D * (KB + VB) + (VB ? 128 : 64); }
 TQB_HD int tl_key_section(int D, int KB) { return 32 * tl_key_lane_bytes(D, KB); }
 TQB_HD int tl_val_section(int D, int VB) { return 32 * tl_val_lane_bytes(D, VB); }
+
+// A lane's key chunk is stored in one piece, except 32-byte chunks (D = 128, 4 bits), which are stored as
+// two 16-byte planes (the token-g half of all 32 lanes, then the token-g+8 half) so that each of the two
+// 128-bit shared loads of a warp is free of bank conflicts.  Piece p of lane l starts here:
+TQB_HD int tl_key_pieces(int D, int KB) { return tl_key_lane_bytes(D, KB) == 32 ? 2 : 1; }
+TQB_HD int tl_key_piece_offset(int D, int KB, int lane, int piece) {
+    const int pb = tl_key_lane_bytes(D, KB) / tl_key_pieces(D, KB);
+    return piece * 32 * pb + lane * pb;
+}
 
 // Where the code of (token row r of the tile, dim d) lives in the KEY section:
 // byte offset of the lane's token half and the bit offset inside it.
@@ -47,7 +61,8 @@ TQB_HD void tl_key_slot(int D, int KB, int r, int d, int& byte_base, int& bit) {
     const int ks = d >> 4, half = (d >> 3) & 1, t = (d & 7) >> 1, hi = d & 1;
     const int e = 2 * ks + half;
     const int KL = tl_key_lane_bytes(D, KB);
-    byte_base = (4 * g + t) * KL + second * (KL / 2);
+    byte_base = tl_key_pieces(D, KB) == 2 ? tl_key_piece_offset(D, KB, 4 * g + t, second)
+                                          : (4 * g + t) * KL + second * (KL / 2);
     bit = e * 2 * KB + hi * KB;
 }
 

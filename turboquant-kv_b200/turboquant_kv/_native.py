@@ -81,6 +81,10 @@ def lib():
                                       c_int, c_void_p]
         L.tqb_scan_topk.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                     c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
+        L.tqb_scan_records_workspace_bytes.restype = c_size_t
+        L.tqb_scan_records_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
+        L.tqb_scan_records_topk.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
+                                            c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
         L.tqb_topk_merge.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         _lib = L
     return _lib

@@ -16,6 +16,7 @@ chunk with the dequantize_prod kernel and scored with a dense matmul.
 """
 from __future__ import annotations
 
+import ctypes
 import struct
 from typing import Optional, Tuple
 
@@ -83,8 +84,14 @@ class TurboQuantIndex:
             raise ValueError(f"Prod mode requires bits >= 2, got {bit_width}")
         self._codebook = tuple(t.to(self.device) for t in lloyd_max_codebook(mse_bits, dim))
         self._S_matrix = _make_qjl_matrix(dim, dim, seed, self.device) if mode == "prod" else None
-        self._packed_codes: Optional[torch.Tensor] = None
-        self._norms: Optional[torch.Tensor] = None
+        # MSE indexes of dim 64 / 128 with 2-4 bits live on the GPU as key-only 16-row records
+        # (csrc/tiled_layout.cuh), the layout the scan kernel streams; _packed_codes / _norms are then
+        # exported upstream-layout copies.  Every other index keeps upstream rows.
+        self._use_records = mode == "mse" and dim in (64, 128) and 2 <= bit_width <= 4
+        self._records: Optional[torch.Tensor] = None
+        self._rec_bytes = int(N.lib().tqb_kv_record_bytes(dim, bit_width, 0)) if self._use_records else 0
+        self._rows_pc: Optional[torch.Tensor] = None     # upstream rows (stored, or cached export)
+        self._rows_nm: Optional[torch.Tensor] = None
         self._qjl_signs: Optional[torch.Tensor] = None
         self._residual_norms: Optional[torch.Tensor] = None
         self.n_vectors = 0
@@ -98,6 +105,58 @@ class TurboQuantIndex:
         idx.add(vectors)
         return idx
 
+    # ---- upstream attribute names (search.py:96-99) -------------------------------------------
+    def _export_rows(self) -> None:
+        if self._rows_pc is not None or not self._use_records or self.n_vectors == 0:
+            return
+        n, bpp = self.n_vectors, (self.dim + 7) // 8
+        pc = torch.empty(n, self.bit_width * bpp, dtype=torch.uint8, device=self.device)
+        nm = torch.empty(n, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_kv_export(N.ptr(self._records), n, self.dim, self.bit_width, 0, None, N.ptr(pc),
+                                          N.ptr(nm), None, None, N.stream_of(pc)))
+        self._rows_pc, self._rows_nm = pc, nm
+
+    @property
+    def _packed_codes(self) -> Optional[torch.Tensor]:
+        self._export_rows()
+        return self._rows_pc
+
+    @_packed_codes.setter
+    def _packed_codes(self, value: Optional[torch.Tensor]) -> None:
+        self._rows_pc = value
+
+    @property
+    def _norms(self) -> Optional[torch.Tensor]:
+        self._export_rows()
+        return self._rows_nm
+
+    @_norms.setter
+    def _norms(self, value: Optional[torch.Tensor]) -> None:
+        self._rows_nm = value
+
+    def _reserve_records(self, rows: int) -> None:
+        have = 0 if self._records is None else self._records.numel() // self._rec_bytes * 16
+        if rows <= have:
+            return
+        cap = max(4096, have)
+        while cap < rows:
+            cap *= 2
+        new = torch.zeros((cap // 16) * self._rec_bytes, dtype=torch.uint8, device=self.device)
+        if self._records is not None:
+            new[: self._records.numel()] = self._records
+        self._records = new
+
+    def _import_rows(self, packed: torch.Tensor, norms: torch.Tensor) -> None:
+        """Upstream rows -> records (used by load())."""
+        n = packed.shape[0]
+        self._reserve_records(n)
+        pc, nm = packed.to(self.device).contiguous(), norms.to(self.device, torch.float32).contiguous()
+        with torch.cuda.device(self.device):
+            N.check(N.lib().tqb_kv_import(N.ptr(self._records), n, self.dim, self.bit_width, 0, None, N.ptr(pc),
+                                          N.ptr(nm), None, None, N.stream_of(pc)))
+        self._rows_pc = self._rows_nm = None
+
     # ------------------------------------------------------------------------------------------
     @staticmethod
     def _grow(old: Optional[torch.Tensor], new: torch.Tensor) -> torch.Tensor:
@@ -109,6 +168,21 @@ class TurboQuantIndex:
             vectors = vectors.unsqueeze(0)
         assert vectors.shape[-1] == self.dim
         x = vectors.to(self.device)
+        if self._use_records:
+            if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                x = x.float()
+            x = x.contiguous()
+            n = x.shape[0]
+            self._reserve_records(self.n_vectors + n)
+            rm = N.RowMap(1, 1, 0, self.n_vectors, None, 1, None, 1)      # row r -> slot n_vectors + r
+            with torch.cuda.device(self.device):
+                N.check(N.lib().tqb_kv_append(N.ptr(x), None, N.dtype_code(x.dtype), n, self.dim, self.dim,
+                                              N.ptr(self._rotation), N.ptr(self._codebook[0]), self.bit_width,
+                                              None, None, 0, N.ptr(self._records), ctypes.byref(rm),
+                                              N.stream_of(x)))
+            self._rows_pc = self._rows_nm = None
+            self.n_vectors += n
+            return
         if self.mode == "mse":
             packed, norms = quantize_mse(x, self.bit_width, dim=self.dim, rotation=self._rotation,
                                          codebook=self._codebook)
@@ -144,6 +218,16 @@ class TurboQuantIndex:
             for lo in range(0, nq, _QUERY_CHUNK):
                 qc = q[lo:lo + _QUERY_CHUNK]
                 n = qc.shape[0]
+                if self._use_records:
+                    need = L.tqb_scan_records_workspace_bytes(n, self.dim, self.bit_width, k)
+                    if self._workspace is None or self._workspace.numel() < need:
+                        self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+                    N.check(L.tqb_scan_records_topk(N.ptr(qc), n, N.ptr(self._records), self.n_vectors, self.dim,
+                                                    self.bit_width, N.ptr(self._rotation), N.ptr(self._codebook[1]),
+                                                    k, self.id_offset, N.ptr(self._workspace),
+                                                    self._workspace.numel(), N.ptr(out_s[lo:lo + n]),
+                                                    N.ptr(out_i[lo:lo + n]), N.stream_of(qc)))
+                    continue
                 need = L.tqb_scan_topk_workspace_bytes(n, self.n_vectors, self.dim, self.bit_width, k)
                 if self._workspace is None or self._workspace.numel() < need:
                     self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
@@ -229,8 +313,13 @@ class TurboQuantIndex:
             return torch.from_numpy(arr)
 
         idx = cls(dim=dim, bit_width=bits, mode=mode, rotation=rotation, seed=seed, device=device)
-        idx._packed_codes = take(n, np.uint8, pbytes).reshape(n, pbytes).to(idx.device)
-        idx._norms = take(n, np.float32, 4).to(idx.device)
+        packed = take(n, np.uint8, pbytes).reshape(n, pbytes)
+        norms = take(n, np.float32, 4)
+        if idx._use_records and n:
+            idx._import_rows(packed, norms)
+        else:
+            idx._packed_codes = packed.to(idx.device)
+            idx._norms = norms.to(idx.device)
         if mode == "prod":
             idx._qjl_signs = take(n, np.uint8, bpp).reshape(n, bpp).to(idx.device)
             idx._residual_norms = take(n, np.float32, 4).to(idx.device)
