@@ -539,6 +539,8 @@ def run_case(args) -> None:
     """Single-kernel cases for profilers: a few eager launches of one hot kernel, timed with CUDA events.
 
     decode    one layer-call = decode_attention over `--layers` layers of the decode workload
+    paged     one layer-call of paged decode attention, Llama-3-8B geometry (head_dim 128, K4/V3, 16-token
+              pages, batch 64, context `--ctx`), random codes
     scan      single-query passes of the 4-bit index scan over `--scan-rows` rows
     quantize  quantize_mse of `--rows` float32 vectors of dim 128 at 4 bits
     """
@@ -574,6 +576,28 @@ def run_case(args) -> None:
         nbytes = BATCH * KV_HEADS * args.ctx * BYTES_PER_TOKEN_HEAD
         out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
                    status=cache.decode_status())
+    elif args.case == "paged":
+        # geometry of the paged Llama-3-8B configuration: head_dim 128, K4/V3, 16-token pages, batch 64,
+        # 8 KV heads x 4 query heads, one layer; the pool holds random codes (timing only) and every
+        # sequence's pages are scattered over the pool by a random permutation
+        from turboquant_kv.kvstore import PackedKVStore
+
+        batch, kvh, qh, dim, bs, ctx = 64, 8, 32, 128, 16, args.ctx
+        kv = PackedKVStore(dim, 4, 3, 42, "dense_qr", device)
+        pages = batch * (ctx // bs)
+        gen = torch.Generator(device=device).manual_seed(1)
+        pool = torch.randint(0, 256, (pages * kvh, bs // 16, kv.record_bytes), dtype=torch.uint8, device=device,
+                             generator=gen)
+        norms = pool.view(pages * kvh, -1)[:, -128:].view(torch.float32)      # the 32 norms of every record
+        norms.copy_(torch.rand(norms.shape, device=device, generator=gen) * 8 + 4)
+        tables = torch.randperm(pages, device=device, generator=gen).to(torch.int32).view(batch, ctx // bs)
+        lens = torch.full((batch,), ctx, dtype=torch.int32, device=device)
+        q = torch.randn(batch, qh, dim, device=device, generator=gen).bfloat16()
+        o = torch.empty_like(q)
+        ms = timed(lambda: kv.decode_attention(pool, q, kvh, lens, ctx, block_tables=tables, block_size=bs, out=o))
+        nbytes = batch * kvh * ctx * (64 + 48 + 8)
+        out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                   status=kv.status(), finite=bool(torch.isfinite(o.float()).all()))
     elif args.case == "scan":
         from turboquant_kv import TurboQuantIndex
 
@@ -602,7 +626,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["decode", "scan", "quantize"],
+    ap.add_argument("--case", default=None, choices=["decode", "paged", "scan", "quantize"],
                     help="run one single-kernel case (for profilers) instead of the benchmark")
     ap.add_argument("--layers", type=int, default=LAYERS, help="--case decode: layers to build")
     ap.add_argument("--rows", type=int, default=65536, help="--case quantize: vectors")

@@ -470,64 +470,72 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
     const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
     const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
 
-    // ---- producer: one lane streams the CTA's items, one bulk copy per stage of a contiguous cache ----
+    // ---- producer warp: streams the CTA's items.  Lane 0 owns the barriers and the stage headers and
+    // issues the one bulk copy of a stage of a contiguous cache; for a paged cache every record is its own
+    // copy (pages are scattered), and the 32 lanes issue them side by side.  All lanes track the cursor.
     if (warp == WARPS) {
-        if (lane == 0) {
-            StageCursor<SR, GROUPS> cur;
-            cur.item = blockIdx.x;
-            cur.total_items = p.batch * p.kv_heads * p.nchunks;
-            cur.stride = gridDim.x;
-            cur.tiles_left = 0;
-            cur.open(p, lens);
-            bool ok = true;
-            int end_marks = 0;
-            uint32_t n = 0;
-            for (;; n++) {
-                const int s = n % NS;
-                if (n >= NS) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
-                if (!ok) break;
-                uint4* meta = reinterpret_cast<uint4*>(smem_gen + meta_addr + s * 16);
-                if (!cur.valid()) {                     // end of stream: one marker stage per consumer group
+        StageCursor<SR, GROUPS> cur;
+        cur.item = blockIdx.x;
+        cur.total_items = p.batch * p.kv_heads * p.nchunks;
+        cur.stride = gridDim.x;
+        cur.tiles_left = 0;
+        cur.open(p, lens);
+        bool ok = true;
+        int end_marks = 0;
+        uint32_t n = 0;
+        for (;; n++) {
+            const int s = n % NS;
+            if (n >= NS) {
+                if (lane == 0) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (!ok) break;
+            uint4* meta = reinterpret_cast<uint4*>(smem_gen + meta_addr + s * 16);
+            if (!cur.valid()) {                     // end of stream: one marker stage per consumer group
+                if (lane == 0) {
                     *meta = make_uint4(0, 0, F_END, 0);
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_addr + 8 * s) : "memory");
-                    if (++end_marks == GROUPS) break;
-                    continue;
                 }
-                const int nt = cur.tiles_here();
-                const int left = cur.tok_end - cur.tile0 * TILE;
+                if (++end_marks == GROUPS) break;
+                continue;
+            }
+            const int nt = cur.tiles_here();
+            const int left = cur.tok_end - cur.tile0 * TILE;
+            if (lane == 0)
                 *meta = make_uint4((uint32_t)cur.unit, (uint32_t)cur.chunk_idx,
                                    (uint32_t)nt | (cur.stage_idx < GROUPS ? F_FIRST : 0u) |
                                        (cur.stage_idx >= cur.stages - GROUPS ? F_LAST : 0u),
                                    (uint32_t)left);
-                if (nt == 0) {                          // padding stage of a short item: flags only
+            if (nt == 0) {                          // padding stage of a short item: flags only
+                if (lane == 0)
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_addr + 8 * s) : "memory");
-                    cur.next(p, lens);
-                    continue;
-                }
-                const uint32_t dst = slot_addr(s);
-                // (the consumers' reads of this slot are ordered before this write by the empty barrier)
-                mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
-                if (PAGED) {
-                    const int rpb = p.block_size / TILE;   // records per page
-                    for (int i = 0; i < nt; i++) {
-                        const int tile = cur.tile0 + i;
-                        const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
-                        const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
-                        bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, full_addr + 8 * s);
-                    }
-                } else {
-                    const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + cur.tile0;
-                    bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), full_addr + 8 * s);
-                }
                 cur.next(p, lens);
+                continue;
             }
-            if (!ok) {
-                // The consumers stopped releasing stages.  Record it and give the copies still in flight a
-                // bounded chance to land before this CTA's shared memory is released.
-                atomicExch(p.status, 1);
-                for (uint32_t i = (n > (uint32_t)NS ? n - NS : 0); i < n; i++)
-                    (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);   // (padding stages complete at once)
+            const uint32_t dst = slot_addr(s);
+            // (the consumers' reads of this slot are ordered before this write by the empty barrier)
+            if (lane == 0) mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
+            __syncwarp();
+            if (PAGED) {
+                const int rpb = p.block_size / TILE;   // records per page
+                for (int i = lane; i < nt; i += 32) {
+                    const int tile = cur.tile0 + i;
+                    const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
+                    const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
+                    bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, full_addr + 8 * s);
+                }
+            } else if (lane == 0) {
+                const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + cur.tile0;
+                bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), full_addr + 8 * s);
             }
+            cur.next(p, lens);
+        }
+        if (!ok && lane == 0) {
+            // The consumers stopped releasing stages.  Record it and give the copies still in flight a
+            // bounded chance to land before this CTA's shared memory is released.
+            atomicExch(p.status, 1);
+            for (uint32_t i = (n > (uint32_t)NS ? n - NS : 0); i < n; i++)
+                (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);   // (padding stages complete at once)
         }
         return;
     }

@@ -805,13 +805,18 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
     if (tid == 0) { surv_n = 0; tau_s = -__builtin_huge_valf(); tau_i = ID_NONE; }
     __syncthreads();
     const int L = p.lists_per_query;
-    for (int l = tid; l < L; l += blockDim.x) {
-        const float hs = cs[(int64_t)l * p.kk];
-        const int hi = ci[(int64_t)l * p.kk];
-        if (hi == ID_NONE) continue;
-        int rank = 0;
-        for (int l2 = 0; l2 < L; l2++) rank += better(cs[(int64_t)l2 * p.kk], ci[(int64_t)l2 * p.kk], hs, hi) ? 1 : 0;
-        if (rank == p.kk - 1) { tau_s = hs; tau_i = hi; }      // (ranks are distinct: at most one writer)
+    if (L <= SURV_MAX) {                    // (more lists than that: no pruning, the general path takes over)
+        // the heads go through shared memory (the survivor buffers are free until the next phase)
+        for (int l = tid; l < L; l += blockDim.x) { sv_s[l] = cs[(int64_t)l * p.kk]; sv_i[l] = ci[(int64_t)l * p.kk]; }
+        __syncthreads();
+        for (int l = tid; l < L; l += blockDim.x) {
+            const float hs = sv_s[l];
+            const int hi = sv_i[l];
+            if (hi == ID_NONE) continue;
+            int rank = 0;
+            for (int l2 = 0; l2 < L; l2++) rank += better(sv_s[l2], sv_i[l2], hs, hi) ? 1 : 0;
+            if (rank == p.kk - 1) { tau_s = hs; tau_i = hi; }      // (ranks are distinct: at most one writer)
+        }
     }
     __syncthreads();
     for (int64_t e = tid; e < ncand; e += blockDim.x) {
