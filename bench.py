@@ -19,7 +19,8 @@ One JSON line is printed by rank 0:
   value     tokens/s with everything resident in HBM: the step is captured once in a CUDA graph
             (launch-bound otherwise: 48 launches per step) and K replays are timed with CUDA events
   e2e       the same step fed from pinned host buffers: H2D of q/k/v of all layers, the step, D2H of the
-            attention output, every step
+            attention output, every step; uploads and downloads run on copy streams over two alternating
+            buffer sets, so they overlap the neighbouring steps' kernels
   roofline  HBM roofline of the dominant kernel (decode_partial_kernel); bytes per launch are the packed
             K/V rows and norms of one layer; its duration is measured with CUDA events in an extra pass
             of the same steps launched eagerly, launch by launch (events cannot be read inside a captured
@@ -234,7 +235,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
         raise SystemExit(f"--gpus must divide {KV_HEADS} KV heads")
     kvh, qh = KV_HEADS // world, Q_HEADS // world
     ctx, K, W = args.ctx, args.steps, args.warmup
-    total_steps = 3 * (K + W) + 8
+    total_steps = 3 * (K + W) + 12
 
     def barrier():
         if world > 1:
@@ -255,10 +256,14 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     v_in = torch.randn(LAYERS, BATCH, kvh, 1, HEAD_DIM, generator=gen, device=device).bfloat16()
     out = torch.empty(LAYERS, BATCH, qh, HEAD_DIM, device=device, dtype=torch.bfloat16)
 
-    def step_eager(events=None):
+    def step_eager(events=None, bufs=None):
         """One decode step: per layer, append the new token and attend (the fused three-launch call).
         With `events`, every call is split into its launches so that the streaming kernel alone sits
         between an event pair (a whole-call pair is recorded as well)."""
+        if bufs is not None:
+            for layer in range(LAYERS):
+                cache.decode_step(layer, bufs[0][layer], bufs[1][layer], bufs[2][layer], out=bufs[3][layer])
+            return
         for layer in range(LAYERS):
             if events is None:
                 cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
@@ -320,19 +325,50 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     ms_step = max_over_ranks(e0.elapsed_time(e1) / K)
 
     # ---- e2e: pinned host buffers in, attention output back, every step ----
+    # Every step copies its q/k/v from pinned host memory and its output back to pinned host memory.  The
+    # copies run on their own streams and two sets of device buffers (with a captured step each) alternate,
+    # so the upload of step i+1 and the download of step i-1 overlap the kernels of step i, as a serving
+    # loop would arrange it; events keep every buffer's upload -> compute -> download order.
     h_q, h_k, h_v = (t.cpu().pin_memory() for t in (q_in, k_in, v_in))
-    h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h_outs = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
     h2d = sum(t.numel() * t.element_size() for t in (h_q, h_k, h_v))
-    d2h = h_out.numel() * h_out.element_size()
+    d2h = h_outs[0].numel() * h_outs[0].element_size()
+    bufs = [(q_in, k_in, v_in, out), tuple(torch.empty_like(t) for t in (q_in, k_in, v_in, out))]
+    graph_b = torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph_b, stream=side):
+            step_eager(bufs=bufs[1])
+    torch.cuda.current_stream().wait_stream(side)
+    cache.seq_lens -= 1
+    graphs = [graph, graph_b]
+    main_stream = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    ev_in, ev_comp, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+    e2e_count = [0]
 
     def step_e2e(n):
         for _ in range(n):
-            q_in.copy_(h_q, non_blocking=True)
-            k_in.copy_(h_k, non_blocking=True)
-            v_in.copy_(h_v, non_blocking=True)
-            graph.replay()
-            h_out.copy_(out, non_blocking=True)
+            b = e2e_count[0] & 1
+            e2e_count[0] += 1
+            q_d, k_d, v_d, o_d = bufs[b]
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_comp[b])         # the step that last read this input set has finished
+                q_d.copy_(h_q, non_blocking=True)
+                k_d.copy_(h_k, non_blocking=True)
+                v_d.copy_(h_v, non_blocking=True)
+                ev_in[b].record(s_in)
+            main_stream.wait_event(ev_in[b])
+            main_stream.wait_event(ev_out[b])       # this output set has been downloaded
+            graphs[b].replay()
+            ev_comp[b].record(main_stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[b])
+                h_outs[b].copy_(o_d, non_blocking=True)
+                ev_out[b].record(s_out)
         cache.seq_lens += n
+        main_stream.wait_stream(s_in)
+        main_stream.wait_stream(s_out)
 
     step_e2e(W)
     barrier()

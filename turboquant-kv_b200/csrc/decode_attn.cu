@@ -199,7 +199,11 @@ struct DecodeCfg {
     static constexpr int SMALL_K = KBYTE ? 0 : LUTK_ENTRIES * 128;  // tables that need no alignment
     static constexpr int SMALL_V = VBYTE ? 0 : LUTV_ENTRIES * 128;
     static constexpr int MT = D / 16;                               // m-tiles of O^T / k-steps of the scores
+    // head_dim 64: 16 consumer warps (96 registers each).  head_dim 128 keeps twice the accumulators: 8
+    // consumer warps with four records in flight each measured faster than 12 warps with two (0.76 vs
+    // 0.85 ms per layer at batch 64 x 32,768 tokens, K4/V3).
     static constexpr int WARPS = D == 64 ? 16 : 8;                  // consumer warps
+    static constexpr int NTMAX = 4;                                 // records a warp processes at once
     static constexpr int GROUPS = 2;                                // consumer warp groups; stage n goes to group n % GROUPS
     static constexpr int WPG = WARPS / GROUPS;
     static constexpr int RPW = 4;                                   // records per warp per stage
@@ -555,7 +559,10 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         uint4 meta;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(meta.x), "=r"(meta.y), "=r"(meta.z), "=r"(meta.w) : "r"(meta_addr + s * 16));
-        if (meta.z & F_END) break;                    // end of the stream
+        if (meta.z & F_END) {                         // end of the stream (release the marker's slot as well)
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
+            break;
+        }
         const int nt = meta.z & 0xffff;
         if (meta.z & F_FIRST) {                       // this group's first stage of an item
             unit = (int)meta.x; chunk_idx = (int)meta.y;
@@ -570,7 +577,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
             const uint32_t rec = slot_addr(s) + r0 * C::REC;
             const int lv = (int)meta.w - r0 * TILE;   // valid tokens from this warp's first record on
             const int mine = min(RPW, nt - r0);
-            if (mine == 4 && lv >= 4 * TILE) {
+            if (C::NTMAX == 4 && mine == 4 && lv >= 4 * TILE) {
                 process_tiles<D, KB, VB, 4, false>(st, rec, tabK, tabV, lane, g, 4 * TILE);
             } else {
                 for (int i0 = 0; i0 < mine; i0 += 2) {
