@@ -630,7 +630,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
 // One CTA per (unit, query head of the group).  Threads are (chunk group cg) x (dimension j).  Every
 // global load that does not depend on another one is issued up front (chunk maxima and sums, the first
 // eight accumulator rows of the thread, its rows of R_v), so the kernel costs about one memory round
-// trip; the chunk weights 2^(m_c - M) are then recomputed by every thread from shared memory.
+// trip.
 // 256 threads for head_dim 64 (all CTAs of the benchmark shape are then resident at once), else 512.
 constexpr int MERGE_MAX_CHUNKS = 1024;
 constexpr int MERGE_BATCH = 16;
@@ -673,16 +673,24 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
 
     float M = NEG_INF;
     for (int c = 0; c < nch; c++) M = fmaxf(M, sm_m[c]);
+    __syncthreads();
+    // the chunk weights 2^(m_c - M) are computed once (by the threads that loaded the chunk's m and l)
+    for (int c = tid; c < nch; c += MERGE_THREADS) {
+        const float w = exp2f(sm_m[c] - M);
+        sm_m[c] = w;
+        sm_l[c] *= w;
+    }
+    __syncthreads();
     float L = 0.0f;
-    for (int c = 0; c < nch; c++) L = fmaf(exp2f(sm_m[c] - M), sm_l[c], L);
+    for (int c = 0; c < nch; c++) L += sm_l[c];
     float acc = 0.0f;
 #pragma unroll
     for (int k = 0; k < MERGE_BATCH; k++) {
         const int c = cg + k * groups;
-        if (c < nch) acc = fmaf(exp2f(sm_m[c] - M), raw[k], acc);
+        if (c < nch) acc = fmaf(sm_m[c], raw[k], acc);
     }
     for (int c = cg + MERGE_BATCH * groups; c < nch; c += groups)     // very long contexts only
-        acc = fmaf(exp2f(sm_m[c] - M), p.part_acc[(pbase + (int64_t)c * p.group) * dim + j], acc);
+        acc = fmaf(sm_m[c], p.part_acc[(pbase + (int64_t)c * p.group) * dim + j], acc);
     red[tid] = acc;
     __syncthreads();
     if (tid < dim) {
