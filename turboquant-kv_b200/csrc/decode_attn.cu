@@ -35,6 +35,12 @@ constexpr float NEG_INF = -__builtin_huge_valf();
 constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score exceeds m + 4 (log2)
 constexpr int TILE = 16;                // tokens per MMA tile
 
+// Which launches carry the attribute (bit 0 preparation, 1 streaming kernel, 2 merge).  Measured on the
+// benchmark step (1 GPU, ms per step): none 1.366, streaming + merge 1.317, all three 1.414 -- early-resident
+// preparation CTAs of the next call get in the way of the merge, so the preparation is launched plainly.
+static constexpr int PDL_MASK = 6;
+static constexpr int pdl_mask() { return PDL_MASK; }
+
 // ---- launch parameters --------------------------------------------------------------------------
 struct DecodeParams {
     const uint8_t* store;            // tiled records (tiled_layout.cuh)
@@ -104,6 +110,8 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(
     __shared__ uint32_t codes[2][128];
     const int u = blockIdx.x, b = u / kv_heads, h = u - b * kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();          // inputs may come from the previous kernel; the workspace is still read by it
+    pdl_trigger();
     if (u == 0 && threadIdx.x == 0) *status = 0;
     const bool step = key != nullptr;
     const int pos = step ? lens_in[b] : 0;
@@ -430,11 +438,9 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
+    pdl_trigger();
 
     const bool lens_in_smem = p.batch <= C::LENS_MAX;
-    if (lens_in_smem)
-        for (int i = threadIdx.x; i < p.batch; i += blockDim.x)
-            reinterpret_cast<int32_t*>(smem_gen + lens_addr)[i] = p.seq_lens[i];
     const int32_t* lens = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + lens_addr) : p.seq_lens;
     if (threadIdx.x < 16) {
         float* cf = reinterpret_cast<float*>(smem_gen + cent_addr);
@@ -470,6 +476,11 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
             }
         }
     }
+    // everything above depends on constants only; from here on the preparation kernel's output is read
+    pdl_wait();
+    if (lens_in_smem)
+        for (int i = threadIdx.x; i < p.batch; i += blockDim.x)
+            reinterpret_cast<int32_t*>(smem_gen + lens_addr)[i] = p.seq_lens[i];
     __syncthreads();
     const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
     const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
@@ -646,14 +657,20 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
     __shared__ float y[128];
     const int u = blockIdx.x / p.group, n = blockIdx.x - u * p.group;
     const int b = u / p.kv_heads, h = u - b * p.kv_heads;
+    const int tid = threadIdx.x, groups = MERGE_THREADS / dim, cg = tid / dim, j = tid - cg * dim;
+    const int rows = dim / groups;                       // rows of R_v per thread (8, 16 or 32)
+    pdl_trigger();
+    constexpr int RVN = MERGE_THREADS == 256 ? 16 : 8;
+    float rv[RVN];                                       // first RVN of this thread's R_v rows (a constant input:
+#pragma unroll                                           // fetched while the streaming kernel may still be running)
+    for (int k = 0; k < RVN; k++) rv[k] = k < rows ? Rv[(int64_t)(cg + k * groups) * dim + j] : 0.0f;
+    pdl_wait();
     const int S = p.seq_lens[b];
     // a fused step publishes the new length once nothing of this call reads the caller's array any more
     if (advance && h == 0 && n == 0 && threadIdx.x == 0) advance[b] = S;
     // every chunk contributes one partial per consumer warp of the streaming kernel
     const int nch = min(((S + p.chunk - 1) / p.chunk) * p.sets, MERGE_MAX_CHUNKS);
-    const int tid = threadIdx.x, groups = MERGE_THREADS / dim, cg = tid / dim, j = tid - cg * dim;
     const int64_t pbase = (int64_t)u * p.nchunks * p.sets * p.group + n;
-    const int rows = dim / groups;                       // rows of R_v per thread (8 or 32)
 
     for (int c = tid; c < nch; c += MERGE_THREADS) {
         sm_m[c] = p.part_m[pbase + (int64_t)c * p.group];
@@ -665,10 +682,6 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
         const int c = cg + k * groups;
         raw[k] = c < nch ? p.part_acc[(pbase + (int64_t)c * p.group) * dim + j] : 0.0f;
     }
-    constexpr int RVN = MERGE_THREADS == 256 ? 16 : 8;
-    float rv[RVN];                                       // first RVN of this thread's R_v rows
-#pragma unroll
-    for (int k = 0; k < RVN; k++) rv[k] = k < rows ? Rv[(int64_t)(cg + k * groups) * dim + j] : 0.0f;
     __syncthreads();
 
     float M = NEG_INF;
@@ -766,7 +779,7 @@ static int launch_partial(const DecodeParams& p, cudaStream_t st) {
     if (items + sm_count() >= 0x7fffffff)
         return fail(TQB_ERR_UNSUPPORTED, "decode_attention: too many (sequence, head, chunk) work items");
     const int grid = (int)std::min<int64_t>(sm_count(), items);
-    kern<<<grid, C::THREADS, C::DYN, st>>>(p);
+    TQB_CUDA(launch_pdl(pdl_mask() & 2, kern, dim3(grid), dim3(C::THREADS), C::DYN, st, p));
     return check_launch("decode_partial");
 }
 
@@ -846,8 +859,9 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
 
     int32_t* lens_now = reinterpret_cast<int32_t*>(ws + w.off_lens);
     if (key) p.seq_lens = lens_now;
+    cudaError_t launch_err = cudaSuccess;
     if (g_phases & 1) {
-#define TQB_PREP(T, NQ) decode_prepare_kernel<T, NQ><<<units, 256, 0, st>>>(                                       \
+#define TQB_PREP(T, NQ) launch_err = launch_pdl(pdl_mask() & 1, decode_prepare_kernel<T, NQ>, dim3(units), dim3(256), 0, st,            \
         (const T*)query, (const T*)key, (const T*)value, kv_stride, q_heads, kv_heads, group, dim, rot_k, rot_v, \
         bnd_k, bnd_v, kbits, vbits, scale, const_cast<uint8_t*>(store), max_seq, seq_lens, lens_now, qfrag, p.status)
         switch (q_dtype) {
@@ -857,6 +871,7 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
             default: return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
         }
 #undef TQB_PREP
+        TQB_CUDA(launch_err);
         if (int e = check_launch("decode_prepare")) return e;
     }
 
@@ -868,7 +883,7 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
     }
 
     if (!(g_phases & 4)) return TQB_OK;
-#define TQB_MERGE(T, TH) decode_merge_kernel<T, TH><<<units * group, TH, 0, st>>>(p, dim, rot_v, (T*)out, lens_mut)
+#define TQB_MERGE(T, TH) launch_err = launch_pdl(pdl_mask() & 4, decode_merge_kernel<T, TH>, dim3(units * group), dim3(TH), 0, st, p, dim, rot_v, (T*)out, lens_mut)
     switch (out_dtype) {
         case TQB_F32: if (dim == 64) TQB_MERGE(float, 256); else TQB_MERGE(float, 512); break;
         case TQB_F16: if (dim == 64) TQB_MERGE(__half, 256); else TQB_MERGE(__half, 512); break;
@@ -876,6 +891,7 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
         default: return fail(TQB_ERR_INVALID, "decode_attention: unknown output dtype %d", out_dtype);
     }
 #undef TQB_MERGE
+    TQB_CUDA(launch_err);
     return check_launch("decode_merge");
 }
 }  // namespace tqb

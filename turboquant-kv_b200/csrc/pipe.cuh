@@ -134,4 +134,23 @@ __device__ __forceinline__ uint32_t entry_addr(const uint32_t (&w)[NW], int bit,
     return lut_offset<NW, 7>(w, bit, bits) + tab;
 }
 
+// Programmatic dependent launch: the three kernels of a call are launched so that each may be set up
+// while its predecessor still runs.  A kernel lets its successor launch early (pdl_trigger at its start) and
+// waits (pdl_wait) for the complete predecessor -- all its memory writes included -- before it touches
+// anything a predecessor writes or reads.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch with (enable != 0) or without the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(int enable, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = enable ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 }  // namespace tqb

@@ -27,7 +27,6 @@
 #include "tiled_layout.cuh"
 
 #include <mutex>
-#include <cstdlib>
 
 namespace tqb {
 
@@ -135,6 +134,8 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
     float* qr = sm + p.dim;             // QG * dim (rotated queries); the raw queries follow
     __shared__ float qmax[QG];
     const int grp = blockIdx.x;
+    pdl_wait();
+    pdl_trigger();
     if (grp == 0 && threadIdx.x == 0) *p.status = 0;
     // all QG queries of the group go through one pass over R: row j is read once (128-bit loads), each
     // query keeps its own sum, accumulated in k order with separate multiply and add
@@ -501,6 +502,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
 
+    pdl_trigger();
     if (threadIdx.x < 16)
         reinterpret_cast<float*>(smem_gen + cent_addr)[threadIdx.x] =
             threadIdx.x < (1 << BITS) ? p.cent[threadIdx.x] * CENT_SCALE : 0.0f;
@@ -522,6 +524,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
             *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + 128 + lane * 4) = pack_half2(a - ah, b - bh);
         }
     }
+    pdl_wait();                                      // the query fragments come from the preparation kernel
     __syncthreads();
 
     const int64_t nrec = p.n / SCAN_TILE;            // full records; the last n % 16 rows belong to the merge kernel
@@ -551,15 +554,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
                 const int nt = (nrec - r0) < SR ? (int)(nrec - r0) : SR;
                 *meta = make_uint2((uint32_t)r0, (uint32_t)nt);
                 mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
-                {
-                    const int parts = max(1, p.combine >> 8);          // experiment: copies per stage
-                    const int per = (nt + parts - 1) / parts;
-                    for (int r = 0; r < nt; r += per) {
-                        const int c = min(per, nt - r);
-                        bulk_g2s(slot_addr(s) + r * C::REC, p.records + (r0 + r) * C::REC, (uint32_t)(c * C::REC),
-                                 full_addr + 8 * s);
-                    }
-                }
+                bulk_g2s(slot_addr(s), p.records + r0 * C::REC, (uint32_t)(nt * C::REC), full_addr + 8 * s);
                 st += gridDim.x;
             }
             if (!ok) {
@@ -587,7 +582,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         const int myq = grp * QG + t;                 // the query whose scores this lane receives
         const float qsc = myq < p.nq ? p.qscale[myq] : 0.0f;
         ScanThreshold thr{-__builtin_huge_valf(), ID_NONE};
-        const bool live = myq < p.nq && !(p.combine & 2);
+        const bool live = myq < p.nq;
         const int r0w = RPW * (warp % WPG);
         int s = warp / WPG - GROUPS;                  // slot of this group's current stage and its parity
         uint32_t par = 0;
@@ -607,8 +602,6 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
             }
             const int nt = (int)meta.y;
             const int mine = min(RPW, nt - r0w);
-            if (p.combine & 4) { thr.s += ldsf(slot_addr(s) + lane * 4); }
-            else
             for (int i0 = 0; i0 < mine; i0 += NT) {
                 const uint32_t rec = slot_addr(s) + (r0w + i0) * C::REC;
                 float acc[NT][4];
@@ -789,6 +782,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
     __shared__ float cur_s;
     __shared__ int cur_i;
     const int q = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
+    pdl_wait();
     for (int e = tid; e < p.dim * levels; e += blockDim.x)
         T[e] = __fmul_rn(p.qrot[(int64_t)q * p.dim + e / levels], p.cent[e % levels]);
     const int64_t ncand = (int64_t)p.lists_per_query * p.kk;
@@ -1044,7 +1039,8 @@ static int launch_scan_records(const ScanParams& p, int ngroups, int grid_x, cud
     auto kern = scan_records_kernel<D, BITS>;
     TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
     dim3 grid(grid_x, ngroups);
-    kern<<<grid, C::THREADS, C::DYN, st>>>(p);
+    // (programmatic dependent launch: the table build overlaps the end of the preparation kernel)
+    TQB_CUDA(launch_pdl(1, kern, grid, dim3(C::THREADS), (size_t)C::DYN, st, p));
     return check_launch("scan_records");
 }
 
@@ -1086,8 +1082,7 @@ extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t
     p.cand_s = reinterpret_cast<float*>(ws + pl.off_cs);
     p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
     p.out_scores = out_scores; p.out_ids = out_ids;
-    p.combine = (rec_combine(pl.kk) ? 1 : 0) | (getenv("TQB_NOOFFER") ? 2 : 0) | (getenv("TQB_PROBE") ? 4 : 0) |
-                (getenv("TQB_SPLIT") ? atoi(getenv("TQB_SPLIT")) << 8 : 0);
+    p.combine = rec_combine(pl.kk) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int grid_x = sm_count();
     p.lists_per_query = grid_x * (p.combine ? 1 : 16);
@@ -1101,7 +1096,7 @@ extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t
     if (e) return e;
     const size_t msmem = sizeof(float) * (size_t)dim * (1 << bits);
     TQB_CUDA(cudaFuncSetAttribute(scan_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(msmem, 48 * 1024)));
-    scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
+    TQB_CUDA(launch_pdl(1, scan_merge_kernel, dim3(nq), dim3(MERGE_THREADS), msmem, st, p));
     return check_launch("scan_merge");
 }
 
