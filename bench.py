@@ -506,6 +506,28 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         torch.cuda.empty_cache()
     res["decode_context_sweep"] = sweep
 
+    # ---- paged decode, Llama-3-8B geometry, ONE layer on random codes (kernel-level figure) ----
+    def timed_events(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / 10
+
+    ms, nbytes, status, finite = paged_layer(torch, device, kvh, qh, 32768, timed_events)
+    ms = sync_max(ms)
+    res["paged_decode_layer"] = {
+        "geometry": "head_dim 128, K4/V3, 16-token pages, batch 64, context 32768, %d KV heads x 4 query heads per GPU" % kvh,
+        "ms_per_layer_call": ms, "hbm_gbs_per_gpu": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+        "tokens_per_s_if_32_layers": 64 / (32 * ms * 1e-3), "status": status, "finite": finite,
+        "note": "one layer on random codes, eager launches; the 32-layer figure is an extrapolation, not a measurement"}
+    torch.cuda.empty_cache()
+
     # ---- 4-bit index scan, 10M x 128 rows sharded by rows, top-10 ----
     n_total, dim, nq, k = args.scan_rows, 128, args.scan_queries, 10
     lo, hi = shard_rows(n_total, world, rank)
@@ -571,6 +593,30 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     return res
 
 
+def paged_layer(torch, device, kvh: int, qh: int, ctx: int, timed):
+    """One layer of paged decode attention in the geometry of the paged Llama-3-8B configuration: head_dim
+    128, K4/V3, 16-token pages, batch 64, `kvh` KV heads x 4 query heads.  The pool holds random codes
+    (timing only) and every sequence's pages are scattered over the pool by a random permutation.
+    Returns (ms per call, algorithmic bytes, status word, output finite)."""
+    from turboquant_kv.kvstore import PackedKVStore
+
+    batch, dim, bs = 64, 128, 16
+    kv = PackedKVStore(dim, 4, 3, 42, "dense_qr", device)
+    pages = batch * (ctx // bs)
+    gen = torch.Generator(device=device).manual_seed(1)
+    pool = torch.randint(0, 256, (pages * kvh, bs // 16, kv.record_bytes), dtype=torch.uint8, device=device,
+                         generator=gen)
+    norms = pool.view(pages * kvh, -1)[:, -128:].view(torch.float32)      # the 32 norms of every record
+    norms.copy_(torch.rand(norms.shape, device=device, generator=gen) * 8 + 4)
+    tables = torch.randperm(pages, device=device, generator=gen).to(torch.int32).view(batch, ctx // bs)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=device)
+    q = torch.randn(batch, qh, dim, device=device, generator=gen).bfloat16()
+    o = torch.empty_like(q)
+    ms = timed(lambda: kv.decode_attention(pool, q, kvh, lens, ctx, block_tables=tables, block_size=bs, out=o))
+    nbytes = batch * kvh * ctx * (64 + 48 + 8)
+    return ms, nbytes, kv.status(), bool(torch.isfinite(o.float()).all())
+
+
 def run_case(args) -> None:
     """Single-kernel cases for profilers: a few eager launches of one hot kernel, timed with CUDA events.
 
@@ -613,27 +659,9 @@ def run_case(args) -> None:
         out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
                    status=cache.decode_status())
     elif args.case == "paged":
-        # geometry of the paged Llama-3-8B configuration: head_dim 128, K4/V3, 16-token pages, batch 64,
-        # 8 KV heads x 4 query heads, one layer; the pool holds random codes (timing only) and every
-        # sequence's pages are scattered over the pool by a random permutation
-        from turboquant_kv.kvstore import PackedKVStore
-
-        batch, kvh, qh, dim, bs, ctx = 64, 8, 32, 128, 16, args.ctx
-        kv = PackedKVStore(dim, 4, 3, 42, "dense_qr", device)
-        pages = batch * (ctx // bs)
-        gen = torch.Generator(device=device).manual_seed(1)
-        pool = torch.randint(0, 256, (pages * kvh, bs // 16, kv.record_bytes), dtype=torch.uint8, device=device,
-                             generator=gen)
-        norms = pool.view(pages * kvh, -1)[:, -128:].view(torch.float32)      # the 32 norms of every record
-        norms.copy_(torch.rand(norms.shape, device=device, generator=gen) * 8 + 4)
-        tables = torch.randperm(pages, device=device, generator=gen).to(torch.int32).view(batch, ctx // bs)
-        lens = torch.full((batch,), ctx, dtype=torch.int32, device=device)
-        q = torch.randn(batch, qh, dim, device=device, generator=gen).bfloat16()
-        o = torch.empty_like(q)
-        ms = timed(lambda: kv.decode_attention(pool, q, kvh, lens, ctx, block_tables=tables, block_size=bs, out=o))
-        nbytes = batch * kvh * ctx * (64 + 48 + 8)
+        ms, nbytes, status, finite = paged_layer(torch, device, 8, 32, args.ctx, timed)
         out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                   status=kv.status(), finite=bool(torch.isfinite(o.float()).all()))
+                   status=status, finite=finite)
     elif args.case == "scan":
         from turboquant_kv import TurboQuantIndex
 
