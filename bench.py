@@ -533,12 +533,14 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     lo, hi = shard_rows(n_total, world, rank)
     index = ShardedTurboQuantIndex(dim, bit_width=4, seed=42, id_offset=lo, device=device)
     gam = torch.distributions.Gamma(torch.tensor(0.5, device=device), torch.tensor(1.0 / 40.0, device=device))
-    chunk = 1_000_000
+    # the database is generated in global chunks of 250,000 rows, chunk c from seed 1000 + c, so that
+    # every shard count sees the same 10 M rows (a shard takes the part of each chunk that falls in its range)
+    chunk = 250_000
     t_add = 0.0
-    for c0 in range(lo, hi, chunk):
-        torch.manual_seed(1000 + c0 // chunk)
-        rows = min(chunk, hi - c0)
-        x = gam.sample((rows, dim)).clamp_(0, 255).round_()
+    for c in range(lo // chunk, (hi + chunk - 1) // chunk):
+        torch.manual_seed(1000 + c)
+        x = gam.sample((min(chunk, n_total - c * chunk), dim)).clamp_(0, 255).round_()
+        x = x[max(lo - c * chunk, 0): hi - c * chunk].contiguous()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         index.add(x)

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(
         const int n = idx / dim, k = idx - n * dim;
         vec[n][k] = to_f32<T>(q[((int64_t)b * q_heads + h * group + n) * dim + k]);
     }
-    if (step && warp >= 6) {                   // warps 6, 7: norm and unit vector of the key, the value
+    if (step && (warp == 6 || warp == 7)) {    // warps 6, 7: norm and unit vector of the key, the value
         const int which = warp - 6;
         const T* x = (which ? value : key) + (int64_t)u * kv_stride;
         float v[NQ], ss = 0.0f;
