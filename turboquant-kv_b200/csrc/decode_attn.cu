@@ -231,6 +231,7 @@ struct DecodeCfg {
     static constexpr int NS_FIT = SLOTS_A + SLOTS_B;
     static constexpr int NS = NS_FIT > 8 ? 8 : NS_FIT;              // stages in the ring
     static_assert(NS >= 2, "shared memory: the ring needs at least two stages");
+    static_assert(SR <= 32, "a paged stage is issued as one copy per producer lane");
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -500,6 +501,15 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         uint32_t n = 0;
         for (;; n++) {
             const int s = n % NS;
+            // paged cache: this lane's page of the coming stage is looked up before the wait for the slot,
+            // so that the table read's latency hides behind it
+            int64_t my_rec = -1;
+            if (PAGED && cur.valid() && lane < cur.tiles_here()) {
+                const int rpb = p.block_size / TILE;   // records per page
+                const int tile = cur.tile0 + lane;
+                const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
+                my_rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
+            }
             if (n >= NS) {
                 if (lane == 0) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -531,14 +541,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
             // (the consumers' reads of this slot are ordered before this write by the empty barrier)
             if (lane == 0) mbar_expect_tx(full_addr + 8 * s, (uint32_t)(nt * C::REC));
             __syncwarp();
-            if (PAGED) {
-                const int rpb = p.block_size / TILE;   // records per page
-                for (int i = lane; i < nt; i += 32) {
-                    const int tile = cur.tile0 + i;
-                    const int blk = p.block_tables[(int64_t)cur.b * p.max_blocks + tile / rpb];
-                    const int64_t rec = ((int64_t)blk * p.kv_heads + cur.h) * rpb + tile % rpb;
-                    bulk_g2s(dst + i * C::REC, p.store + rec * C::REC, C::REC, full_addr + 8 * s);
-                }
+            if (PAGED) {                            // (a stage has at most 32 records: one per lane)
+                if (lane < nt) bulk_g2s(dst + lane * C::REC, p.store + my_rec * C::REC, C::REC, full_addr + 8 * s);
             } else if (lane == 0) {
                 const int64_t rec = (int64_t)cur.unit * (p.max_seq / TILE) + cur.tile0;
                 bulk_g2s(dst, p.store + rec * C::REC, (uint32_t)(nt * C::REC), full_addr + 8 * s);
