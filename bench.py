@@ -528,6 +528,59 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         "note": "one layer on random codes, eager launches; the 32-layer figure is an extrapolation, not a measurement"}
     torch.cuda.empty_cache()
 
+    # ---- quantise: MSE 4-bit round trip (65,536 unit vectors, d = 128) and Prod 3-bit estimator ----
+    if rank == 0:
+        from turboquant_kv import dequantize_mse, dequantize_prod, quantize_mse, quantize_prod
+        from turboquant_kv.reference import _make_qjl_matrix, lloyd_max_codebook, make_rotation_matrix
+
+        # the constants are made once (host-side QR / Lloyd-Max), as the cache and index classes do
+        rot = make_rotation_matrix(128, 42).to(device)
+        cb4 = tuple(t.to(device) for t in lloyd_max_codebook(4, 128))
+        cb2 = tuple(t.to(device) for t in lloyd_max_codebook(2, 128))
+        S = _make_qjl_matrix(128, 128, 42, device)
+
+        def timed_ms(fn, reps=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        g0 = torch.Generator(device=device).manual_seed(0)
+        x = torch.randn(65536, 128, generator=g0, device=device)
+        x = x / x.norm(dim=-1, keepdim=True)
+        ms_q = timed_ms(lambda: quantize_mse(x, 4, rotation=rot, codebook=cb4))
+        pk, nm = quantize_mse(x, 4, rotation=rot, codebook=cb4)
+        ms_d = timed_ms(lambda: dequantize_mse(pk, nm, 4, 128, rotation=rot, codebook=cb4))
+        mse = float(((dequantize_mse(pk, nm, 4, 128, rotation=rot, codebook=cb4) - x) ** 2).sum(-1).mean())
+        # Prod: rows with per-coordinate variances log-uniform in [0.1, 10], L2-normalised (shared variance vector)
+        g1 = torch.Generator(device=device).manual_seed(1)
+        sig = torch.exp(torch.empty(128, device=device).uniform_(math.log(0.1), math.log(10.0), generator=g1)).sqrt()
+        db = torch.randn(1_000_000, 128, generator=g1, device=device) * sig
+        db = db / db.norm(dim=-1, keepdim=True)
+        qs = torch.randn(1024, 128, generator=g1, device=device) * sig
+        qs = qs / qs.norm(dim=-1, keepdim=True)
+        ms_p = timed_ms(lambda: quantize_prod(db, 3, rotation=rot, codebook=cb2, S_matrix=S), reps=3)
+        mp, sg, rn, nr = quantize_prod(db[:100_000], 3, rotation=rot, codebook=cb2, S_matrix=S)
+        est = qs @ dequantize_prod(mp, sg, rn, nr, 3, 128, rotation=rot, codebook=cb2, S_matrix=S).t()
+        exact = qs @ db[:100_000].t()
+        slope = float((est * exact).sum() / (exact * exact).sum())
+        res["quantize"] = {
+            "mse_4bit_d128_vectors_per_s": 65536 / (ms_q * 1e-3), "mse_4bit_quantize_ms": ms_q,
+            "mse_4bit_dequantize_ms": ms_d, "mse_4bit_tflops_fp32": 2 * 128 * 128 * 65536 / (ms_q * 1e-3) / 1e12,
+            "mse_4bit_per_vector_squared_error": mse,
+            "prod_3bit_d128_vectors_per_s": 1_000_000 / (ms_p * 1e-3),
+            "prod_3bit_estimator_bias": float((est - exact).mean()), "prod_3bit_estimator_slope": slope,
+            "note": "rank 0 only; the rotation is an fp32 FMA contraction (codes must match float32 upstream "
+                    "arithmetic bit for bit), so the tensor pipe is idle in these kernels"}
+        del db, x, est, exact
+        torch.cuda.empty_cache()
+
     # ---- 4-bit index scan, 10M x 128 rows sharded by rows, top-10 ----
     n_total, dim, nq, k = args.scan_rows, 128, args.scan_queries, 10
     lo, hi = shard_rows(n_total, world, rank)
