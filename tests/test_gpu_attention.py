@@ -296,6 +296,42 @@ def test_paged_decode_with_ragged_lengths(orc):
         attention_close(out[b:b + 1].cpu().numpy(), ref)
 
 
+def test_decode_with_empty_and_ragged_sequences(orc):
+    """Sequences of length 0 give zero rows; the others attend over exactly their own tokens."""
+    from turboquant_kv.kvstore import PackedKVStore
+    from turboquant_kv import _native as N
+
+    kv_heads, group, dim, pitch = 2, 4, 64, 64
+    lens = [0, 37, 0, 64, 5]
+    batch = len(lens)
+    kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
+    store = kv.alloc(batch * kv_heads, pitch)
+    k, v = _fill(batch, kv_heads, pitch, dim, seed=21)
+    rm = N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1)              # row (unit, t) -> slot unit * pitch + t
+    kv.append(store, k.cuda(), v.cuda(), rm)
+    q = torch.randn(batch, kv_heads * group, dim, generator=torch.Generator().manual_seed(4))
+    seq = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    out = kv.decode_attention(store, q.cuda(), kv_heads, seq, max(lens), pitch=pitch).cpu().numpy()
+    assert kv.status() == 0
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(2, dim)
+    for b, l in enumerate(lens):
+        if l == 0:
+            assert not out[b].any()
+            continue
+        kp, kn = orc.quantize_mse(k[b, :, :l].reshape(-1, dim).numpy(), 4, rk, bk)
+        vp, vn = orc.quantize_mse(v[b, :, :l].reshape(-1, dim).numpy(), 2, rv, bv)
+        ref = orc.decode_attention(q[b:b + 1].numpy(), kp.reshape(1, kv_heads, l, -1), kn.reshape(1, kv_heads, l),
+                                   vp.reshape(1, kv_heads, l, -1), vn.reshape(1, kv_heads, l),
+                                   np.array([l], np.int32), rk, ck, 4, rv, cv, 2)
+        attention_close(out[b:b + 1], ref)
+    # nothing to attend to at all: every row is zero
+    none = kv.decode_attention(store, q.cuda(), kv_heads, torch.zeros(batch, dtype=torch.int32, device="cuda"), 0,
+                               pitch=pitch)
+    assert not none.cpu().numpy().any()
+
+
 def test_protected_layers_and_upstream_cache_checks():
     """The behaviours upstream tests/test_cache.py pins: incremental lengths, compression ratio in (3, 10),
     fp16-exact protected layers, outlier_channels accepted."""

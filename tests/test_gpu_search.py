@@ -187,3 +187,38 @@ def test_row_sharded_search_merges_to_the_global_answer(orc):
         parts_i.append(i)
     got_s, got_i = merge_topk(torch.stack(parts_s, 1), torch.stack(parts_i, 1), 10)
     assert torch.equal(got_i, want_i) and torch.equal(got_s, want_s)
+
+
+@pytest.mark.parametrize("dim,bits", [(64, 2), (64, 3), (64, 4), (128, 2), (128, 3), (128, 4)])
+def test_index_records_hold_exactly_the_upstream_rows(dim, bits):
+    """The index stores key-only 16-row records; exported, they are the rows quantize_mse produces, and
+    rows imported into records come back unchanged (any row count, including a partial last record)."""
+    from turboquant_kv import TurboQuantIndex, _native as N, quantize_mse
+
+    rng = np.random.default_rng(dim + bits)
+    n = 1000 + 7
+    x = torch.from_numpy(rng.standard_normal((n, dim)).astype(np.float32)).cuda()
+    idx = TurboQuantIndex(dim=dim, bit_width=bits, seed=7, device="cuda")
+    idx.add(x[:333])
+    idx.add(x[333:])                                   # a second add starts in the middle of a record
+    assert idx._use_records and idx.n_vectors == n
+    packed, norms = quantize_mse(x, bits, rotation=idx._rotation, codebook=idx._codebook)
+    assert torch.equal(idx._packed_codes, packed)
+    assert torch.equal(idx._norms, norms)
+    # import -> export round trip through the C ABI on random codes
+    L = N.lib()
+    rec_bytes = L.tqb_kv_record_bytes(dim, bits, 0)
+    assert rec_bytes == 2 * dim * bits + 64
+    codes = torch.from_numpy(rng.integers(0, 256, size=(n, bits * dim // 8), dtype=np.uint8)).cuda()
+    nrm = torch.from_numpy(rng.random(n).astype(np.float32)).cuda()
+    store = torch.zeros(((n + 15) // 16) * rec_bytes, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    N.check(L.tqb_kv_import(store.data_ptr(), n, dim, bits, 0, None, codes.data_ptr(), nrm.data_ptr(), None, None, st))
+    back_c, back_n = torch.empty_like(codes), torch.empty_like(nrm)
+    N.check(L.tqb_kv_export(store.data_ptr(), n, dim, bits, 0, None, back_c.data_ptr(), back_n.data_ptr(), None, None, st))
+    torch.cuda.synchronize()
+    assert torch.equal(back_c, codes) and torch.equal(back_n, nrm)
+    # key-only records have no value rows
+    rc = L.tqb_kv_export(store.data_ptr(), n, dim, bits, 0, None, back_c.data_ptr(), back_n.data_ptr(),
+                         back_c.data_ptr(), None, st)
+    assert rc != 0 and "key-only" in L.tqb_last_error().decode()
