@@ -150,11 +150,13 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
         float s[QG];
 #pragma unroll
         for (int jq = 0; jq < QG; jq++) s[jq] = 0.0f;
-#pragma unroll 4
+        const int nvalid = min(QG, p.nq - grp * QG);     // queries of this group that exist
+#pragma unroll 8
         for (int k4 = 0; k4 < p.dim / 4; k4++) {
             const float4 r = __ldg(row + k4);
 #pragma unroll
             for (int jq = 0; jq < QG; jq++) {
+                if (jq >= nvalid) break;
                 const float* qv = qin_all + jq * p.dim + 4 * k4;
                 s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[0], r.x));
                 s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[1], r.y));
