@@ -185,3 +185,24 @@ def test_row_sharded_merge_on_two_gloo_ranks(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=280)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert r.stdout.count("ok") == 2
+
+
+def test_vllm_v1_backend_conforms_to_the_installed_interface():
+    """The v1 adapter subclasses the installed vLLM's abstract classes and is instantiable (no GPU work)."""
+    v1 = pytest.importorskip("turboquant_kv.vllm_plugin.v1_backend")
+    from vllm.v1.attention.backend import AttentionBackend, AttentionImpl, AttentionMetadataBuilder
+
+    B = v1.TurboQuantV1Backend
+    assert issubclass(B, AttentionBackend) and B.get_name() == "TURBOQUANT"
+    assert issubclass(B.get_impl_cls(), AttentionImpl) and issubclass(B.get_builder_cls(), AttentionMetadataBuilder)
+    assert B.get_kv_cache_shape(7, 32, 8, 64) == (7, 8, 2 * (2 * 64 * 6 + 128))
+    assert B.get_kv_cache_block_dim(16, 8, 128) == 0
+    assert B.supports_block_size(16) and not B.supports_block_size(8) and not B.supports_head_size(96)
+    with pytest.raises(ValueError):
+        B.get_kv_cache_shape(7, 24, 8, 64)
+    impl = B.get_impl_cls()(32, 64, 0.125, 8)
+    assert impl.num_kv_heads == 8 and impl.scale == 0.125
+    with pytest.raises(NotImplementedError):
+        B.get_impl_cls()(32, 64, 0.125, 8, sliding_window=128)
+    builder = B.get_builder_cls()(None, ["l0"], None, "cpu")
+    assert builder.layer_names == ["l0"]
