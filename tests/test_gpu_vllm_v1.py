@@ -89,5 +89,12 @@ def test_v1_backend_prefill_decode_and_mixed_batches(orc, dim, kb, vb):
         run([(20, 37), (5, 6), (64, 65)])                   # mixed: chunked prefill + two decodes
         run([(37, 38), (6, 7), (65, 66)])                   # pure decode batch -> fused paged kernel
         run([(38, 40), (7, 8), (66, 67)])                   # a two-token query (speculative verification shape)
+        # the library fallback for oversized expansions gives the same answers
+        K2 = [k.clone() for k in K]
+        impl.MAX_EXPANDED_TABLE = 0
+        cache.zero_()
+        run([(0, 20), (0, 5), (0, 64)])
+        run([(20, 37), (5, 6), (64, 65)])
+        assert all(torch.equal(a, b) for a, b in zip(K, K2))
     finally:
         B.configure()

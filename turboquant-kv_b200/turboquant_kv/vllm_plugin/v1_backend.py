@@ -14,10 +14,11 @@ interface the installed engine really has:
 The KV cache of a layer is one uint8 tensor ``(num_blocks, kv_heads, block_size / 16 * record_bytes)``:
 the 16-token records of ``kvstore.PackedKVStore`` (keys ``KEY_BITS``, values ``VALUE_BITS``), page-major,
 so vLLM's block ids and slot mapping address it directly.  Requests with one new token (decode) run the
-fused paged decode kernel.  Requests with several new tokens (prefill, chunked prefill, speculative
-verification) take a library path: their cached rows are exported and dequantised and
-``torch.nn.functional.scaled_dot_product_attention`` runs causally over them -- correct but not fast;
-a fused prefill kernel over packed K/V is not part of this build.
+fused paged decode kernel.  Batches with several new tokens per request (prefill, chunked prefill,
+speculative verification) run the same kernel with every query token as a sequence of its own (its
+request's block-table row, its causal prefix as the length): nothing is dequantised, but every token
+streams its prefix again -- right for short chunks, quadratic for long prompts.  Beyond a size limit a
+library path (export + dequantise + ``scaled_dot_product_attention``) takes over.
 
 vLLM is imported when this module is imported; nothing else in the package depends on it.
 """
@@ -140,6 +141,9 @@ class TurboQuantV1Impl(AttentionImpl[TurboQuantV1Metadata]):
         self.kv_cache_dtype = kv_cache_dtype
         self._kv: Optional[PackedKVStore] = None
 
+    # largest (tokens x blocks per request) table the multi-token path materialises (int32 entries)
+    MAX_EXPANDED_TABLE = 1 << 26
+
     def _store(self, device) -> PackedKVStore:
         if self._kv is None:
             B = TurboQuantV1Backend
@@ -187,7 +191,26 @@ class TurboQuantV1Impl(AttentionImpl[TurboQuantV1Metadata]):
                                               block_size=block_size, scale=self.scale))
             return output
 
-        # 2b. requests with several new tokens: dequantise the request's rows, causal attention in torch
+        # 2b. requests with several new tokens (prefill chunks, speculative verification): every query token is
+        # handed to the fused kernel as a sequence of its own -- the request's block-table row and its causal
+        # prefix as the length -- so nothing is dequantised.  (Each token streams its prefix again; a kernel
+        # that shares the stream between the tokens of a request is not part of this build.)
+        if n * bt.shape[1] <= self.MAX_EXPANDED_TABLE:
+            qsl = md.query_start_loc.to(torch.int64)
+            qlens = qsl[1:md.num_reqs + 1] - qsl[:md.num_reqs]
+            req = torch.repeat_interleave(torch.arange(md.num_reqs, device=q.device), qlens, output_size=n)
+            if md.causal:
+                pos = torch.arange(n, device=q.device) - qsl[req]
+                tok_lens = (lens.to(torch.int64)[req] - qlens[req] + pos + 1).to(torch.int32)
+            else:
+                tok_lens = lens[req]
+            tok_tables = bt[req].contiguous()
+            res = kv.decode_attention(pool, q, HK, tok_lens.contiguous(), md.max_seq_len, block_tables=tok_tables,
+                                      block_size=block_size, scale=self.scale)
+            out.copy_(res)
+            return output
+
+        # 2c. fallback for very large expansions: dequantise the request's rows, causal attention in torch
         starts = md.query_start_loc_cpu.tolist()
         lens_cpu = lens.cpu().tolist()
         group = H // HK
