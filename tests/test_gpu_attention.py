@@ -296,6 +296,29 @@ def test_paged_decode_with_ragged_lengths(orc):
         attention_close(out[b:b + 1].cpu().numpy(), ref)
 
 
+def test_fused_step_on_a_full_unit_reports_status_3():
+    """The device-side guard: a sequence already at its pitch stores nothing, keeps its length and raises
+    status 3; the other sequences of the batch advance normally."""
+    from turboquant_kv.kvstore import PackedKVStore
+    from turboquant_kv import _native as N
+
+    kv_heads, group, dim, pitch = 2, 4, 64, 32
+    kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
+    store = kv.alloc(2 * kv_heads, pitch)
+    k, v = _fill(2, kv_heads, pitch, dim, seed=31)
+    kv.append(store, k.cuda(), v.cuda(), N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1))
+    lens = torch.tensor([pitch, 7], dtype=torch.int32, device="cuda")      # sequence 0 is full
+    before = store.clone()
+    q = torch.randn(2, kv_heads * group, dim).cuda()
+    newk, newv = torch.randn(2, kv_heads, dim).cuda(), torch.randn(2, kv_heads, dim).cuda()
+    out = kv.decode_step(store, q, newk, newv, kv_heads, lens, pitch, pitch)
+    assert kv.status() == 3
+    assert lens.tolist() == [pitch, 8]
+    units0 = slice(0, kv_heads)                                             # records of sequence 0 untouched
+    assert torch.equal(store[units0], before[units0]) and not torch.equal(store[kv_heads:], before[kv_heads:])
+    assert torch.isfinite(out).all()
+
+
 def test_decode_with_empty_and_ragged_sequences(orc):
     """Sequences of length 0 give zero rows; the others attend over exactly their own tokens."""
     from turboquant_kv.kvstore import PackedKVStore
