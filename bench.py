@@ -648,7 +648,7 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     return res
 
 
-def paged_layer(torch, device, kvh: int, qh: int, ctx: int, timed):
+def paged_layer(torch, device, kvh: int, qh: int, ctx: int, timed, contiguous: bool = False):
     """One layer of paged decode attention in the geometry of the paged Llama-3-8B configuration: head_dim
     128, K4/V3, 16-token pages, batch 64, `kvh` KV heads x 4 query heads.  The pool holds random codes
     (timing only) and every sequence's pages are scattered over the pool by a random permutation.
@@ -667,7 +667,11 @@ def paged_layer(torch, device, kvh: int, qh: int, ctx: int, timed):
     lens = torch.full((batch,), ctx, dtype=torch.int32, device=device)
     q = torch.randn(batch, qh, dim, device=device, generator=gen).bfloat16()
     o = torch.empty_like(q)
-    ms = timed(lambda: kv.decode_attention(pool, q, kvh, lens, ctx, block_tables=tables, block_size=bs, out=o))
+    if contiguous:      # the same records read as one contiguous cache (unit = sequence x head, pitch = ctx)
+        ms = timed(lambda: kv.decode_attention(pool.view(batch * kvh, ctx // 16, kv.record_bytes), q, kvh, lens, ctx,
+                                               pitch=ctx, out=o))
+    else:
+        ms = timed(lambda: kv.decode_attention(pool, q, kvh, lens, ctx, block_tables=tables, block_size=bs, out=o))
     nbytes = batch * kvh * ctx * (64 + 48 + 8)
     return ms, nbytes, kv.status(), bool(torch.isfinite(o.float()).all())
 
@@ -714,8 +718,8 @@ def run_case(args) -> None:
         out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
                    status=cache.decode_status())
     elif args.case == "paged":
-        ms, nbytes, status, finite = paged_layer(torch, device, 8, 32, args.ctx, timed)
-        out.update(ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
+        ms, nbytes, status, finite = paged_layer(torch, device, 8, 32, args.ctx, timed, args.contiguous)
+        out.update(contiguous=bool(args.contiguous), ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
                    status=status, finite=finite)
     elif args.case == "scan":
         from turboquant_kv import TurboQuantIndex
@@ -749,6 +753,8 @@ def main() -> None:
                     help="run one single-kernel case (for profilers) instead of the benchmark")
     ap.add_argument("--layers", type=int, default=LAYERS, help="--case decode: layers to build")
     ap.add_argument("--rows", type=int, default=65536, help="--case quantize: vectors")
+    ap.add_argument("--contiguous", action="store_true",
+                    help="--case paged: read the same records as a contiguous cache (no block tables)")
     ap.add_argument("--queries-per-call", type=int, default=1, help="--case scan: queries per search call")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
