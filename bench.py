@@ -10,21 +10,21 @@ Workload (synthetic stand-in with the shapes of a Llama-3.2-1B decode step): 16 
 cache, one new token per sequence per step.  K entries ~ N(0,1) with 4 outlier channels per
 (layer, KV head) scaled x20, V entries ~ N(0,1), bf16.  One step = for every layer: quantise and append
 the new K/V token, then attend over the whole packed cache (grouped-query heads) -- the fused
-decode_step call: three launches per layer.
+decode_step call: one launch per layer.
 
 N > 1: KV heads are sharded over the ranks (8/N per rank, with their 4 query heads each); there is no
 collective on the path, total work is fixed ("strong" scaling), value = batch / max-over-ranks step time.
 
 One JSON line is printed by rank 0:
   value     tokens/s with everything resident in HBM: the step is captured once in a CUDA graph
-            (launch-bound otherwise: 48 launches per step) and K replays are timed with CUDA events
+            (16 launches per step) and K replays are timed with CUDA events
   e2e       the same step fed from pinned host buffers: H2D of q/k/v of all layers, the step, D2H of the
             attention output, every step; uploads and downloads run on copy streams over two alternating
             buffer sets, so they overlap the neighbouring steps' kernels
-  roofline  HBM roofline of the dominant kernel (decode_partial_kernel); bytes per launch are the packed
+  roofline  HBM roofline of the one kernel of the path (decode_fused_kernel); bytes per launch are the packed
             K/V rows and norms of one layer; its duration is measured with CUDA events in an extra pass
-            of the same steps launched eagerly, launch by launch (events cannot be read inside a captured
-            graph), with one event pair around the streaming kernel alone
+            of the same steps launched eagerly (events cannot be read inside a captured graph), one event
+            pair per launch
   cpu_baseline  the CPU checker (oracle/, an OpenMP port of the upstream dequantise-then-attend path)
             timed on this machine's cores on a sample of the same workload
   extra     secondary figures: shorter contexts, and the 4-bit index scan (QPS and HBM GB/s)
@@ -133,11 +133,12 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU port (the reference arm and the cpu_baseline leg)
 # ------------------------------------------------------------------------------------------------
-def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int):
+def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice = slice(0, KV_HEADS), threads: int = 0):
     """Dequantise-then-attend on the host for `sample_seqs` sequences x 8 KV heads of ONE layer.
 
     Returns (tokens_per_s extrapolated to the full step, seconds per sample step, cores, description,
-    data) -- data holds the sample's inputs/outputs for the parity check of the GPU arm."""
+    data) -- data holds the sample's inputs/outputs for the parity check of the GPU arm.  `heads` keeps a
+    slice of the KV heads (and their query heads) of the same sample: a rank's share under head sharding."""
     import numpy as np
 
     from oracle import build as obuild
@@ -145,7 +146,7 @@ def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int):
     obuild.build_oracle()
     from oracle import oracle as orc
 
-    cores = os.cpu_count() or 1
+    cores = threads or os.cpu_count() or 1
     orc.set_num_threads(cores)
     rng = np.random.default_rng(4000)
     n = sample_seqs * KV_HEADS * ctx
@@ -163,6 +164,10 @@ def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int):
     kn, vn = kn.reshape(shape), vn.reshape(shape)
     lens = np.full(sample_seqs, ctx, np.int32)
     newk = rng.standard_normal((sample_seqs * KV_HEADS, HEAD_DIM), dtype=np.float32)
+    if heads != slice(0, KV_HEADS):
+        group = Q_HEADS // KV_HEADS
+        kp, kn, vp, vn = (np.ascontiguousarray(a[:, heads]) for a in (kp, kn, vp, vn))
+        q = np.ascontiguousarray(q[:, heads.start * group:heads.stop * group])
 
     def one_step():
         orc.quantize_mse(newk, KEY_BITS, rk, bk)       # the appended token of this layer
@@ -257,9 +262,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     out = torch.empty(LAYERS, BATCH, qh, HEAD_DIM, device=device, dtype=torch.bfloat16)
 
     def step_eager(events=None, bufs=None):
-        """One decode step: per layer, append the new token and attend (the fused three-launch call).
-        With `events`, every call is split into its launches so that the streaming kernel alone sits
-        between an event pair (a whole-call pair is recorded as well)."""
+        """One decode step: per layer, append the new token and attend (one fused launch per layer).
+        With `events`, every launch sits between its own event pair."""
         if bufs is not None:
             for layer in range(LAYERS):
                 cache.decode_step(layer, bufs[0][layer], bufs[1][layer], bufs[2][layer], out=bufs[3][layer])
@@ -271,21 +275,10 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
             if layer == 0:
                 torch.cuda._sleep(20_000_000)      # ~10 ms: the launches below queue up behind it, so no
                                                    # event pair contains a wait for the host
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            lib = _native.lib()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             ev[0].record()
-            lib.tqb_debug_decode_phases(1)
             cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
-            cache.seq_lens[layer] -= 1             # the length advances in the merge launch
             ev[1].record()
-            lib.tqb_debug_decode_phases(2)
-            cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
-            cache.seq_lens[layer] -= 1
-            ev[2].record()
-            lib.tqb_debug_decode_phases(4)
-            cache.decode_step(layer, q_in[layer], k_in[layer], v_in[layer], out=out[layer])
-            ev[3].record()
-            lib.tqb_debug_decode_phases(7)
             events.append(ev)
 
     for _ in range(2):            # allocations, attribute settings, first-touch effects
@@ -387,21 +380,19 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
     for _ in range(K):
         step_eager(events)
     barrier()
-    per_call_ms = sum(ev[0].elapsed_time(ev[3]) for ev in events) / len(events)
-    kernel_ms = sum(ev[1].elapsed_time(ev[2]) for ev in events) / len(events)
+    kernel_ms = sum(ev[0].elapsed_time(ev[1]) for ev in events) / len(events)
     assert cache.decode_status() == 0, "a bounded device-side wait expired"
     seq_now = int(cache.seq_lens[0])
     bytes_per_launch = BATCH * kvh * seq_now * BYTES_PER_TOKEN_HEAD
     peaks = measured_peaks()
     achieved = bytes_per_launch / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "decode_partial_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+    roofline = {"bound": "hbm", "kernel": "decode_fused_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO, "traffic_source": NCU_TRAFFIC_SOURCE,
                 "bytes_per_launch": bytes_per_launch, "ms_per_launch": kernel_ms,
-                "ms_per_call_all_launches": per_call_ms,
-                "note": "ms_per_launch: the streaming kernel alone between an event pair; ms_per_call_all_launches: "
-                        "the three launches of one decode_step call (append + query rotation, streaming kernel, "
-                        "merge) launched one by one"}
+                "note": "ms_per_launch: one decode_step call = one launch of the fused kernel (append, query "
+                        "rotation, streaming attention, merge) between an event pair, launched eagerly behind a "
+                        "queue of earlier launches"}
 
     line = {"metric": METRIC, "value": BATCH / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -418,6 +409,14 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
         line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
                                 "sample_step_s": dt}
         line["parity"] = parity_check(torch, data, device)
+    elif world > 1 and not args.no_cpu:
+        # every rank checks ITS head slice (2 sequences x its KV heads x the full context) against the CPU port
+        _, _, _, _, data = cpu_sample(ctx, 2, 1, 0, heads=slice(rank * kvh, (rank + 1) * kvh), threads=max(1, (os.cpu_count() or 1) // world))
+        mine = parity_check(torch, data, device)
+        t = torch.tensor([mine["max_abs"], -mine["cosine"]], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        line["parity"] = {"max_abs": float(t[0].item()), "cosine": -float(t[1].item()), "tolerance": mine["tolerance"],
+                          "against": "CPU port on every rank's own head slice (2 sequences x %d KV heads), worst rank" % kvh}
     if not args.no_extra:
         try:
             line["extra"] = extras(torch, dist, args, rank, world, device)

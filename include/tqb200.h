@@ -130,7 +130,7 @@ int tqb_attention_values_packed(const float* weights, int64_t bh, int64_t seq, i
  * else in the kernel.  Tokens are stored in RECORDS of 16 tokens of one (sequence, KV head), laid out
  * in the order the consuming mma.sync lanes read them (csrc/tiled_layout.cuh documents every bit):
  *     [32 lanes x dim*kbits/16 bytes of key codes][32 lanes x dim*vbits/16 bytes of value codes]
- *     [16 key norms f32][16 value norms f32]            = 2*dim*(kbits+vbits) + 128 bytes,
+ *     [32 norms f32: 8 groups {key g, key g+8, value g, value g+8}] = 2*dim*(kbits+vbits) + 128 bytes,
  * the same codes and the same bytes per token as upstream.  A token SLOT is a flat index
  * slot = unit * pitch + position (pitch a multiple of 16); its record is slot / 16.  Contiguous cache:
  * unit = sequence * kv_heads + head, pitch = padded max_seq.  Paged cache: unit = block * kv_heads +
@@ -177,10 +177,22 @@ int tqb_kv_import(uint8_t* store, int64_t n, int dim, int kbits, int vbits, cons
  * b * kv_heads + head, `max_seq` = token pitch of a unit (multiple of 16).  Paged cache: block_tables
  * (batch, max_blocks) int32 device, block_size a multiple of 16.
  *
- * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  workspace: device scratch of at least
- * tqb_decode_attention_workspace_bytes(...) bytes, 256-byte aligned, not shared between calls that
- * may overlap on the device.  Its first 4 bytes are a status word the kernels set to non-zero when a
- * bounded device-side wait expired (results are then invalid). */
+ * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  One kernel launch per call.
+ *
+ * workspace: device scratch of at least tqb_decode_attention_workspace_bytes(...) bytes, 256-byte
+ * aligned, not shared between calls that may overlap on the device.  The caller ZEROES it once before
+ * its first use (cudaMemsetAsync); after that the kernel keeps its counters clean by itself.  Its first
+ * 4 bytes are a status word in which the kernel only ever SETS bits (TQB_DECODE_* below); the caller
+ * reads and clears it.  After TQB_DECODE_WAIT_EXPIRED or TQB_DECODE_NO_SMEM the results of that call
+ * are invalid and the whole workspace must be zeroed again before the next call.
+ *
+ * Lengths are clamped on the device: a seq_lens[b] that is negative or exceeds max_len (a stale host
+ * bound) is treated as 0 / max_len and reported with TQB_DECODE_LEN_CLAMPED; nothing is read beyond
+ * max_len tokens of a unit. */
+#define TQB_DECODE_WAIT_EXPIRED 1 /* a bounded device-side wait ran out: results invalid */
+#define TQB_DECODE_NO_SMEM 2      /* the shared-memory plan did not fit: results invalid */
+#define TQB_DECODE_UNIT_FULL 4    /* tqb_decode_step: a unit was full, its new token was not stored */
+#define TQB_DECODE_LEN_CLAMPED 8  /* a sequence length outside [0, max_len] was clamped */
 size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, int kv_heads, int dim,
                                             int64_t max_len);
 int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads, int kv_heads,
@@ -191,15 +203,16 @@ int tqb_decode_attention(const void* query, int q_dtype, int batch, int q_heads,
                          void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                          void* stream);
 
-/* One whole decode step of a layer in three launches: the new token's key and value of every
+/* One whole decode step of a layer in ONE launch: the new token's key and value of every
  * (sequence, KV head) are quantised and stored at position seq_lens[b] of their unit (what
  * QuantizedKVCache.append, turboquant_kv/cache.py:116-184, does for one token), the queries are
- * rotated in the same launch, attention runs over seq_lens[b] + 1 tokens, and seq_lens[b] is advanced
- * by one at the end (device side, so a captured CUDA graph of the step can be replayed).
+ * rotated, attention runs over seq_lens[b] + 1 tokens, and seq_lens[b] is advanced by one at the end
+ * (device side, so a captured CUDA graph of the step can be replayed).
  * query (batch, q_heads, dim), key / value (batch, kv_heads, dim) with kv_stride elements between
  * (sequence, head) rows, all of `dtype`; contiguous caches only (unit pitch max_seq); max_len (host) >=
  * every seq_lens[b] + 1.  The stored codes equal those tqb_kv_append stores.  A unit that is already
- * full (seq_lens[b] == max_seq) stores nothing and sets the status word to 3.
+ * full (seq_lens[b] == max_seq) stores nothing, keeps its length and sets TQB_DECODE_UNIT_FULL; a
+ * position at or beyond max_len (stale host bound) is not stored either (TQB_DECODE_LEN_CLAMPED).
  * Workspace as for tqb_decode_attention (same size query, with max_len counting the new token). */
 int tqb_decode_step(const void* query, const void* key, const void* value, int dtype, int64_t kv_stride,
                     int batch, int q_heads, int kv_heads, int dim, uint8_t* store, int64_t max_seq,
@@ -207,13 +220,6 @@ int tqb_decode_step(const void* query, const void* key, const void* value, int d
                     const float* cent_k, int kbits, const float* rot_v, const float* bnd_v,
                     const float* cent_v, int vbits, float scale, void* workspace, size_t workspace_bytes,
                     void* out, int out_dtype, void* stream);
-
-/* Measurement aid (no upstream counterpart): restricts the following tqb_decode_attention /
- * tqb_decode_step calls of this process to a subset of their three launches (bit 0: preparation,
- * bit 1: the streaming kernel, bit 2: the merge), so that a benchmark can bracket one kernel with
- * events.  A call made with a subset reuses the workspace contents of the previous launches.  7 restores
- * normal operation. */
-void tqb_debug_decode_phases(int mask);
 
 /* ---- packed-code inner-product scan with top-k ------------------------------------------------
  * Replaces turboquant::search_packed (csrc/core/turboquant_core.cpp:407-514) as bound by
@@ -247,8 +253,9 @@ int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, 
  * routine.  Meant for hosts that have already handed all free device memory to pools of their own,
  * where an allocation fails or shrinks a pool, and for latency-critical loops in which a device
  * allocation would stall every stream of the process.  Calls that need more scratch than
- * tqb_scan_topk_static_capacity() bytes (tqb_scan_topk_workspace_bytes tells; e.g. more than 16 queries
- * at k = 10) are rejected with TQB_ERR_WORKSPACE and a message; use tqb_scan_topk for those.
+ * tqb_scan_topk_static_capacity() bytes are rejected with TQB_ERR_WORKSPACE and a message: a call fits
+ * exactly when tqb_scan_topk_workspace_bytes(nq, n, dim, bits, k) <= the capacity (the figure grows with
+ * nq, k and the GPU's SM count: about two dozen queries at k = 10 on a B200); use tqb_scan_topk beyond.
  * The first call on a device resolves the array's address (cudaGetSymbolAddress, with that device
  * current): make it early, before any stream capture is begun.  All calls on a device share the array:
  * the status word at its start is cleared on `stream` by every call, the rest is rewritten before it

@@ -296,27 +296,126 @@ def test_paged_decode_with_ragged_lengths(orc):
         attention_close(out[b:b + 1].cpu().numpy(), ref)
 
 
-def test_fused_step_on_a_full_unit_reports_status_3():
+def test_paged_decode_llama3_8b_geometry_long_context(orc):
+    """The paged Llama-3-8B geometry (head_dim 128, K4/V3, 8 KV heads x 4 query heads, 16-token pages) on REAL
+    quantised data with thousands of tokens per sequence, pages scattered over the pool by a permutation,
+    ragged lengths around page and chunk borders: against dequantise-then-attend on the exported rows."""
+    from turboquant_kv.vllm_plugin import TurboQuantKVCacheConfig, TurboQuantPagedKVCache
+
+    kv_heads, group, dim, bs = 8, 4, 128, 16
+    lens = [4096, 4611, 4097]
+    batch = len(lens)
+    nblocks = sum((l + bs - 1) // bs for l in lens) + 5
+    cfg = TurboQuantKVCacheConfig(key_bits=4, value_bits=3, block_size=bs, num_gpu_blocks=nblocks, seed=42)
+    pool = TurboQuantPagedKVCache(cfg, num_layers=1, num_heads=kv_heads, head_dim=dim, device="cuda")
+    gen = torch.Generator().manual_seed(8)
+    perm = torch.randperm(nblocks, generator=gen)
+    max_blocks = max((l + bs - 1) // bs for l in lens)
+    tables = torch.zeros(batch, max_blocks, dtype=torch.int32)
+    rows, nxt = [], 0
+    for b, l in enumerate(lens):
+        nb = (l + bs - 1) // bs
+        blocks = perm[nxt:nxt + nb]
+        nxt += nb
+        tables[b, :nb] = blocks.to(torch.int32)
+        k = torch.randn(l, kv_heads, dim, generator=gen)
+        v = torch.randn(l, kv_heads, dim, generator=gen)
+        for h in range(kv_heads):
+            k[:, h, torch.randperm(dim, generator=gen)[:4]] *= 20.0
+        t = torch.arange(l)
+        slots = blocks[t // bs].to(torch.int64) * bs + t % bs
+        pool.append_slots(0, k.cuda().bfloat16(), v.cuda().bfloat16(), slots)
+        rows.append((k, v, slots))
+    q = torch.randn(batch, kv_heads * group, dim, generator=gen)
+    out = pool.paged_decode_attention(0, q.cuda().bfloat16(), tables, torch.tensor(lens, dtype=torch.int32),
+                                      max_seq_len=max(lens)).float().cpu().numpy()
+    assert pool.kv.status() == 0
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(3, dim)
+    for b, l in enumerate(lens):
+        k, v, _ = rows[b]
+        kp, kn = orc.quantize_mse(k.bfloat16().float().transpose(0, 1).reshape(-1, dim).numpy(), 4, rk, bk)
+        vp, vn = orc.quantize_mse(v.bfloat16().float().transpose(0, 1).reshape(-1, dim).numpy(), 3, rv, bv)
+        ref = orc.decode_attention(q[b:b + 1].bfloat16().float().numpy(), kp.reshape(1, kv_heads, l, -1),
+                                   kn.reshape(1, kv_heads, l), vp.reshape(1, kv_heads, l, -1), vn.reshape(1, kv_heads, l),
+                                   np.array([l], np.int32), rk, ck, 4, rv, cv, 3)
+        attention_close(out[b:b + 1], ref)
+
+
+@pytest.mark.parametrize("full", [0, 2])          # the full sequence first, or last in the batch
+def test_fused_step_on_a_full_unit_reports_it(orc, full):
     """The device-side guard: a sequence already at its pitch stores nothing, keeps its length and raises
-    status 3; the other sequences of the batch advance normally."""
-    from turboquant_kv.kvstore import PackedKVStore
+    STATUS_UNIT_FULL (wherever it sits in the batch); the other sequences advance normally, and everybody
+    attends to what its unit holds."""
+    from turboquant_kv.kvstore import STATUS_UNIT_FULL, PackedKVStore
     from turboquant_kv import _native as N
 
-    kv_heads, group, dim, pitch = 2, 4, 64, 32
+    batch, kv_heads, group, dim, pitch = 3, 2, 4, 64, 32
     kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
-    store = kv.alloc(2 * kv_heads, pitch)
-    k, v = _fill(2, kv_heads, pitch, dim, seed=31)
+    store = kv.alloc(batch * kv_heads, pitch)
+    k, v = _fill(batch, kv_heads, pitch, dim, seed=31)
     kv.append(store, k.cuda(), v.cuda(), N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1))
-    lens = torch.tensor([pitch, 7], dtype=torch.int32, device="cuda")      # sequence 0 is full
+    start = [7, 9, 11]
+    start[full] = pitch
+    lens = torch.tensor(start, dtype=torch.int32, device="cuda")
     before = store.clone()
-    q = torch.randn(2, kv_heads * group, dim).cuda()
-    newk, newv = torch.randn(2, kv_heads, dim).cuda(), torch.randn(2, kv_heads, dim).cuda()
+    q = torch.randn(batch, kv_heads * group, dim).cuda()
+    newk, newv = torch.randn(batch, kv_heads, dim).cuda(), torch.randn(batch, kv_heads, dim).cuda()
     out = kv.decode_step(store, q, newk, newv, kv_heads, lens, pitch, pitch)
-    assert kv.status() == 3
-    assert lens.tolist() == [pitch, 8]
-    units0 = slice(0, kv_heads)                                             # records of sequence 0 untouched
-    assert torch.equal(store[units0], before[units0]) and not torch.equal(store[kv_heads:], before[kv_heads:])
-    assert torch.isfinite(out).all()
+    assert kv.status() == STATUS_UNIT_FULL
+    assert kv.status() == 0                                                 # reading the status clears it
+    want = [l + 1 for l in start]
+    want[full] = pitch
+    assert lens.tolist() == want
+    for b in range(batch):
+        units = slice(b * kv_heads, (b + 1) * kv_heads)
+        assert torch.equal(store[units], before[units]) == (b == full)      # records of the full sequence untouched
+    # every sequence attended to exactly the tokens its unit now holds
+    rm = N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1)
+    kp, kn, vp, vn = (t.cpu().numpy() for t in kv.export_rows(store, batch * kv_heads * pitch, rm))
+    shape = (batch, kv_heads, pitch)
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(4, dim)
+    _, cv = orc.lloyd_max_codebook(2, dim)
+    ref = orc.decode_attention(q.cpu().numpy(), kp.reshape(*shape, -1), kn.reshape(shape), vp.reshape(*shape, -1),
+                               vn.reshape(shape), np.array(want, np.int32), rk, ck, 4, rv, cv, 2)
+    attention_close(out.cpu().numpy(), ref)
+
+
+def test_stale_host_bound_is_clamped_on_the_device(orc):
+    """Lengths live on the device; a max_len the host forgot to raise must not send the kernel past its
+    work plan: the sequence is attended up to max_len and STATUS_LEN_CLAMPED is raised.  A negative
+    length counts as empty."""
+    from turboquant_kv.kvstore import STATUS_LEN_CLAMPED, PackedKVStore
+    from turboquant_kv import _native as N
+
+    batch, kv_heads, group, dim, pitch = 3, 2, 4, 64, 128
+    kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
+    store = kv.alloc(batch * kv_heads, pitch)
+    k, v = _fill(batch, kv_heads, pitch, dim, seed=33)
+    rm = N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1)
+    kv.append(store, k.cuda(), v.cuda(), rm)
+    lens = torch.tensor([100, 40, -3], dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, kv_heads * group, dim, generator=torch.Generator().manual_seed(5))
+    out = kv.decode_attention(store, q.cuda(), kv_heads, lens, 48, pitch=pitch).cpu().numpy()   # 48 < 100
+    assert kv.status() == STATUS_LEN_CLAMPED
+    kp, kn, vp, vn = (t.cpu().numpy() for t in kv.export_rows(store, batch * kv_heads * pitch, rm))
+    shape = (batch, kv_heads, pitch)
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    _, ck = orc.lloyd_max_codebook(4, dim)
+    _, cv = orc.lloyd_max_codebook(2, dim)
+    ref = orc.decode_attention(q.numpy()[:2], kp.reshape(*shape, -1)[:2], kn.reshape(shape)[:2],
+                               vp.reshape(*shape, -1)[:2], vn.reshape(shape)[:2], np.array([48, 40], np.int32),
+                               rk, ck, 4, rv, cv, 2)
+    attention_close(out[:2], ref)
+    assert not out[2].any()
+    # the same in a fused step: the position lies beyond max_len, so the token is dropped and the length kept
+    lens2 = torch.tensor([100, 40, 5], dtype=torch.int32, device="cuda")
+    newk, newv = torch.randn(batch, kv_heads, dim).cuda(), torch.randn(batch, kv_heads, dim).cuda()
+    kv.decode_step(store, q.cuda(), newk, newv, kv_heads, lens2, 48, pitch)
+    assert kv.status() == STATUS_LEN_CLAMPED
+    assert lens2.tolist() == [100, 41, 6]
 
 
 def test_decode_with_empty_and_ragged_sequences(orc):

@@ -66,6 +66,14 @@ def test_c_abi_reports_errors_without_raising_across_the_boundary():
                                 None, 0, 0, N.ptr(x), N.ptr(x), 4, N.ptr(x), N.ptr(x), 2, ctypes.c_float(1.0),
                                 N.ptr(x), 16, N.ptr(x), 0, None)
     assert rc == -4 and b"workspace" in L.tqb_last_error()
+    # unsupported bit widths and absurd lengths are refused before anything is launched
+    before = N.launch_count()
+    big = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    rc = L.tqb_decode_attention(N.ptr(x), 0, 1, 4, 4, 64, N.ptr(x), 16, N.ptr(x), 16,
+                                None, 0, 0, N.ptr(x), N.ptr(x), 5, N.ptr(x), N.ptr(x), 2, ctypes.c_float(1.0),
+                                N.ptr(big), big.numel(), N.ptr(x), 0, None)
+    assert rc == -2 and b"bits" in L.tqb_last_error() and N.launch_count() == before
+    assert L.tqb_decode_attention_workspace_bytes(1, 4, 4, 64, 1 << 40) == 0
     before = N.launch_count()
     y = torch.zeros(4, 8, dtype=torch.uint8, device="cuda")
     assert L.tqb_pack_codes(N.ptr(torch.zeros(4, 64, dtype=torch.uint8, device="cuda")), 4, 64, 1, N.ptr(y), None) == 0

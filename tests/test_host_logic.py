@@ -66,7 +66,7 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in tqb200.h but not exported"
     lib.tqb_abi_version.restype = ctypes.c_int
-    assert lib.tqb_abi_version() == 1
+    assert lib.tqb_abi_version() == 2
     out = subprocess.run(["nm", "-D", "--defined-only", LIB], capture_output=True, text=True).stdout
     exported = set(re.findall(r" T (tqb_[a-z0-9_]+)", out))
     assert exported == declared, exported ^ declared

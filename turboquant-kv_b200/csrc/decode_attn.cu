@@ -1,32 +1,64 @@
 // decode_attn.cu -- fused decode attention over a packed KV cache (one new token per sequence).
 //
 // Replaces "dequantise every cached key and value, then attend" (upstream
-// turboquant_kv/cache.py:216-339) by three launches that never materialise dense K/V:
+// turboquant_kv/cache.py:216-339) by ONE launch per layer call that never materialises dense K/V.
 //
-//   1. decode_prepare_kernel q_rot = R_k q per head, times scale * log2(e), written directly as
-//                            mma.sync B fragments (fp16); for a fused step it also quantises and
-//                            stores the new token's key and value.
-//   2. decode_partial_kernel one persistent CTA per SM.  A producer warp streams the 16-token records
-//                            of the CTA's work items into a ring of shared-memory stages, one TMA bulk
-//                            copy (cp.async.bulk + mbarrier) of up to 28 KB per stage; two groups of
-//                            consumer warps take alternate stages, four records per warp.  Per record:
-//                            scores = K-codes x q on tensor cores (codes -> fp16 centroids through a
-//                            256-entry shared-memory table indexed by one byte = 2 codes), online
-//                            softmax in the log2 domain with a lazy running maximum, P^T via movmatrix,
-//                            O^T += V^T-codes x P^T on tensor cores, all in ROTATED space.  One
-//                            (m, l, acc) partial per (unit, chunk, consumer warp).
-//   3. decode_merge_kernel   combines the partials of a (sequence, query head), divides by l and
-//                            applies the inverse value rotation acc @ R_v (reference.py:362).
+// decode_fused_kernel: one persistent CTA per SM.  A work item is (unit, chunk of the context); a unit
+// is one (sequence, KV head), whose `group` query heads ride along as the N dimension of the MMA
+// (grouped-query attention: decode cost is paid once per KV head).  Items are dealt round-robin to
+// the CTAs.  Warp roles inside a CTA:
 //
-// A unit is one (sequence, KV head); its `group` query heads ride along as the N dimension of the
-// MMA (grouped-query attention: decode cost is paid once per KV head).  HBM traffic per token and
-// KV head is the packed K row + packed V row + two float norms; everything else lives in L2/SMEM.
+//   producer warp   streams the 16-token records of the CTA's items into a ring of shared-memory
+//                   stages, one TMA bulk copy (cp.async.bulk + mbarrier) of up to 28 KB per stage.
+//   helper warp     prepares the items one ahead of the consumers: q_rot = R_k q per head, times
+//                   scale * log2(e), written as mma.sync B fragments (fp16) into one of two
+//                   shared-memory slots; for a fused step it also quantises the unit's new key and value
+//                   and stores them into the record store before the producer copies that record (the
+//                   item that holds the write position does this).  The CTA's first item is prepared by
+//                   all warps together before the roles split, so the start-up costs one round trip.
+//   consumer warps  two groups take alternate stages, four records per warp.  Per record: scores =
+//                   K-codes x q on tensor cores (codes -> fp16 centroids through a 256-entry
+//                   shared-memory table indexed by one byte = 2 codes), online softmax in the log2
+//                   domain with a lazy running maximum, P^T via movmatrix, O^T += V^T-codes x P^T on
+//                   tensor cores, all in ROTATED space.  One (m, l, acc) partial per (item, warp).
+//   tail phase      every warp that writes a partial bumps its unit's arrival counter; the warp that
+//                   completes a unit queues it, and once the CTA's own items are done its consumer warps
+//                   merge the queued units: combine the partials of a (unit, query head), divide by l,
+//                   apply the inverse value rotation acc @ R_v (reference.py:362) and write the output.
+//                   No warp ever waits for another CTA.  The CTA that leaves last (exit counter)
+//                   publishes the advanced sequence lengths of a fused step.
 //
-// Every wait is bounded: a warp that gives up records it in the status word at the start of the
-// workspace and returns, so a lost copy cannot hang the device.
+// HBM traffic per token and KV head is the packed K row + packed V row + two float norms; everything
+// else lives in L2 / shared memory.
+//
+// Every wait is bounded: a warp that gives up raises a bit of the status word at the start of the
+// workspace and leaves, so a lost copy cannot hang the device.  The kernel only ever SETS bits of the
+// status word (atomicOr, TQB_DECODE_* in tqb200.h); the arrival counters return to zero by themselves at
+// the end of every call that ran to completion.  The caller zeroes the workspace once before its first
+// use and after a status with TQB_DECODE_WAIT_EXPIRED or TQB_DECODE_NO_SMEM set.
 #include "common.cuh"
 #include "pipe.cuh"
 #include "tiled_layout.cuh"
+
+#ifdef TQB_DECODE_TRACE
+// Development aid, compiled only with -DTQB_DECODE_TRACE (never in the shipped library): wall-clock
+// timestamps of the phases of every CTA.
+__device__ unsigned long long g_decode_trace[256][16];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TQB_TRACE(slot) do { g_decode_trace[blockIdx.x][slot] = trace_now(); } while (0)
+#define TQB_TRACE_ADD(slot, v) do { g_decode_trace[blockIdx.x][slot] += (unsigned long long)(v); } while (0)
+extern "C" int tqb_debug_decode_trace(unsigned long long* host, int clear) {
+    if (clear) { static unsigned long long z[256 * 16]; return (int)cudaMemcpyToSymbol(g_decode_trace, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host, g_decode_trace, sizeof(unsigned long long) * 256 * 16);
+}
+#else
+#define TQB_TRACE(slot) do {} while (0)
+#define TQB_TRACE_ADD(slot, v) do {} while (0)
+#endif
 
 namespace tqb {
 
@@ -34,155 +66,88 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_INF = -__builtin_huge_valf();
 constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score exceeds m + 4 (log2)
 constexpr int TILE = 16;                // tokens per MMA tile
-
-// Which launches carry the attribute (bit 0 preparation, 1 streaming kernel, 2 merge).  Measured on the
-// benchmark step (1 GPU, ms per step): none 1.366, streaming + merge 1.317, all three 1.414 -- early-resident
-// preparation CTAs of the next call get in the way of the merge, so the preparation is launched plainly.
-static constexpr int PDL_MASK = 6;
-static constexpr int pdl_mask() { return PDL_MASK; }
+constexpr int QSLOTS = 2;               // query-fragment slots (the helper warp works one item ahead)
+constexpr int TODO_MAX = 64;            // completed units a CTA queues for its tail phase
+constexpr int LEN_ROOM = 1 << 30;       // flag in an encoded length: this step appends a token to the sequence
+constexpr int LEN_MASK = LEN_ROOM - 1;
+constexpr int64_t MAX_LEN_LIMIT = (int64_t)1 << 30;
+constexpr int MERGE_MAX_CHUNKS = 1024;  // partials per (unit, query head) the planner allows
 
 // ---- launch parameters --------------------------------------------------------------------------
 struct DecodeParams {
-    const uint8_t* store;            // tiled records (tiled_layout.cuh)
-    const int32_t* seq_lens; const int32_t* block_tables;
+    uint8_t* store;                  // tiled records (tiled_layout.cuh)
+    const int32_t* lens_in;          // the caller's sequence lengths
+    int32_t* lens_out;               // fused step: the same array, advanced by the CTA that leaves last
+    const int32_t* block_tables;
     int64_t max_seq;                 // token pitch of a unit (contiguous cache), multiple of 16
+    int64_t max_len;                 // host bound of the attended lengths: the work plan covers [0, max_len)
     int batch, q_heads, kv_heads, group, max_blocks, block_size;
     int chunk, nchunks;              // tokens per (unit, chunk) work item
-    int sets;                        // partials per work item (consumer warps of the streaming kernel)
+    int step;                        // 1: append the new token of every unit first (tqb_decode_step)
+    const void* query; const void* key; const void* value;
+    int in_dtype; int64_t kv_stride;
+    const float* rot_k; const float* rot_v; const float* bnd_k; const float* bnd_v;
     const float* cent_k; const float* cent_v;
+    float scale;
+    void* out; int out_dtype;
     // workspace views
-    int* status; const uint32_t* qfrag;
+    int* status; int* done; int* unit_cnt;
     float* part_m; float* part_l; float* part_acc;
 };
 
 // Workspace layout shared by the size query and the launcher.
 struct DecodeWorkspace {
-    size_t off_status, off_lens, off_qfrag, off_m, off_l, off_acc, total;
+    size_t off_status, off_cnt, off_m, off_l, off_acc, total;
     int chunk, nchunks;
 };
 
-
-// =================================================================================================
-// 1. query rotation -> B fragments
-// =================================================================================================
-// Fragments carry q_rot * scale * log2(e): fp16 keeps 11 significant bits whatever the magnitude and
-// the products stay far inside its range, so no separate per-head factor is needed.
-__device__ __forceinline__ void write_query_fragments(const float (*qr)[128], int u, int group, int dim,
-                                                      float scale, uint32_t* __restrict__ qfrag) {
-    const float fold = scale * LOG2E;
-    const int ksteps = dim >> 4;
-    for (int idx = threadIdx.x; idx < ksteps * 64; idx += blockDim.x) {
-        const int ks = idx >> 6, rem = idx & 63, fl = rem >> 1, half = rem & 1;
-        const int g = fl >> 2, t = fl & 3;
-        float lo = 0.0f, hi = 0.0f;
-        if (g < group) {
-            const int dlo = 16 * ks + 8 * half + 2 * t, dhi = dlo + 1;   // k index = dimension
-            lo = qr[g][dlo] * fold;
-            hi = qr[g][dhi] * fold;
-        }
-        qfrag[((int64_t)u * ksteps + ks) * 64 + rem] = pack_half2_sat(lo, hi);
+__device__ __forceinline__ float load_in(const void* base, int dtype, int64_t idx) {
+    if (dtype == TQB_F32) return reinterpret_cast<const float*>(base)[idx];
+    if (dtype == TQB_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+// Four consecutive elements (idx a multiple of 4, rows 8-byte aligned at least) as float4.
+__device__ __forceinline__ float4 load_in4(const void* base, int dtype, int64_t idx) {
+    if (dtype == TQB_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+    const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx);
+    if (dtype == TQB_F16) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+        return make_float4(a.x, a.y, c.x, c.y);
     }
+    return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u),
+                       __uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store_out(void* base, int dtype, int64_t idx, float v) {
+    if (dtype == TQB_F32) reinterpret_cast<float*>(base)[idx] = v;
+    else if (dtype == TQB_F16) reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ uint16_t half_bits_sat(float v) {   // fp16 with saturation to the largest finite value
+    uint16_t r;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(r) : "f"(v));
+    return r;
 }
 
-// -------------------------------------------------------------------------------------------------
-// One CTA (8 warps) per unit rotates the unit's queries into B fragments: element (ks, lane = 4g+t, half)
-// of head g holds the rotated query coordinates (16ks + 8half + 2t, +1); heads >= group are zero columns.
-// With key != nullptr it is one decode step's whole preparation: it also quantises and stores the new
-// token's key and value of the unit.
-//
-// The code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums and a
-// butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
-// code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
-// The token goes to position lens_in[b] of its unit; lens_now[b] = lens_in[b] + 1 is what the
-// attention kernels of this step read.  A full unit (position >= max_seq) stores nothing, raises
-// status 3 and attends to the tokens it has.
-template <typename T, int NQ>
-__global__ void __launch_bounds__(256) decode_prepare_kernel(
-    const T* __restrict__ q, const T* __restrict__ key, const T* __restrict__ value, int64_t kv_stride,
-    int q_heads, int kv_heads, int group, int dim, const float* __restrict__ Rk, const float* __restrict__ Rv,
-    const float* __restrict__ bnd_k, const float* __restrict__ bnd_v, int kbits, int vbits, float scale,
-    uint8_t* __restrict__ store, int64_t max_seq, const int32_t* __restrict__ lens_in,
-    int32_t* __restrict__ lens_now, uint32_t* __restrict__ qfrag, int* status) {
-    __shared__ float vec[10][128];            // rows 0..group-1: queries; 8: unit key; 9: unit value
-    __shared__ float qr[8][128];
-    __shared__ float bnd[2][16];
-    __shared__ float nrm[2];
-    __shared__ uint32_t codes[2][128];
-    const int u = blockIdx.x, b = u / kv_heads, h = u - b * kv_heads;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_wait();          // inputs may come from the previous kernel; the workspace is still read by it
-    pdl_trigger();
-    if (u == 0 && threadIdx.x == 0) *status = 0;
-    const bool step = key != nullptr;
-    const int pos = step ? lens_in[b] : 0;
-    const bool room = step && pos < max_seq;
-    if (step && h == 0 && threadIdx.x == 0) lens_now[b] = room ? pos + 1 : pos;
-    if (step && !room && threadIdx.x == 0) atomicExch(status, 3);
-    if (step && threadIdx.x < 32) {            // (the boundary tables are null without a new token)
-        const int which = threadIdx.x >> 4, i = threadIdx.x & 15;
-        const int nb = (1 << (which ? vbits : kbits)) - 1;
-        bnd[which][i] = i < nb ? (which ? bnd_v : bnd_k)[i] : __int_as_float(0x7f800000);
+// Encoded length of a sequence: bits 0..29 = tokens attended in this call, LEN_ROOM = a fused step stores
+// its new token at position (attended - 1).  `flag` receives the status bits the length deserves:
+// TQB_DECODE_UNIT_FULL (the step stores nothing) or TQB_DECODE_LEN_CLAMPED (the length lies outside what
+// the host announced: negative, or beyond max_len).  The device never reads or writes beyond max_len / max_seq.
+__device__ __forceinline__ int encode_len(const DecodeParams& p, int raw, int& flag) {
+    flag = 0;
+    const int cap = (int)min((int64_t)LEN_MASK, p.max_len);
+    if (raw < 0) { flag = TQB_DECODE_LEN_CLAMPED; return 0; }
+    if (!p.step) {
+        if (raw > cap) { flag = TQB_DECODE_LEN_CLAMPED; return cap; }
+        return raw;
     }
-    for (int idx = threadIdx.x; idx < group * dim; idx += blockDim.x) {
-        const int n = idx / dim, k = idx - n * dim;
-        vec[n][k] = to_f32<T>(q[((int64_t)b * q_heads + h * group + n) * dim + k]);
-    }
-    if (step && (warp == 6 || warp == 7)) {    // warps 6, 7: norm and unit vector of the key, the value
-        const int which = warp - 6;
-        const T* x = (which ? value : key) + (int64_t)u * kv_stride;
-        float v[NQ], ss = 0.0f;
-#pragma unroll
-        for (int qq = 0; qq < NQ; qq++) {
-            const int j = lane + 32 * qq;
-            v[qq] = j < dim ? to_f32<T>(x[j]) : 0.0f;
-            ss = fmaf(v[qq], v[qq], ss);
-        }
-        const float n = sqrtf(warp_sum(ss));
-        const float den = fmaxf(n, 1e-10f);
-#pragma unroll
-        for (int qq = 0; qq < NQ; qq++)
-            if (lane + 32 * qq < dim) vec[8 + which][lane + 32 * qq] = v[qq] / den;
-        if (lane == 0) nrm[which] = n;
-    }
-    __syncthreads();
-    // one thread per output coordinate of (group + 2) vectors
-    const int total = (group + (step ? 2 : 0)) * dim;
-    for (int o = threadIdx.x; o < total; o += blockDim.x) {
-        const int vi = o / dim, j = o - vi * dim;
-        const float* src = vec[vi < group ? vi : 8 + (vi - group)];
-        const float4* row = reinterpret_cast<const float4*>((vi <= group ? Rk : Rv) + (int64_t)j * dim);
-        float acc = 0.0f;
-#pragma unroll 8
-        for (int k4 = 0; k4 < dim / 4; k4++) {
-            const float4 r = __ldg(row + k4);
-            acc = fmaf(src[4 * k4], r.x, acc);
-            acc = fmaf(src[4 * k4 + 1], r.y, acc);
-            acc = fmaf(src[4 * k4 + 2], r.z, acc);
-            acc = fmaf(src[4 * k4 + 3], r.w, acc);
-        }
-        if (vi < group) {
-            qr[vi][j] = acc;
-        } else {
-            const int which = vi - group;
-            uint32_t c = 0;
-            for (int step = 1 << ((which ? vbits : kbits) - 1); step > 0; step >>= 1)
-                if (bnd[which][c + step - 1] < acc) c += step;
-            codes[which][j] = c;
-        }
-    }
-    __syncthreads();
-    if (warp < 2 && room) {                    // warp 0 stores the key, warp 1 the value
-        uint32_t code[NQ];
-#pragma unroll
-        for (int qq = 0; qq < NQ; qq++) code[qq] = lane + 32 * qq < dim ? codes[warp][lane + 32 * qq] : 0u;
-        tiled_store_row<NQ>(store, warp + 1, kbits, vbits, (int64_t)u * max_seq + pos, code, nrm[warp], lane, dim);
-    }
-    write_query_fragments(qr, u, group, dim, scale, qfrag);
+    if ((int64_t)raw >= p.max_seq) { flag = TQB_DECODE_UNIT_FULL; return (int)min((int64_t)cap, p.max_seq); }
+    if (raw >= cap) { flag = TQB_DECODE_LEN_CLAMPED; return cap; }
+    return (raw + 1) | LEN_ROOM;
 }
 
-
 // =================================================================================================
-// 2. streaming partial attention over tiled records
+// streaming configuration
 // =================================================================================================
 template <int D, int KB, int VB>
 struct DecodeCfg {
@@ -199,7 +164,6 @@ struct DecodeCfg {
     static constexpr bool VBYTE = VQUAD || (2 * VB == 8);
     static constexpr int LUTK_ENTRIES = 1 << (2 * KB);
     static constexpr int LUTV_ENTRIES = VQUAD ? 256 : (1 << (2 * VB));
-    static constexpr int LUTV_WORDS = VQUAD ? 2 : 1;               // 8-byte entries for 2-bit values
     // When both tables are BYTE tables they share ONE 64 KB region: the 256 bytes of entry x hold the key
     // entry in [0,128) (32 lanes x 4 B) and the value entry in [128,256) (32 lanes x 4 B, or 16 lane slots
     // x 8 B: a 64-bit shared load is served half a warp at a time, so lanes l and l+16 can share a slot).
@@ -218,16 +182,24 @@ struct DecodeCfg {
     static constexpr int SR = WPG * RPW;                            // records per stage (one bulk copy)
     static constexpr int STAGE = SR * REC;
     static constexpr int STAGE_TOKENS = SR * 16;
-    static constexpr int THREADS = (WARPS + 1) * 32;                // consumer warps + one producer warp
+    static constexpr int THREADS = (WARPS + 2) * 32;                // consumer warps + producer warp + helper warp
     // Shared-memory plan (dynamic, the whole opt-in maximum):  [ring A | aligned tables | misc | ring B]
     static constexpr int DYN = 227 * 1024;
-    static constexpr int LENS_MAX = 512;
-    static constexpr int MISC = SMALL_K + SMALL_V + 256 /*centroids*/ + 8 * (8 + 8 + 16) /*barriers, stage headers*/
-                                + LENS_MAX * 4;
+    static constexpr int LENS_MAX = 256;
+    static constexpr int QFRAG = MT * 256;                          // one slot of query fragments: MT x 32 lanes x 8 B
+    // misc: centroids (256) | barriers and stage headers (8*(8+8+16) = 256) | helper barriers (64) |
+    //       boundaries (128) | unit vectors of the new key / value (2*D*4) | their codes (2*D) and norms (16) |
+    //       tail-phase queue (16 + 4*TODO_MAX) | lengths | query-fragment slots
+    static constexpr int OFF_BARS = 256, OFF_QBARS = OFF_BARS + 256, OFF_BND = OFF_QBARS + 64;
+    static constexpr int OFF_UNIT = OFF_BND + 128, OFF_CODES = OFF_UNIT + 2 * D * 4, OFF_NRM = OFF_CODES + 2 * D;
+    static constexpr int OFF_TODO = OFF_NRM + 16, OFF_LENS = OFF_TODO + 16 + 4 * TODO_MAX;
+    static constexpr int OFF_QFRAG = (OFF_LENS + LENS_MAX * 4 + 127) / 128 * 128;
+    static constexpr int MISC_FIXED = OFF_QFRAG + QSLOTS * QFRAG;
+    static constexpr int MISC = SMALL_K + SMALL_V + MISC_FIXED;
     static constexpr int BASE_MAX = 4096;                           // assumed upper bound of the window offset
     static constexpr int SLOTS_A = NALIGNED ? (65536 - BASE_MAX) / STAGE : 0;
     static constexpr int TAIL = NALIGNED ? DYN - 2 * 65536 : DYN - BASE_MAX;
-    static constexpr int SLOTS_B = (TAIL - MISC) / STAGE;
+    static constexpr int SLOTS_B = (TAIL - MISC - 128) / STAGE;
     static constexpr int NS_FIT = SLOTS_A + SLOTS_B;
     static constexpr int NS = NS_FIT > 8 ? 8 : NS_FIT;              // stages in the ring
     static_assert(NS >= 2, "shared memory: the ring needs at least two stages");
@@ -239,25 +211,47 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// Sequence lengths as the kernel sees them: encoded (encode_len), from a shared-memory copy when the
+// batch fits, else recomputed from the caller's array.
+struct Lens {
+    const int32_t* sm;               // null: not cached
+    __device__ __forceinline__ int get(const DecodeParams& p, int b) const {
+        if (sm) return sm[b];
+        int flag;
+        return encode_len(p, p.lens_in[b], flag);
+    }
+};
+
 // Position of a CTA in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to CTAs;
 // an item is streamed in stages of up to SR records, which the consumer warps share (RPW records each).
 template <int SR, int GROUPS>
 struct StageCursor {
     int item, total_items, stride;     // (the host checks that the item count fits 31 bits)
+    int seq;                            // items of this CTA opened so far, minus one
     int tiles_left, tile0;              // tiles of the item not yet taken; index of the next one in its unit
     int unit, b, h, chunk_idx, tok_end;
+    bool append;                        // this item holds the position a fused step writes its new token to
     int stage_idx, stages;              // position in the item; an item takes at least GROUPS stages (empty ones
                                         // if need be) so that every consumer group sees its start and its end
+    __device__ __forceinline__ void start(const DecodeParams& p, const Lens& lens) {
+        item = blockIdx.x;
+        total_items = p.batch * p.kv_heads * p.nchunks;
+        stride = gridDim.x;
+        seq = -1;
+        tiles_left = 0;
+        open(p, lens);
+    }
     __device__ __forceinline__ bool valid() const { return item < total_items; }
     __device__ __forceinline__ int tiles_here() const { return min(SR, tiles_left); }
-    // `lens`: the sequence lengths (a shared-memory copy when the batch fits, else the global array)
-    __device__ __forceinline__ void open(const DecodeParams& p, const int32_t* lens) {
+    __device__ __forceinline__ void open(const DecodeParams& p, const Lens& lens) {
         while (item < total_items) {
             unit = item / p.nchunks;
             chunk_idx = item - unit * p.nchunks;
             b = unit / p.kv_heads;
             h = unit - b * p.kv_heads;
-            const int S = lens[b];
+            const int e = lens.get(p, b);
+            const int S = e & LEN_MASK;
             const int tok0 = chunk_idx * p.chunk;
             tok_end = min(S, tok0 + p.chunk);
             if (tok0 < tok_end) {
@@ -265,17 +259,142 @@ struct StageCursor {
                 tile0 = tok0 / TILE;
                 stage_idx = 0;
                 stages = max(GROUPS, (tiles_left + SR - 1) / SR);
+                append = (e & LEN_ROOM) && (S - 1) / p.chunk == chunk_idx;
+                seq++;
                 return;
             }
             item += stride;
         }
     }
-    __device__ __forceinline__ void next(const DecodeParams& p, const int32_t* lens) {
+    __device__ __forceinline__ void next(const DecodeParams& p, const Lens& lens) {
         const int n = tiles_here();
         tiles_left -= n; tile0 += n; stage_idx++;
         if (stage_idx == stages) { item += stride; open(p, lens); }
     }
+    __device__ __forceinline__ void next_item(const DecodeParams& p, const Lens& lens) {
+        item += stride;
+        open(p, lens);
+    }
 };
+
+// =================================================================================================
+// item preparation: query fragments, and the new token of a fused step
+// =================================================================================================
+// Shared-memory scratch of the preparation (DecodeCfg::OFF_*), as generic pointers.
+struct PrepScratch {
+    const float* bnd;                // [2][16] boundaries (keys, values), +inf beyond the last
+    float* unit;                     // [2][D]  unit vector of the new key / value
+    uint8_t* codes;                  // [2][D]
+    float* nrm;                      // [2]
+};
+
+// Prepares one item with `nthreads` threads (`tid` = 0..nthreads-1): a whole CTA (CTA_WIDE, barriers are
+// __syncthreads) or one warp.  Writes the B fragments of the unit's rotated queries into `qslot`:
+// element (ks, lane = 4n+t, half) of head n holds the rotated query coordinates (16ks + 8half + 2t, +1)
+// times scale * log2(e) as fp16 (11 significant bits whatever the magnitude; the products stay far inside
+// fp16's range); the columns of heads >= group stay zero.
+//
+// With `append` it first quantises the unit's new key and value and stores them at position `pos`.  The
+// code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums and a
+// butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
+// code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
+// The stores are followed by a proxy fence: the producer copies that record with the TMA engine.
+template <int D, int KB, int VB, bool CTA_WIDE>
+__device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bool append, int pos,
+                                             uint16_t* qslot, const PrepScratch& sc, int tid, int nthreads) {
+    constexpr int NQ = D / 32;
+    const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
+    const int warp = tid >> 5, lane = tid & 31;
+    auto sync = [&]() { if (CTA_WIDE) __syncthreads(); else __syncwarp(); };
+    if (append) {
+        // norm and unit vector of the key (which = 0) and the value (1): one warp each, or one after the other
+        for (int which = CTA_WIDE ? warp : 0; which < 2; which += CTA_WIDE ? 2 : 1) {
+            if (CTA_WIDE && warp >= 2) break;
+            const void* x = which ? p.value : p.key;
+            const int64_t x0 = (int64_t)unit * p.kv_stride;
+            float v[NQ], ss = 0.0f;
+#pragma unroll
+            for (int qq = 0; qq < NQ; qq++) {
+                v[qq] = load_in(x, p.in_dtype, x0 + lane + 32 * qq);
+                ss = fmaf(v[qq], v[qq], ss);
+            }
+            const float n = sqrtf(warp_sum(ss));
+            const float den = fmaxf(n, 1e-10f);
+#pragma unroll
+            for (int qq = 0; qq < NQ; qq++) sc.unit[which * D + lane + 32 * qq] = v[qq] / den;
+            if (lane == 0) sc.nrm[which] = n;
+        }
+    }
+    sync();
+    // One thread per ROW of a rotation matrix: row j of R_k serves the unit's `group` queries and its new key
+    // (the row is fetched once for all of them), row j of R_v the new value.  A row is fetched in batches of
+    // eight 128-bit loads that are all in flight together; the sums run over k ascending.
+    const float fold = p.scale * LOG2E;
+    const int ntasks = append ? 2 * D : D;
+    const int64_t q0 = ((int64_t)b * p.q_heads + h * p.group) * D;
+    for (int task = tid; task < ntasks; task += nthreads) {
+        const int which = task / D, j = task - which * D;           // 0: R_k row (queries, key), 1: R_v row (value)
+        const float4* row = reinterpret_cast<const float4*>((which ? p.rot_v : p.rot_k) + (int64_t)j * D);
+        float aq[8], ax = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 8; n++) aq[n] = 0.0f;
+#pragma unroll 1
+        for (int k8 = 0; k8 < D / 4; k8 += 8) {
+            float4 r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __ldg(row + k8 + i);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k0 = 4 * (k8 + i);
+                if (which == 0) {
+#pragma unroll
+                    for (int n = 0; n < 8; n++) {
+                        if (n < p.group) {
+                            const float4 x = load_in4(p.query, p.in_dtype, q0 + (int64_t)n * D + k0);
+                            aq[n] = fmaf(x.x, r[i].x, aq[n]);
+                            aq[n] = fmaf(x.y, r[i].y, aq[n]);
+                            aq[n] = fmaf(x.z, r[i].z, aq[n]);
+                            aq[n] = fmaf(x.w, r[i].w, aq[n]);
+                        }
+                    }
+                }
+                if (append) {
+                    const float4 u = *reinterpret_cast<const float4*>(sc.unit + which * D + k0);
+                    ax = fmaf(u.x, r[i].x, ax);
+                    ax = fmaf(u.y, r[i].y, ax);
+                    ax = fmaf(u.z, r[i].z, ax);
+                    ax = fmaf(u.w, r[i].w, ax);
+                }
+            }
+        }
+        if (which == 0) {
+            const int ks = j >> 4, half = (j >> 3) & 1, t = (j & 7) >> 1, hi = j & 1;
+#pragma unroll
+            for (int n = 0; n < 8; n++)
+                if (n < p.group) qslot[2 * (ks * 64 + (4 * n + t) * 2 + half) + hi] = half_bits_sat(aq[n] * fold);
+        }
+        if (append) {
+            const float* bnd = sc.bnd + which * 16;
+            uint32_t c = 0;
+            for (int s = 1 << ((which ? VB : KB) - 1); s > 0; s >>= 1)
+                if (bnd[c + s - 1] < ax) c += s;
+            sc.codes[which * D + j] = (uint8_t)c;
+        }
+    }
+    sync();
+    if (append) {
+        for (int which = CTA_WIDE ? warp : 0; which < 2; which += CTA_WIDE ? 2 : 1) {
+            if (CTA_WIDE && warp >= 2) break;
+            uint32_t code[NQ];
+#pragma unroll
+            for (int qq = 0; qq < NQ; qq++) code[qq] = sc.codes[which * D + lane + 32 * qq];
+            tiled_store_row<NQ>(p.store, which + 1, KB, VB, (int64_t)unit * p.max_seq + pos, code, sc.nrm[which], lane, D);
+            // generic-proxy stores above, async-proxy (TMA) read of the same record below
+            asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        sync();
+    }
+}
 
 // Per-warp softmax state of the item being processed.
 template <int MT>
@@ -286,7 +405,7 @@ struct WarpState {
     uint32_t qf[MT][2];
 };
 
-// NT (1, 2 or 4) 16-token records at once: scores, online softmax, accumulation.  Both records go through
+// NT (1, 2 or 4) 16-token records at once: scores, online softmax, accumulation.  All records go through
 // every phase together so that their independent instruction chains interleave.  MASKED handles the
 // partial last tile of an item (tokens >= valid contribute nothing).
 template <int D, int KB, int VB, int NT, bool MASKED>
@@ -322,11 +441,15 @@ __device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t re
     float tm0 = NEG_INF, tm1 = NEG_INF;
 #pragma unroll
     for (int i = 0; i < NT; i++) {
-        const uint32_t nk = rec0 + i * C::REC + C::KSEC + C::VSEC + 4 * g;   // key norms, then 16 value norms
+        // the four norms this lane needs of the record: keys of tokens g, g+8, values of tokens g, g+8
+        uint32_t nw[4];
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(nw[0]), "=r"(nw[1]), "=r"(nw[2]), "=r"(nw[3])
+                     : "r"(rec0 + i * C::REC + C::KSEC + C::VSEC + 16 * g));
         const bool val_g = !MASKED || 16 * i + g < valid, val_g8 = !MASKED || 16 * i + g + 8 < valid;
-        float nkg = ldsf(nk), nkg8 = ldsf(nk + 32);
-        nvg[i] = ldsf(nk + 64);
-        nvg8[i] = ldsf(nk + 96);
+        float nkg = __uint_as_float(nw[0]), nkg8 = __uint_as_float(nw[1]);
+        nvg[i] = __uint_as_float(nw[2]);
+        nvg8[i] = __uint_as_float(nw[3]);
         if (MASKED) {
             if (!val_g) { nkg = 0.0f; nvg[i] = 0.0f; }
             if (!val_g8) { nkg8 = 0.0f; nvg8[i] = 0.0f; }
@@ -399,8 +522,85 @@ __device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t re
     }
 }
 
+// =================================================================================================
+// tail phase: merge of a (unit, query head) + inverse value rotation, by one warp
+// =================================================================================================
+// Partial c (< nparts) of head n sits at part_*[pbase + c * group] (and * D for the accumulators).  The
+// partials were written by other warps, possibly of other CTAs, before they bumped the unit's arrival
+// counter: they are read past L1 (ld.global.cg).
+template <int D>
+__device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int n, int nparts, int lane) {
+    constexpr int NQ = D / 32;
+    const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
+    const int64_t pbase = (int64_t)unit * p.nchunks * (D == 64 ? 16 : 8) * p.group + n;
+    float M = NEG_INF;
+    for (int c = lane; c < nparts; c += 32) M = fmaxf(M, __ldcg(p.part_m + pbase + (int64_t)c * p.group));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.0f, acc[NQ];
+#pragma unroll
+    for (int i = 0; i < NQ; i++) acc[i] = 0.0f;
+    for (int c0 = 0; c0 < nparts; c0 += 32) {
+        const int c = c0 + lane;
+        float w = 0.0f;
+        if (c < nparts) {
+            const float m = __ldcg(p.part_m + pbase + (int64_t)c * p.group);
+            w = (m == NEG_INF) ? 0.0f : exp2f(m - M);
+            L = fmaf(__ldcg(p.part_l + pbase + (int64_t)c * p.group), w, L);
+        }
+        const int cn = min(32, nparts - c0);                        // (a multiple of 8: 8 or 16 partials per chunk)
+        for (int cb = 0; cb < cn; cb += 8) {                        // eight partial rows in flight together
+            float v[8][NQ];
+#pragma unroll
+            for (int cc = 0; cc < 8; cc++) {
+                const float* row = p.part_acc + (pbase + (int64_t)(c0 + cb + cc) * p.group) * D + lane;
+#pragma unroll
+                for (int i = 0; i < NQ; i++) v[cc][i] = __ldcg(row + 32 * i);
+            }
+#pragma unroll
+            for (int cc = 0; cc < 8; cc++) {
+                const float wc = __shfl_sync(0xffffffffu, w, cb + cc);
+#pragma unroll
+                for (int i = 0; i < NQ; i++) acc[i] = fmaf(wc, v[cc][i], acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    const float inv = (nparts > 0 && L > 0.0f) ? 1.0f / L : 0.0f;
+    float y[NQ], out[NQ];
+#pragma unroll
+    for (int i = 0; i < NQ; i++) { y[i] = acc[i] * inv; out[i] = 0.0f; }
+    // out_k = sum_j y_j Rv[j][k]  (x = y @ R, reference.py:362); lane holds k = lane + 32 i
+#pragma unroll
+    for (int ij = 0; ij < NQ; ij++) {
+#pragma unroll 1
+        for (int jb = 0; jb < 32; jb += 8) {                        // eight rows of R_v in flight together
+            float r[8][NQ];
+#pragma unroll
+            for (int jj = 0; jj < 8; jj++) {
+                const float* row = p.rot_v + (int64_t)(32 * ij + jb + jj) * D + lane;
+#pragma unroll
+                for (int i = 0; i < NQ; i++) r[jj][i] = __ldg(row + 32 * i);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; jj++) {
+                const float yj = __shfl_sync(0xffffffffu, y[ij], jb + jj);
+#pragma unroll
+                for (int i = 0; i < NQ; i++) out[i] = fmaf(yj, r[jj][i], out[i]);
+            }
+        }
+    }
+    const int64_t o0 = ((int64_t)b * p.q_heads + h * p.group + n) * D + lane;
+#pragma unroll
+    for (int i = 0; i < NQ; i++) store_out(p.out, p.out_dtype, o0 + 32 * i, out[i]);
+}
+
+// =================================================================================================
+// the kernel
+// =================================================================================================
 template <int D, int KB, int VB, bool PAGED>
-__global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_partial_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KB, VB>;
     constexpr int WARPS = C::WARPS, NS = C::NS, SR = C::SR, RPW = C::RPW, GROUPS = C::GROUPS, WPG = C::WPG;
     constexpr uint32_t F_FIRST = 1u << 16, F_LAST = 1u << 17, F_END = 1u << 18;
@@ -420,51 +620,69 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         tabV_base = C::VBYTE ? al + (C::KBYTE ? 128u : 0u) : 0;   // second half of every 256-byte entry block
         misc = al + 65536u;
     } else {
-        slotsA = 0; tabK_base = tabV_base = 0; misc = base;
+        slotsA = 0; tabK_base = tabV_base = 0; misc = (base + 127u) & ~127u;
     }
     if (!C::KBYTE) { tabK_base = misc; misc += C::SMALL_K; }
     if (!C::VBYTE) { tabV_base = misc; misc += C::SMALL_V; }
-    const uint32_t cent_addr = misc;                 // 32 floats
-    const uint32_t full_addr = misc + 256;           // full[s]: the stage's bytes have landed
-    const uint32_t empty_addr = full_addr + 8 * 8;   // empty[s]: every warp of the stage's group has finished with it
-    const uint32_t meta_addr = empty_addr + 8 * 8;   // one uint4 per stage: {unit, chunk, tiles | flags, valid tokens}
-    const uint32_t lens_addr = meta_addr + 8 * 16;   // sequence lengths of up to LENS_MAX sequences
-    ringB = (lens_addr + C::LENS_MAX * 4 + 127u) & ~127u;
-    const int slotsB = (int)((end - ringB) / C::STAGE);
+    const uint32_t cent_addr = misc;                             // 32 floats
+    const uint32_t full_addr = misc + C::OFF_BARS;               // full[s]: the stage's bytes have landed
+    const uint32_t empty_addr = full_addr + 8 * 8;               // empty[s]: every warp of the stage's group has finished with it
+    const uint32_t meta_addr = empty_addr + 8 * 8;               // one uint4 per stage: {unit, chunk, tiles | flags, valid tokens}
+    const uint32_t qfull_addr = misc + C::OFF_QBARS;             // qfull[q]: the item's query fragments are in slot q
+    const uint32_t qempty_addr = qfull_addr + 8 * QSLOTS;        // qempty[q]: every consumer warp has taken them
+    const uint32_t qfrag_addr = misc + C::OFF_QFRAG;
+    ringB = (misc + C::MISC_FIXED + 127u) & ~127u;
+    const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
     if (slotsA + slotsB < NS) {                      // cannot happen unless the window offset is unusually large
-        if (threadIdx.x == 0) atomicExch(p.status, 2);
+        if (threadIdx.x == 0) atomicOr(p.status, TQB_DECODE_NO_SMEM);
         return;
     }
     auto slot_addr = [&](int slot) -> uint32_t {
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
+    int* const todo = reinterpret_cast<int*>(smem_gen + misc + C::OFF_TODO);     // [0] count, [1] exit flag, [4..] units
+    PrepScratch scratch;
+    scratch.bnd = reinterpret_cast<const float*>(smem_gen + misc + C::OFF_BND);
+    scratch.unit = reinterpret_cast<float*>(smem_gen + misc + C::OFF_UNIT);
+    scratch.codes = smem_gen + misc + C::OFF_CODES;
+    scratch.nrm = reinterpret_cast<float*>(smem_gen + misc + C::OFF_NRM);
     pdl_trigger();
+    if (threadIdx.x == 0) TQB_TRACE(0);
 
-    const bool lens_in_smem = p.batch <= C::LENS_MAX;
-    const int32_t* lens = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + lens_addr) : p.seq_lens;
+    // ---- constants: centroids, boundaries, barriers, empty query slots, lookup tables ----
     if (threadIdx.x < 16) {
         float* cf = reinterpret_cast<float*>(smem_gen + cent_addr);
         cf[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
         cf[16 + threadIdx.x] = threadIdx.x < (1 << VB) ? p.cent_v[threadIdx.x] : 0.0f;
+    } else if (threadIdx.x < 48 && p.step) {
+        const int which = (threadIdx.x - 16) >> 4, i = threadIdx.x & 15;
+        const int nb = (1 << (which ? VB : KB)) - 1;
+        reinterpret_cast<float*>(smem_gen + misc + C::OFF_BND)[which * 16 + i] =
+            i < nb ? (which ? p.bnd_v : p.bnd_k)[i] : __int_as_float(0x7f800000);
     }
     if (threadIdx.x < NS) {
         mbar_init(full_addr + threadIdx.x * 8, 1);
         mbar_init(empty_addr + threadIdx.x * 8, WPG);
     }
+    if (threadIdx.x < QSLOTS) {
+        mbar_init(qfull_addr + threadIdx.x * 8, 1);
+        mbar_init(qempty_addr + threadIdx.x * 8, WARPS);
+    }
+    if (threadIdx.x == 0) { todo[0] = 0; todo[1] = 0; }
+    for (int i = threadIdx.x; i < QSLOTS * C::QFRAG / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(smem_gen + qfrag_addr)[i] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-
-    // ---- lookup tables ----
     {
         const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
         constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
-        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS + 1) {
+        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS + 2) {
             int clo, chi;
             tl_key_field_codes((uint32_t)x, KB, clo, chi);
             *reinterpret_cast<uint32_t*>(smem_gen + tabK_base + x * KSTR + lane * 4) = pack_half2(cf[clo], cf[chi]);
         }
-        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS + 1) {
+        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS + 2) {
             if (C::VQUAD) {
                 int ag, bg, ag8, bg8;
                 tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
@@ -477,25 +695,48 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
             }
         }
     }
-    // everything above depends on constants only; from here on the preparation kernel's output is read
+    // everything above depends on constants only; from here on the caller's tensors and the workspace are used
+    if (threadIdx.x == 0) TQB_TRACE(1);
     pdl_wait();
-    if (lens_in_smem)
-        for (int i = threadIdx.x; i < p.batch; i += blockDim.x)
-            reinterpret_cast<int32_t*>(smem_gen + lens_addr)[i] = p.seq_lens[i];
+
+    // ---- sequence lengths (clamped to what the host announced); CTA 0 reports and clears empty sequences ----
+    const bool lens_in_smem = p.batch <= C::LENS_MAX;
+    Lens lens;
+    lens.sm = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + misc + C::OFF_LENS) : nullptr;
+    if (lens_in_smem || blockIdx.x == 0) {
+        for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
+            int flag;
+            const int e = encode_len(p, p.lens_in[i], flag);
+            if (lens_in_smem) reinterpret_cast<int32_t*>(smem_gen + misc + C::OFF_LENS)[i] = e;
+            if (blockIdx.x == 0) {
+                if (flag) atomicOr(p.status, flag);
+                if ((e & LEN_MASK) == 0)            // nothing to attend to: the output rows are zero
+                    for (int k = 0; k < p.q_heads * D; k++) store_out(p.out, p.out_dtype, (int64_t)i * p.q_heads * D + k, 0.0f);
+            }
+        }
+    }
     __syncthreads();
+
+    // ---- the CTA's first item is prepared by all warps together ----
+    if (threadIdx.x == 0) TQB_TRACE(2);
+    StageCursor<SR, GROUPS> cur;
+    cur.start(p, lens);
+    if (cur.valid()) {                                // (uniform over the CTA)
+        prepare_item<D, KB, VB, true>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                      reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch,
+                                      threadIdx.x, blockDim.x);
+        __syncthreads();
+        if (threadIdx.x == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
+    }
+    if (threadIdx.x == 0) TQB_TRACE(3);
     const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
     const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
 
-    // ---- producer warp: streams the CTA's items.  Lane 0 owns the barriers and the stage headers and
-    // issues the one bulk copy of a stage of a contiguous cache; for a paged cache every record is its own
-    // copy (pages are scattered), and the 32 lanes issue them side by side.  All lanes track the cursor.
     if (warp == WARPS) {
-        StageCursor<SR, GROUPS> cur;
-        cur.item = blockIdx.x;
-        cur.total_items = p.batch * p.kv_heads * p.nchunks;
-        cur.stride = gridDim.x;
-        cur.tiles_left = 0;
-        cur.open(p, lens);
+        // ---- producer warp: streams the CTA's items.  Lane 0 owns the barriers and the stage headers and
+        // issues the one bulk copy of a stage of a contiguous cache; for a paged cache every record is its own
+        // copy (pages are scattered), and the 32 lanes issue them side by side.  All lanes track the cursor.
         bool ok = true;
         int end_marks = 0;
         uint32_t n = 0;
@@ -512,6 +753,11 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
             }
             if (n >= NS) {
                 if (lane == 0) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (ok && cur.valid() && cur.append && cur.stage_idx == 0) {
+                // the new token of this item's unit must be in the record store before its record is copied
+                if (lane == 0) ok = mbar_wait(qfull_addr + 8 * (cur.seq % QSLOTS), (cur.seq / QSLOTS) & 1);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
             if (!ok) break;
@@ -552,41 +798,104 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         if (!ok && lane == 0) {
             // The consumers stopped releasing stages.  Record it and give the copies still in flight a
             // bounded chance to land before this CTA's shared memory is released.
-            atomicExch(p.status, 1);
+            atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
             for (uint32_t i = (n > (uint32_t)NS ? n - NS : 0); i < n; i++)
                 (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);   // (padding stages complete at once)
         }
-        return;
-    }
-
+    } else if (warp == WARPS + 1) {
+        // ---- helper warp: prepares the CTA's second, third, ... item while the previous one streams ----
+        for (;;) {
+            cur.next_item(p, lens);
+            if (!cur.valid()) break;
+            const int q = cur.seq % QSLOTS, use = cur.seq / QSLOTS;
+            bool ok = true;
+            if (use >= 1) {                         // the slot's previous fragments have been taken by every consumer warp
+                if (lane == 0) ok = mbar_wait(qempty_addr + 8 * q, (use - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (!ok) {
+                if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
+                break;
+            }
+#ifdef TQB_DECODE_TRACE
+            const unsigned long long tp0 = trace_now();
+#endif
+            prepare_item<D, KB, VB, false>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                           reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr + q * C::QFRAG), scratch, lane, 32);
+            __syncwarp();
+#ifdef TQB_DECODE_TRACE
+            if (lane == 0) { TQB_TRACE_ADD(8, trace_now() - tp0); TQB_TRACE_ADD(9, 1); }
+#endif
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr + 8 * q) : "memory");
+        }
+    } else {
     // ---- consumers: group (warp / WPG) takes every GROUPS-th stage; its warp i takes records RPW*i .. RPW*i+RPW-1 ----
     WarpState<C::MT> st;
-    int unit = 0, chunk_idx = 0;
+    int unit = 0, chunk_idx = 0, seq = -1;
+    int owed = -1;                                    // unit whose arrival this warp still has to announce
     st.m0 = st.m1 = st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
     const int r0 = RPW * (warp % WPG);
+    // Arrival of this warp's partial of unit u: the warp that brings the unit's count to (its chunks) x
+    // (consumer warps) owns the merge and queues the unit for the tail phase.
+    auto announce = [&](int u) {
+        __threadfence();
+        __syncwarp();
+        int merge_here = 0;
+        if (lane == 0) {
+            const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
+            const int expected = ((S + p.chunk - 1) / p.chunk) * WARPS;
+            if (atomicAdd(p.unit_cnt + u, 1) + 1 == expected) {
+                atomicExch(p.unit_cnt + u, 0);                    // clean for the next call
+                __threadfence();
+                const int slot = atomicAdd(todo, 1);
+                if (slot < TODO_MAX) todo[4 + slot] = u;
+                else merge_here = 1;                              // queue full: merge right here
+            }
+        }
+        if (__shfl_sync(0xffffffffu, merge_here, 0)) {
+            const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
+            const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
+            for (int nh = 0; nh < p.group; nh++) merge_head<D>(p, u, nh, nparts, lane);
+        }
+    };
     for (uint32_t n = warp / WPG;; n += GROUPS) {
         const int s = n % NS;
-        const bool ok = mbar_wait(full_addr + 8 * s, (n / NS) & 1);
-        if (!__all_sync(0xffffffffu, ok)) {           // a copy never arrived: flag it and stop
-            if (lane == 0) atomicExch(p.status, 1);
+        bool ok = mbar_wait(full_addr + 8 * s, (n / NS) & 1);
+        uint4 meta = make_uint4(0, 0, 0, 0);
+        if (ok)
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(meta.x), "=r"(meta.y), "=r"(meta.z), "=r"(meta.w) : "r"(meta_addr + s * 16));
+        if (ok && (meta.z & F_FIRST) && !(meta.z & F_END)) {      // this group's first stage of an item
+            seq++;
+#ifdef TQB_DECODE_TRACE
+            const unsigned long long tq0 = trace_now();
+            if (threadIdx.x == 0 && seq == 0) TQB_TRACE(4);
+#endif
+            ok = mbar_wait(qfull_addr + 8 * (seq % QSLOTS), (seq / QSLOTS) & 1);
+#ifdef TQB_DECODE_TRACE
+            if (threadIdx.x == 0) TQB_TRACE_ADD(10, trace_now() - tq0);
+#endif
+        }
+        if (!__all_sync(0xffffffffu, ok)) {           // a copy or the helper warp never arrived: flag it and stop
+            if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
             break;
         }
-        uint4 meta;
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(meta.x), "=r"(meta.y), "=r"(meta.z), "=r"(meta.w) : "r"(meta_addr + s * 16));
         if (meta.z & F_END) {                         // end of the stream (release the marker's slot as well)
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
             break;
         }
         const int nt = meta.z & 0xffff;
-        if (meta.z & F_FIRST) {                       // this group's first stage of an item
+        if (meta.z & F_FIRST) {
             unit = (int)meta.x; chunk_idx = (int)meta.y;
             st.m0 = st.m1 = 0.0f; st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
 #pragma unroll
             for (int mt = 0; mt < C::MT; mt++) { st.O[mt][0] = st.O[mt][1] = st.O[mt][2] = st.O[mt][3] = 0.0f; }
-            const uint2* qsrc = reinterpret_cast<const uint2*>(p.qfrag) + ((int64_t)unit * C::MT) * 32 + lane;
+            const uint32_t qsrc = qfrag_addr + (seq % QSLOTS) * C::QFRAG + lane * 8;
 #pragma unroll
-            for (int ks = 0; ks < C::MT; ks++) { const uint2 v = qsrc[ks * 32]; st.qf[ks][0] = v.x; st.qf[ks][1] = v.y; }
+            for (int ks = 0; ks < C::MT; ks++)
+                asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(st.qf[ks][0]), "=r"(st.qf[ks][1]) : "r"(qsrc + ks * 256));
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qempty_addr + 8 * (seq % QSLOTS)) : "memory");
         }
         if (r0 < nt) {
             const uint32_t rec = slot_addr(s) + r0 * C::REC;
@@ -611,6 +920,15 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
 
         if (meta.z & F_LAST) {                        // this group's last stage of the item: the warp's partial
+            // The arrival of the PREVIOUS item is announced first: its partial was stored an item ago, so the
+            // fence that orders those stores before the counter finds nothing left to wait for.
+#ifdef TQB_DECODE_TRACE
+            const unsigned long long ta0 = trace_now();
+#endif
+            if (owed >= 0) announce(owed);
+#ifdef TQB_DECODE_TRACE
+            if (threadIdx.x == 0) TQB_TRACE_ADD(11, trace_now() - ta0);
+#endif
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
                 st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, o);
@@ -635,99 +953,44 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_parti
                     p.part_acc[(pbase + h1) * D + dg8] = st.O[mt][3];
                 }
             }
+            owed = unit;
         }
     }
-}
+    if (threadIdx.x == 0) TQB_TRACE(5);
+    if (owed >= 0) announce(owed);
 
-// =================================================================================================
-// 3. merge of the chunks + inverse value rotation
-// =================================================================================================
-// One CTA per (unit, query head of the group).  Threads are (chunk group cg) x (dimension j).  Every
-// global load that does not depend on another one is issued up front (chunk maxima and sums, the first
-// eight accumulator rows of the thread, its rows of R_v), so the kernel costs about one memory round
-// trip.
-// 256 threads for head_dim 64 (all CTAs of the benchmark shape are then resident at once), else 512.
-constexpr int MERGE_MAX_CHUNKS = 1024;
-constexpr int MERGE_BATCH = 16;
+    // ---- tail phase (consumer warps only: named barrier 1) ----
+    asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
+    if (threadIdx.x == 0) { TQB_TRACE(6); TQB_TRACE_ADD(12, todo[0]); }
+    {
+        const int queued = min(todo[0], TODO_MAX);
+        for (int task = warp; task < queued * p.group; task += WARPS) {
+            const int u = todo[4 + task / p.group], nh = task % p.group;
+            const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
+            const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
+            merge_head<D>(p, u, nh, nparts, lane);
+        }
+    }
+    if (threadIdx.x == 0) TQB_TRACE(7);
+    }   // consumers
 
-template <typename OutT, int MERGE_THREADS>
-__global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const DecodeParams p, int dim,
-                                                                     const float* __restrict__ Rv,
-                                                                     OutT* __restrict__ out,
-                                                                     int32_t* __restrict__ advance) {
-    __shared__ float sm_m[MERGE_MAX_CHUNKS];
-    __shared__ float sm_l[MERGE_MAX_CHUNKS];
-    __shared__ float red[MERGE_THREADS];
-    __shared__ float y[128];
-    const int u = blockIdx.x / p.group, n = blockIdx.x - u * p.group;
-    const int b = u / p.kv_heads, h = u - b * p.kv_heads;
-    const int tid = threadIdx.x, groups = MERGE_THREADS / dim, cg = tid / dim, j = tid - cg * dim;
-    const int rows = dim / groups;                       // rows of R_v per thread (8, 16 or 32)
-    pdl_trigger();
-    constexpr int RVN = MERGE_THREADS == 256 ? 16 : 8;
-    float rv[RVN];                                       // first RVN of this thread's R_v rows (a constant input:
-#pragma unroll                                           // fetched while the streaming kernel may still be running)
-    for (int k = 0; k < RVN; k++) rv[k] = k < rows ? Rv[(int64_t)(cg + k * groups) * dim + j] : 0.0f;
-    pdl_wait();
-    const int S = p.seq_lens[b];
-    // a fused step publishes the new length once nothing of this call reads the caller's array any more
-    if (advance && h == 0 && n == 0 && threadIdx.x == 0) advance[b] = S;
-    // every chunk contributes one partial per consumer warp of the streaming kernel
-    const int nch = min(((S + p.chunk - 1) / p.chunk) * p.sets, MERGE_MAX_CHUNKS);
-    const int64_t pbase = (int64_t)u * p.nchunks * p.sets * p.group + n;
-
-    for (int c = tid; c < nch; c += MERGE_THREADS) {
-        sm_m[c] = p.part_m[pbase + (int64_t)c * p.group];
-        sm_l[c] = p.part_l[pbase + (int64_t)c * p.group];
-    }
-    float raw[MERGE_BATCH];
-#pragma unroll
-    for (int k = 0; k < MERGE_BATCH; k++) {
-        const int c = cg + k * groups;
-        raw[k] = c < nch ? p.part_acc[(pbase + (int64_t)c * p.group) * dim + j] : 0.0f;
-    }
-    __syncthreads();
-
-    float M = NEG_INF;
-    for (int c = 0; c < nch; c++) M = fmaxf(M, sm_m[c]);
-    __syncthreads();
-    // the chunk weights 2^(m_c - M) are computed once (by the threads that loaded the chunk's m and l)
-    for (int c = tid; c < nch; c += MERGE_THREADS) {
-        const float w = exp2f(sm_m[c] - M);
-        sm_m[c] = w;
-        sm_l[c] *= w;
-    }
-    __syncthreads();
-    float L = 0.0f;
-    for (int c = 0; c < nch; c++) L += sm_l[c];
-    float acc = 0.0f;
-#pragma unroll
-    for (int k = 0; k < MERGE_BATCH; k++) {
-        const int c = cg + k * groups;
-        if (c < nch) acc = fmaf(sm_m[c], raw[k], acc);
-    }
-    for (int c = cg + MERGE_BATCH * groups; c < nch; c += groups)     // very long contexts only
-        acc = fmaf(sm_m[c], p.part_acc[(pbase + (int64_t)c * p.group) * dim + j], acc);
-    red[tid] = acc;
-    __syncthreads();
-    if (tid < dim) {
-        float a = 0.0f;
-        for (int gg = 0; gg < groups; gg++) a += red[gg * dim + tid];
-        y[tid] = (nch > 0 && L > 0.0f) ? a / L : 0.0f;
-    }
-    __syncthreads();
-    // out_k = sum_j y_j Rv[j][k]: this thread takes rows cg, cg + groups, ...
-    float o = 0.0f;
-#pragma unroll
-    for (int k = 0; k < RVN; k++) if (k < rows) o = fmaf(y[cg + k * groups], rv[k], o);
-    for (int k = RVN; k < rows; k++) o = fmaf(y[cg + k * groups], Rv[(int64_t)(cg + k * groups) * dim + j], o);
-    __syncthreads();
-    red[tid] = o;
-    __syncthreads();
-    if (tid < dim) {
-        float a = 0.0f;
-        for (int gg = 0; gg < groups; gg++) a += red[gg * dim + tid];
-        out[((int64_t)b * p.q_heads + h * p.group + n) * dim + tid] = from_f32<OutT>(a);
+    // ---- the CTA that leaves last publishes the new lengths of a fused step ----
+    if (p.step) {
+        __syncthreads();                              // every read of the lengths in this CTA (all roles) is over
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const int last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
+            if (last) atomicExch(p.done, 0);
+            todo[1] = last;
+        }
+        __syncthreads();
+        if (todo[1]) {
+            for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
+                int flag;
+                const int e = encode_len(p, __ldcg(p.lens_in + i), flag);
+                if (e & LEN_ROOM) p.lens_out[i] = e & LEN_MASK;
+            }
+        }
     }
 }
 
@@ -735,17 +998,16 @@ __global__ void __launch_bounds__(MERGE_THREADS) decode_merge_kernel(const Decod
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Tokens per work item: small enough that every warp of the grid gets several items, large enough
-// that the per-item partial (group x (D+2) floats) stays a few percent of the streamed bytes.
 // Tokens per (unit, chunk) work item of the streaming kernel.  Work items are dealt round-robin to the
-// CTAs (one per SM); every item yields one partial per consumer warp, so the chunk count per unit is
-// bounded by what the merge kernel keeps in shared memory.
+// CTAs (one per SM); small enough that every CTA gets several items, large enough that the per-item
+// partials (consumer warps x group x (D+2) floats) stay a few percent of the streamed bytes.  Every item
+// yields one partial per consumer warp, and the merge handles at most MERGE_MAX_CHUNKS per unit.
 static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets) {
     int best = 0;
     double best_cost = 1e300;
-    for (int64_t L = stage_tokens; L <= (int64_t)1 << 24; L *= 2) {
+    for (int64_t L = stage_tokens; L <= (int64_t)1 << 30; L *= 2) {
         const int64_t nch = (max_len + L - 1) / L;
-        if (nch * sets <= 1024) {
+        if (nch * sets <= MERGE_MAX_CHUNKS) {
             const int64_t rounds = (units * nch + ctas - 1) / ctas;
             const double cost = (double)rounds * ((double)std::min<int64_t>(L, max_len) + stage_tokens);
             if (cost <= best_cost) { best_cost = cost; best = (int)L; }
@@ -763,9 +1025,8 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), sm_count(), sets * 32, sets);
     w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
     size_t off = 0;
-    w.off_status = off; off = align_up(off + 256, 256);
-    w.off_lens = off;   off = align_up(off + (size_t)batch * 4, 256);    // sequence lengths of a fused step
-    w.off_qfrag = off;  off = align_up(off + (size_t)units * dim * 16, 256);   // (dim/16) x 64 words
+    w.off_status = off; off = align_up(off + 256, 256);                    // status word, exit counter
+    w.off_cnt = off;    off = align_up(off + (size_t)units * 4, 256);      // arrival counter per unit
     const size_t parts = (size_t)units * w.nchunks * sets * group;
     w.off_m = off;   off = align_up(off + parts * 4, 256);
     w.off_l = off;   off = align_up(off + parts * 4, 256);
@@ -775,21 +1036,22 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
 }
 
 template <int D, int KB, int VB, bool PAGED>
-static int launch_partial(const DecodeParams& p, cudaStream_t st) {
+static int launch_fused(const DecodeParams& p, cudaStream_t st) {
     using C = DecodeCfg<D, KB, VB>;
-    auto kern = decode_partial_kernel<D, KB, VB, PAGED>;
+    auto kern = decode_fused_kernel<D, KB, VB, PAGED>;
     TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
     const int64_t items = (int64_t)p.batch * p.kv_heads * p.nchunks;
     if (items + sm_count() >= 0x7fffffff)
         return fail(TQB_ERR_UNSUPPORTED, "decode_attention: too many (sequence, head, chunk) work items");
     const int grid = (int)std::min<int64_t>(sm_count(), items);
-    TQB_CUDA(launch_pdl(pdl_mask() & 2, kern, dim3(grid), dim3(C::THREADS), C::DYN, st, p));
-    return check_launch("decode_partial");
+    // programmatic dependent launch: the tables are built while the previous kernel of the stream drains
+    TQB_CUDA(launch_pdl(1, kern, dim3(grid), dim3(C::THREADS), C::DYN, st, p));
+    return check_launch("decode_fused");
 }
 
 template <int D, bool PAGED>
 static int dispatch_bits(int kbits, int vbits, const DecodeParams& p, cudaStream_t st) {
-#define TQB_CASE(kb, vb) if (kbits == kb && vbits == vb) return launch_partial<D, kb, vb, PAGED>(p, st);
+#define TQB_CASE(kb, vb) if (kbits == kb && vbits == vb) return launch_fused<D, kb, vb, PAGED>(p, st);
     TQB_CASE(4, 2) TQB_CASE(4, 3) TQB_CASE(4, 4)
     TQB_CASE(3, 2) TQB_CASE(3, 3) TQB_CASE(3, 4)
     TQB_CASE(2, 2) TQB_CASE(2, 3) TQB_CASE(2, 4)
@@ -802,23 +1064,21 @@ static int dispatch_bits(int kbits, int vbits, const DecodeParams& p, cudaStream
 extern "C" size_t tqb_decode_attention_workspace_bytes(int batch, int q_heads, int kv_heads, int dim,
                                                        int64_t max_len) {
     if (batch <= 0 || kv_heads <= 0 || q_heads <= 0 || dim <= 0 || q_heads % kv_heads) return 0;
+    if (max_len < 0 || max_len > tqb::MAX_LEN_LIMIT) return 0;
     return tqb::plan_workspace(batch, q_heads, kv_heads, dim, max_len).total;
 }
 
 namespace tqb {
-static int g_phases = 7;   // launches a decode call makes: 1 = preparation, 2 = streaming kernel, 4 = merge
 
 // Shared by tqb_decode_attention (key == nullptr) and tqb_decode_step (key, value: the new token of every
 // unit; lens_mut: the caller's sequence lengths, advanced by one at the end of the call).
 static int decode_common(const void* query, int q_dtype, const void* key, const void* value, int64_t kv_stride,
                          const float* bnd_k, const float* bnd_v, int32_t* lens_mut,
-                         int batch, int q_heads, int kv_heads,
-                                    int dim, const uint8_t* store, int64_t max_seq,
-                                    const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
-                                    int max_blocks, int block_size, const float* rot_k, const float* cent_k,
-                                    int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,
-                                    void* workspace, size_t workspace_bytes, void* out, int out_dtype,
-                                    void* stream) {
+                         int batch, int q_heads, int kv_heads, int dim, const uint8_t* store, int64_t max_seq,
+                         const int32_t* seq_lens, int64_t max_len, const int32_t* block_tables,
+                         int max_blocks, int block_size, const float* rot_k, const float* cent_k,
+                         int kbits, const float* rot_v, const float* cent_v, int vbits, float scale,
+                         void* workspace, size_t workspace_bytes, void* out, int out_dtype, void* stream) {
     using namespace tqb;
     TQB_REQUIRE(batch >= 0 && q_heads > 0 && kv_heads > 0, "decode_attention: bad head counts");
     TQB_REQUIRE(q_heads % kv_heads == 0, "decode_attention: q_heads (%d) must be a multiple of kv_heads (%d)",
@@ -827,10 +1087,19 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
     if (dim != 64 && dim != 128)
         return fail(TQB_ERR_UNSUPPORTED, "decode_attention: head_dim must be 64 or 128, got %d", dim);
     if (group > 8) return fail(TQB_ERR_UNSUPPORTED, "decode_attention: at most 8 query heads per KV head, got %d", group);
+    // everything is validated before the first launch: a refused call has no side effects
+    if (kbits < 2 || kbits > 4 || vbits < 2 || vbits > 4)
+        return fail(TQB_ERR_UNSUPPORTED, "decode_attention: key/value bits must be 2..4, got %d/%d", kbits, vbits);
+    if (q_dtype != TQB_F32 && q_dtype != TQB_F16 && q_dtype != TQB_BF16)
+        return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
+    if (out_dtype != TQB_F32 && out_dtype != TQB_F16 && out_dtype != TQB_BF16)
+        return fail(TQB_ERR_INVALID, "decode_attention: unknown output dtype %d", out_dtype);
+    TQB_REQUIRE(max_len >= 0, "decode_attention: negative max_len");
+    if (max_len > MAX_LEN_LIMIT)
+        return fail(TQB_ERR_UNSUPPORTED, "decode_attention: max_len %lld exceeds the limit of 2^30 tokens", (long long)max_len);
     if (batch == 0) return TQB_OK;
     TQB_REQUIRE(query && store && seq_lens && rot_k && cent_k && rot_v &&
                 cent_v && workspace && out, "decode_attention: null pointer");
-    TQB_REQUIRE(max_len >= 0, "decode_attention: negative max_len");
     const bool paged = block_tables != nullptr;
     if (paged) {
         TQB_REQUIRE(block_size > 0 && block_size % 16 == 0, "decode_attention: block_size must be a multiple of 16, got %d", block_size);
@@ -847,56 +1116,24 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
 
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     DecodeParams p{};
-    p.store = store; p.sets = dim == 64 ? 16 : 8;
-    p.seq_lens = seq_lens; p.block_tables = block_tables; p.max_seq = max_seq;
+    p.store = const_cast<uint8_t*>(store);
+    p.lens_in = seq_lens; p.lens_out = lens_mut; p.block_tables = block_tables;
+    p.max_seq = paged ? (int64_t)max_blocks * block_size : max_seq; p.max_len = max_len;
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = group;
     p.max_blocks = max_blocks; p.block_size = block_size; p.chunk = w.chunk; p.nchunks = w.nchunks;
-    p.cent_k = cent_k; p.cent_v = cent_v;
+    p.step = key != nullptr ? 1 : 0;
+    p.query = query; p.key = key; p.value = value; p.in_dtype = q_dtype; p.kv_stride = kv_stride;
+    p.rot_k = rot_k; p.rot_v = rot_v; p.bnd_k = bnd_k; p.bnd_v = bnd_v; p.cent_k = cent_k; p.cent_v = cent_v;
+    p.scale = scale; p.out = out; p.out_dtype = out_dtype;
     p.status = reinterpret_cast<int*>(ws + w.off_status);
-    uint32_t* qfrag = reinterpret_cast<uint32_t*>(ws + w.off_qfrag);
-    p.qfrag = qfrag;
+    p.done = p.status + 1;
+    p.unit_cnt = reinterpret_cast<int*>(ws + w.off_cnt);
     p.part_m = reinterpret_cast<float*>(ws + w.off_m);
     p.part_l = reinterpret_cast<float*>(ws + w.off_l);
     p.part_acc = reinterpret_cast<float*>(ws + w.off_acc);
     cudaStream_t st = (cudaStream_t)stream;
-    const int units = batch * kv_heads;
-
-    int32_t* lens_now = reinterpret_cast<int32_t*>(ws + w.off_lens);
-    if (key) p.seq_lens = lens_now;
-    cudaError_t launch_err = cudaSuccess;
-    if (g_phases & 1) {
-#define TQB_PREP(T, NQ) launch_err = launch_pdl(pdl_mask() & 1, decode_prepare_kernel<T, NQ>, dim3(units), dim3(256), 0, st,            \
-        (const T*)query, (const T*)key, (const T*)value, kv_stride, q_heads, kv_heads, group, dim, rot_k, rot_v, \
-        bnd_k, bnd_v, kbits, vbits, scale, const_cast<uint8_t*>(store), max_seq, seq_lens, lens_now, qfrag, p.status)
-        switch (q_dtype) {
-            case TQB_F32: if (dim == 64) TQB_PREP(float, 2); else TQB_PREP(float, 4); break;
-            case TQB_F16: if (dim == 64) TQB_PREP(__half, 2); else TQB_PREP(__half, 4); break;
-            case TQB_BF16: if (dim == 64) TQB_PREP(__nv_bfloat16, 2); else TQB_PREP(__nv_bfloat16, 4); break;
-            default: return fail(TQB_ERR_INVALID, "decode_attention: unknown query dtype %d", q_dtype);
-        }
-#undef TQB_PREP
-        TQB_CUDA(launch_err);
-        if (int e = check_launch("decode_prepare")) return e;
-    }
-
-    if (max_len > 0 && (g_phases & 2)) {
-        int e;
-        if (dim == 64) e = paged ? dispatch_bits<64, true>(kbits, vbits, p, st) : dispatch_bits<64, false>(kbits, vbits, p, st);
-        else e = paged ? dispatch_bits<128, true>(kbits, vbits, p, st) : dispatch_bits<128, false>(kbits, vbits, p, st);
-        if (e) return e;
-    }
-
-    if (!(g_phases & 4)) return TQB_OK;
-#define TQB_MERGE(T, TH) launch_err = launch_pdl(pdl_mask() & 4, decode_merge_kernel<T, TH>, dim3(units * group), dim3(TH), 0, st, p, dim, rot_v, (T*)out, lens_mut)
-    switch (out_dtype) {
-        case TQB_F32: if (dim == 64) TQB_MERGE(float, 256); else TQB_MERGE(float, 512); break;
-        case TQB_F16: if (dim == 64) TQB_MERGE(__half, 256); else TQB_MERGE(__half, 512); break;
-        case TQB_BF16: if (dim == 64) TQB_MERGE(__nv_bfloat16, 256); else TQB_MERGE(__nv_bfloat16, 512); break;
-        default: return fail(TQB_ERR_INVALID, "decode_attention: unknown output dtype %d", out_dtype);
-    }
-#undef TQB_MERGE
-    TQB_CUDA(launch_err);
-    return check_launch("decode_merge");
+    if (dim == 64) return paged ? dispatch_bits<64, true>(kbits, vbits, p, st) : dispatch_bits<64, false>(kbits, vbits, p, st);
+    return paged ? dispatch_bits<128, true>(kbits, vbits, p, st) : dispatch_bits<128, false>(kbits, vbits, p, st);
 }
 }  // namespace tqb
 
@@ -912,8 +1149,6 @@ extern "C" int tqb_decode_attention(const void* query, int q_dtype, int batch, i
                               block_size, rot_k, cent_k, kbits, rot_v, cent_v, vbits, scale, workspace,
                               workspace_bytes, out, out_dtype, stream);
 }
-
-extern "C" void tqb_debug_decode_phases(int mask) { tqb::g_phases = mask & 7; }
 
 extern "C" int tqb_decode_step(const void* query, const void* key, const void* value, int dtype,
                                int64_t kv_stride, int batch, int q_heads, int kv_heads, int dim, uint8_t* store,

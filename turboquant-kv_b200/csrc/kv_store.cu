@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) kv_convert_kernel(const StoreArgs a) {
         if (slot < 0) continue;
         uint8_t* rec = a.store + (slot >> 4) * (int64_t)recb;
         const int r = (int)(slot & 15);
-        float* nrm = reinterpret_cast<float*>(rec + ksec + vsec);
+        uint8_t* nsec = rec + ksec + vsec;
         for (int which = 0; which < (a.vb ? 2 : 1); which++) {   // 0 = keys, 1 = values
             const int bits = which ? a.vb : a.kb;
             uint8_t* packed = which ? a.v_packed : a.k_packed;
@@ -69,8 +69,9 @@ __global__ void __launch_bounds__(256) kv_convert_kernel(const StoreArgs a) {
                 }
             }
             if (norms && lane == 0) {
-                if (IMPORT) nrm[16 * which + r] = norms[row];
-                else norms[row] = nrm[16 * which + r];
+                float* nrm = reinterpret_cast<float*>(nsec + tl_norm_offset(a.vb, which, r));
+                if (IMPORT) *nrm = norms[row];
+                else norms[row] = *nrm;
             }
         }
     }

@@ -26,7 +26,7 @@ int sm_count() {
 
 extern "C" {
 
-int tqb_abi_version(void) { return 1; }
+int tqb_abi_version(void) { return 2; }
 
 const char* tqb_last_error(void) { return tqb::last_error_buffer(); }
 

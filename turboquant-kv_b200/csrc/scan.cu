@@ -8,16 +8,17 @@
 //                           writes them as mma.sync B fragments split into fp16 hi + lo parts.
 //   2. scan_kernel          persistent warps stream 16-row tiles of packed codes + norms through a
 //                           per-warp TMA ring (cp.async.bulk + mbarrier).  Codes become fp16 centroid
-//                           hi/lo pairs through a 256-entry shared-memory table indexed by one byte
-//                           (= two codes); two MMAs per 16 dims (c_hi x [q_hi | q_lo], c_lo x [q_hi | 0])
-//                           give float32-class scores for 4 queries at once.  Each warp keeps a sorted
-//                           candidate list of k+8 entries per query in shared memory; insertions are
-//                           warp-cooperative and rare once the threshold has risen.
-//   3. scan_merge_kernel    per query: selects the best k+8 of all warps' candidates, RE-SCORES them in
+//                           pairs through a 256-entry shared-memory table indexed by one byte (= two
+//                           codes); one MMA per 16 dims (c_fp16 x [q_hi | q_lo]) scores 4 queries at
+//                           once.  Each warp keeps a sorted candidate list of kk = k + 8 entries per
+//                           query; insertions are warp-cooperative and rare once the threshold has risen.
+//   3. scan_merge_kernel    per query: selects the best k + 24 of all lists' candidates, RE-SCORES them in
 //                           float32 in exactly the upstream summation order (table[j][code] added for
 //                           j = 0..d-1, then * norm), sorts by (score desc, id asc) and emits k.
 // The reported scores are therefore bit-identical to the upstream C++ arithmetic; the tensor-core
-// pass only has to rank well enough to put the true top-k among the k+8 survivors.
+// pass only has to RANK: its scores carry the fp16 rounding of the 16 centroids (relative 2^-12 per
+// term, the queries keep 22 bits).  A true top-k row is lost only if more rows than the margin overtake
+// it through that rounding: 8 within the few thousand rows one warp sees, 24 within the whole database.
 //
 // Dims 64 and 128 with 2..4 bits take the tensor-core path; every other supported shape takes
 // scan_generic_kernel (one row per lane, float32 table lookups) with the same list and merge code.
@@ -31,7 +32,8 @@
 namespace tqb {
 
 constexpr int SCAN_TILE = 16;
-constexpr int SCAN_MARGIN = 8;          // extra candidates kept beyond k
+constexpr int SCAN_MARGIN = 8;          // extra candidates a list keeps beyond k
+constexpr int SCAN_SELECT_MARGIN = 24;  // extra candidates the merge re-scores exactly beyond k
 constexpr int SCAN_WARPS = 8;
 constexpr int QG = 4;                   // queries per tensor-core pass
 constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
@@ -74,6 +76,9 @@ __device__ __forceinline__ uint32_t s_pack_half2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Candidates kept per list for a top-k request.
+__host__ __device__ inline int scan_kk(int k) { return k + SCAN_MARGIN; }
+
 // (score, id) ordering used everywhere: higher score first, lower id first among equal scores.
 __device__ __forceinline__ bool better(float s, int id, float ts, int tid) {
     return s > ts || (s == ts && id < tid);
@@ -83,7 +88,7 @@ struct ScanParams {
     const uint8_t* packed; const float* norms; int64_t n;
     const uint8_t* records;             // non-null: the database as key-only 16-row records (tiled_layout.cuh)
     int combine;                        // record scan: one merged candidate list per CTA instead of one per warp
-    int dim, bits, nq, k, kk;           // kk = k + SCAN_MARGIN candidates kept per list
+    int dim, bits, nq, k, kk;           // kk = scan_kk(k) candidates kept per list
     const float* rot; const float* cent; const float* queries;
     int64_t id_offset;
     int lists_per_query;                // candidate lists written per query (= warps in the grid)
@@ -126,9 +131,9 @@ __device__ __forceinline__ void list_insert(float* ls, int* li, int kk, float s,
 // =================================================================================================
 // One CTA per group of QG queries.  q_rot[j] = sum_k q[k] * R[j][k], accumulated in k order with
 // separate multiply and add, the arithmetic of csrc/core/turboquant_core.cpp:425-433.
-// Fragment word layout: qfrag[group][ks][lane] = uint4 {B1 half0, B1 half1, B2 half0, B2 half1};
-// MMA column n = lane/4 holds query n/2 of the group: even n its fp16 hi part, odd n its lo part
-// (B1); B2 repeats the hi part in even columns and is zero in odd ones.
+// Fragment word layout: qfrag[group][ks][lane] = uint2 {half 0, half 1} of the B operand;
+// MMA column n = lane/4 holds query n/2 of the group: even n its fp16 hi part, odd n its lo part,
+// so that the two columns of a query add up to a 22-bit query against the fp16 centroids.
 __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, int use_mma) {
     extern __shared__ float sm[];
     float* qr = sm + p.dim;             // QG * dim (rotated queries); the raw queries follow
@@ -190,7 +195,7 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
         const int ks = idx >> 5, fl = idx & 31, g = fl >> 2, t = fl & 3;
         const int jq = g >> 1, part = g & 1;
         const float inv = qmax[jq] > 0.0f ? QUERY_SCALE / qmax[jq] : 0.0f;
-        uint32_t w[4];
+        uint32_t w[2];
         for (int half = 0; half < 2; half++) {
             int dlo, dhi;
             if (use_mma == 2) { dlo = 16 * ks + 8 * half + 2 * t; dhi = dlo + 1; }   // record layout: dims in order
@@ -198,9 +203,8 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
             const float a = qr[jq * p.dim + dlo] * inv, b = qr[jq * p.dim + dhi] * inv;
             const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
             w[half] = part ? s_pack_half2(a - ah, b - bh) : s_pack_half2(ah, bh);
-            w[2 + half] = part ? 0u : s_pack_half2(ah, bh);
         }
-        reinterpret_cast<uint4*>(p.qfrag)[((int64_t)grp * ksteps + ks) * 32 + fl] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint2*>(p.qfrag)[((int64_t)grp * ksteps + ks) * 32 + fl] = make_uint2(w[0], w[1]);
     }
 }
 
@@ -213,7 +217,7 @@ struct ScanCfg {
     static constexpr int RT = SCAN_TILE * PD;              // rows of a tile
     static constexpr int STAGE = RT + SCAN_TILE * 4;       // + norms
     static constexpr int LUT_ENTRIES = 1 << (2 * BITS);
-    static constexpr int LUT_BYTES = LUT_ENTRIES * 32 * 8; // uint2 {hi pair, lo pair} per lane
+    static constexpr int LUT_BYTES = LUT_ENTRIES * 32 * 4; // one fp16 pair per lane and entry
     static constexpr int KS = D / 16;
 };
 
@@ -221,7 +225,7 @@ template <int D, int BITS, int NS>
 __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanParams p) {
     using C = ScanCfg<D, BITS>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint2* lut = reinterpret_cast<uint2*>(smem_raw);
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem_raw);
     uint8_t* ring_all = smem_raw + C::LUT_BYTES;
     uint64_t* bars_all = reinterpret_cast<uint64_t*>(ring_all + (size_t)SCAN_WARPS * NS * C::STAGE);
     float* lists_s = reinterpret_cast<float*>(bars_all + SCAN_WARPS * NS);
@@ -244,16 +248,14 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
     for (int x = warp; x < C::LUT_ENTRIES; x += SCAN_WARPS) {
         int clo, chi;
         pair_index_codes<BITS>((uint32_t)x, clo, chi);
-        const float a = s_c[clo], b = s_c[chi];
-        const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
-        lut[x * 32 + lane] = make_uint2(s_pack_half2(ah, bh), s_pack_half2(a - ah, b - bh));
+        lut[x * 32 + lane] = s_pack_half2(s_c[clo], s_c[chi]);
     }
     __syncthreads();
 
     // B fragments of this query group stay in registers for the whole scan
-    uint4 qf[C::KS];
+    uint2 qf[C::KS];
     {
-        const uint4* src = reinterpret_cast<const uint4*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
+        const uint2* src = reinterpret_cast<const uint2*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
 #pragma unroll
         for (int ks = 0; ks < C::KS; ks++) qf[ks] = src[ks * 32];
     }
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
             for (int u = 0; u < 4; u++) iw[w][u] = pair_index_word<BITS>(P[w], u);
 #pragma unroll
         for (int ks = 0; ks < C::KS; ks++) {
-            uint2 e[4];
+            uint32_t e[4];
 #pragma unroll
             for (int half = 0; half < 2; half++)
 #pragma unroll
@@ -312,8 +314,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
                     key_element_slot<D>(2 * ks + half, second != 0, u, w, bl);
                     e[2 * half + second] = lut[((iw[w][u] >> (8 * bl)) & 0xFFu) * 32 + lane];
                 }
-            s_mma(acc, e[0].x, e[1].x, e[2].x, e[3].x, qf[ks].x, qf[ks].y);
-            s_mma(acc, e[0].y, e[1].y, e[2].y, e[3].y, qf[ks].z, qf[ks].w);
+            s_mma(acc, e[0], e[1], e[2], e[3], qf[ks].x, qf[ks].y);
         }
         const bool v0 = row0 + g < p.n, v1 = row0 + g + 8 < p.n;
         const float sc0 = v0 ? (acc[0] + acc[1]) * (nr[g] * qsc) : 0.0f;
@@ -362,11 +363,12 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32, 1) scan_kernel(const ScanPara
 // =================================================================================================
 // 2c. record scan: the database stored as key-only 16-row records (tiled_layout.cuh)
 // =================================================================================================
-// Same arithmetic as scan_kernel (two MMAs per 16 dims on fp16 hi / lo parts), but the rows arrive in
-// the order the MMA lanes consume them: one shared-memory load brings a lane's code fields of a record,
-// and each field (two codes) is the index of a 64-bit table entry {hi pair, lo pair}.  For 4-bit codes a
-// field is one byte and a single byte permute forms the entry's shared address (256-byte entries in a
-// 64 KB table on a 64 KB boundary of the shared window).  One persistent CTA per SM and query group: a
+// Same arithmetic as scan_kernel (one MMA per 16 dims, fp16 centroids x 22-bit queries), but the rows
+// arrive in the order the MMA lanes consume them: one shared-memory load brings a lane's code fields of a
+// record, and each field (two codes) is the index of a table entry holding the two centroids as an fp16
+// pair.  For 4-bit codes a field is one byte and a single byte permute forms the entry's shared address
+// (entries 256 bytes apart in a 64 KB window on a 64 KB boundary; the lanes' copies fill the first 128
+// bytes of an entry).  One persistent CTA per SM and query group: a
 // producer warp streams stages of SR records with one TMA bulk copy each; GROUPS groups of consumer
 // warps take the stages in turn, RPW records per warp.  Every wait is bounded.
 template <int D, int BITS>
@@ -376,7 +378,7 @@ struct RecScanCfg {
     static constexpr int REC = KSEC + 64;                    // + 16 norms
     static constexpr bool KBYTE = (2 * BITS == 8);
     static constexpr int LUT_ENTRIES = 1 << (2 * BITS);
-    static constexpr int LUT_BYTES = LUT_ENTRIES * 256;      // uint2 x 32 lanes per entry
+    static constexpr int LUT_BYTES = LUT_ENTRIES * 256;      // 32 lanes x 4 bytes per entry, entries 256 bytes apart
     static constexpr int KS = D / 16;
     static constexpr int NT = D == 64 ? 4 : 2;               // records a warp has in flight at once
     // Two consumer groups share the ring: with 8 stages each group has 4 stages in flight, which covers
@@ -390,12 +392,9 @@ struct RecScanCfg {
 };
 
 // NT records at once: acc[i] = this lane's part of the 16 x 8 score tile of record i.
-// Table entry x occupies 256 bytes: [hi pair of every lane: 32 x 4 B][lo pair: 32 x 4 B], so both parts
-// come from one computed address (32-bit loads may land in any register, which keeps the four operand
-// registers of an MMA contiguous without moves).  qf[ks] = B fragment {[q_hi | q_lo] half 0, half 1};
-// the second MMA needs [q_hi | 0]: the same registers with the odd columns (odd lane / 4) cleared.
+// qf[ks] = B fragment {[q_hi | q_lo] half 0, half 1}.
 template <int D, int BITS, int NT>
-__device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, const uint2 (&qf)[D / 16], uint32_t keep,
+__device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, const uint2 (&qf)[D / 16],
                                                int lane, float (&acc)[NT][4]) {
     using C = RecScanCfg<D, BITS>;
     uint32_t kw[NT][C::KL / 4];
@@ -406,7 +405,7 @@ __device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, cons
     }
 #pragma unroll
     for (int ks = 0; ks < C::KS; ks++) {
-        uint32_t ah[NT][4], al[NT][4];
+        uint32_t ah[NT][4];
 #pragma unroll
         for (int i = 0; i < NT; i++)
 #pragma unroll
@@ -417,13 +416,9 @@ __device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, cons
                     const uint32_t addr = C::KBYTE ? entry_addr<true>(kw[i], bit, 8, tab)
                                                    : lut_offset<C::KL / 4, 8>(kw[i], bit, 2 * BITS) + tab;
                     ah[i][2 * half + second] = lds32(addr);
-                    al[i][2 * half + second] = lds32(addr + 128);
                 }
-        const uint32_t b0 = qf[ks].x & keep, b1 = qf[ks].y & keep;
 #pragma unroll
         for (int i = 0; i < NT; i++) mma_f16(acc[i], ah[i], qf[ks].x, qf[ks].y);
-#pragma unroll
-        for (int i = 0; i < NT; i++) mma_f16(acc[i], al[i], b0, b1);
     }
 }
 
@@ -488,15 +483,18 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     }
     misc = tab_base + C::LUT_BYTES;
     const uint32_t full_addr = misc, empty_addr = misc + 64, meta_addr = misc + 128, cent_addr = misc + 192;
-    const uint32_t lists_addr = misc + C::FIXED;
+    // Candidate lists of up to 32 entries live in registers while the rows stream; they are written to
+    // shared memory only once the stream has ended, over the then idle second part of the ring.
+    const bool reg_lists = p.kk <= 32;
     const uint32_t lists_bytes = (uint32_t)WARPS * QG * p.kk * 8;
-    const uint32_t ringB = (lists_addr + lists_bytes + 127u) & ~127u;
+    const uint32_t ringB = (misc + C::FIXED + (reg_lists ? 0u : lists_bytes) + 127u) & ~127u;
+    const uint32_t lists_addr = reg_lists ? ringB : misc + C::FIXED;
     const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
     const int NS = min(C::MAX_NS, slotsA + slotsB);
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
     float* lists_s = reinterpret_cast<float*>(smem_gen + lists_addr);
     int* lists_i = reinterpret_cast<int*>(lists_s + WARPS * QG * p.kk);
-    if (NS < 2) {                                    // the host sizes kk so that this cannot happen
+    if (NS < 2 || lists_addr + lists_bytes > end) {  // the host sizes kk so that this cannot happen
         if (threadIdx.x == 0) atomicExch(p.status, 2);
         return;
     }
@@ -513,17 +511,15 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         mbar_init(empty_addr + threadIdx.x * 8, WPG);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (int e = threadIdx.x; e < WARPS * QG * p.kk; e += blockDim.x) { lists_s[e] = -__builtin_huge_valf(); lists_i[e] = ID_NONE; }
+    if (!reg_lists)
+        for (int e = threadIdx.x; e < WARPS * QG * p.kk; e += blockDim.x) { lists_s[e] = -__builtin_huge_valf(); lists_i[e] = ID_NONE; }
     __syncthreads();
     {
         const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
         for (int x = warp; x < C::LUT_ENTRIES; x += WARPS + 1) {
             int clo, chi;
             tl_key_field_codes((uint32_t)x, BITS, clo, chi);
-            const float a = cf[clo], b = cf[chi];
-            const float ah = __half2float(__float2half_rn(a)), bh = __half2float(__float2half_rn(b));
-            *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + lane * 4) = pack_half2(ah, bh);
-            *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + 128 + lane * 4) = pack_half2(a - ah, b - bh);
+            *reinterpret_cast<uint32_t*>(smem_gen + tab_base + x * 256 + lane * 4) = pack_half2(cf[clo], cf[chi]);
         }
     }
     pdl_wait();                                      // the query fragments come from the preparation kernel
@@ -531,6 +527,9 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
 
     const int64_t nrec = p.n / SCAN_TILE;            // full records; the last n % 16 rows belong to the merge kernel
     const int64_t nstages = (nrec + SR - 1) / SR;
+    RegLists RL;
+#pragma unroll
+    for (int jq = 0; jq < QG; jq++) { RL.s[jq] = -__builtin_huge_valf(); RL.i[jq] = ID_NONE; }
 
     if (warp == WARPS) {
         // ---- producer: stage index blockIdx.x, + gridDim.x, ...; one bulk copy per stage ----
@@ -570,17 +569,12 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         const uint32_t tab = C::KBYTE ? (tab_base | (uint32_t)(lane * 4)) : tab_base + lane * 4;
         uint2 qf[C::KS];
         {
-            const uint4* src = reinterpret_cast<const uint4*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
+            const uint2* src = reinterpret_cast<const uint2*>(p.qfrag) + ((int64_t)grp * C::KS) * 32 + lane;
 #pragma unroll
-            for (int ks = 0; ks < C::KS; ks++) { const uint4 v = src[ks * 32]; qf[ks] = make_uint2(v.x, v.y); }
+            for (int ks = 0; ks < C::KS; ks++) qf[ks] = src[ks * 32];
         }
-        const uint32_t keep = (g & 1) ? 0u : 0xffffffffu;
         float* ls = lists_s + (size_t)warp * QG * p.kk;
         int* li = lists_i + (size_t)warp * QG * p.kk;
-        const bool reg_lists = p.kk <= 32;            // else the lists stay in shared memory
-        RegLists RL;
-#pragma unroll
-        for (int jq = 0; jq < QG; jq++) { RL.s[jq] = -__builtin_huge_valf(); RL.i[jq] = ID_NONE; }
         const int myq = grp * QG + t;                 // the query whose scores this lane receives
         const float qsc = myq < p.nq ? p.qscale[myq] : 0.0f;
         ScanThreshold thr{-__builtin_huge_valf(), ID_NONE};
@@ -608,13 +602,14 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
                 const uint32_t rec = slot_addr(s) + (r0w + i0) * C::REC;
                 float acc[NT][4];
                 // (records past the stage's end hold stale bytes: computed but never inserted)
-                rec_scan_tiles<D, BITS, NT>(rec, tab, qf, keep, lane, acc);
+                rec_scan_tiles<D, BITS, NT>(rec, tab, qf, lane, acc);
 #pragma unroll
                 for (int i = 0; i < NT; i++) {
                     if (i0 + i >= mine) break;
-                    const uint32_t nr = rec + i * C::REC + C::KSEC + 4 * g;
-                    const float sc0 = (acc[i][0] + acc[i][1]) * (ldsf(nr) * qsc);
-                    const float sc1 = (acc[i][2] + acc[i][3]) * (ldsf(nr + 32) * qsc);
+                    uint2 nr;                          // norms of rows g and g + 8
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(nr.x), "=r"(nr.y) : "r"(rec + i * C::REC + C::KSEC + 8 * g));
+                    const float sc0 = (acc[i][0] + acc[i][1]) * (__uint_as_float(nr.x) * qsc);
+                    const float sc1 = (acc[i][2] + acc[i][3]) * (__uint_as_float(nr.y) * qsc);
                     const int id0 = (int)(meta.x + r0w + i0 + i) * SCAN_TILE + g, id1 = id0 + 8;
                     const bool ok0 = live && better(sc0, id0, thr.s, thr.i);
                     const bool ok1 = live && better(sc1, id1, thr.s, thr.i);
@@ -655,13 +650,17 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
         }
-        if (reg_lists && lane < p.kk) {
-#pragma unroll
-            for (int jq = 0; jq < QG; jq++) { ls[jq * p.kk + lane] = RL.s[jq]; li[jq * p.kk + lane] = RL.i[jq]; }
-        }
     }
 
     // ---- candidates -> global (every thread of the CTA gets here) ----
+    __syncthreads();                                  // nobody reads a stage any more: the ring may be reused
+    if (reg_lists && warp < WARPS && lane < p.kk) {
+#pragma unroll
+        for (int jq = 0; jq < QG; jq++) {
+            lists_s[(warp * QG + jq) * p.kk + lane] = RL.s[jq];
+            lists_i[(warp * QG + jq) * p.kk + lane] = RL.i[jq];
+        }
+    }
     __syncthreads();
     if (p.combine) {
         // one list per CTA and query: rank every candidate among the CTA's WARPS * kk by counting
@@ -770,7 +769,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) scan_generic_kernel(const Sca
 // 3. merge: best kk candidates per query -> exact float32 re-score -> sort -> top k
 // =================================================================================================
 constexpr int MERGE_THREADS = 256;
-constexpr int MERGE_MAX = TQB_SCAN_MAX_K + SCAN_MARGIN + SCAN_TILE;   // selected + tail rows
+constexpr int MERGE_MAX = TQB_SCAN_MAX_K + SCAN_SELECT_MARGIN + SCAN_TILE;   // selected + tail rows
 constexpr int SURV_MAX = 1024;          // candidates the fast selection path ranks among themselves
 
 __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanParams p) {
@@ -791,9 +790,10 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
     const int64_t ncand = (int64_t)p.lists_per_query * p.kk;
     const float* cs = p.cand_s + (int64_t)q * ncand;
     const int* ci = p.cand_id + (int64_t)q * ncand;
-    // ---- selection by the scan's scores ----
-    // Fast path: every list is sorted best-first, so the kk-th best of the list HEADS is a lower bound of
-    // the kk-th best candidate overall; the few candidates not below it are ranked among themselves.
+    // ---- selection by the scan's scores: the best ksel candidates go on to the exact re-score ----
+    // Fast path: every list is sorted best-first, so the ksel-th best of the list HEADS is a lower bound of
+    // the ksel-th best candidate overall; the few candidates not below it are ranked among themselves.
+    const int ksel = p.k + SCAN_SELECT_MARGIN;
     __shared__ float sv_s[SURV_MAX];
     __shared__ int sv_i[SURV_MAX];
     __shared__ int surv_n;
@@ -812,33 +812,42 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
             if (hi == ID_NONE) continue;
             int rank = 0;
             for (int l2 = 0; l2 < L; l2++) rank += better(sv_s[l2], sv_i[l2], hs, hi) ? 1 : 0;
-            if (rank == p.kk - 1) { tau_s = hs; tau_i = hi; }      // (ranks are distinct: at most one writer)
+            if (rank == ksel - 1) { tau_s = hs; tau_i = hi; }      // (ranks are distinct: at most one writer)
         }
     }
     __syncthreads();
-    for (int64_t e = tid; e < ncand; e += blockDim.x) {
-        const float sc = cs[e];
-        const int id = ci[e];
-        if (id == ID_NONE || better(tau_s, tau_i, sc, id)) continue;
-        const int pos = atomicAdd(&surv_n, 1);
-        if (pos < SURV_MAX) { sv_s[pos] = sc; sv_i[pos] = id; }
+    for (int64_t e0 = tid; e0 < ncand; e0 += (int64_t)blockDim.x * 8) {   // eight candidates per thread in flight
+        float sc[8];
+        int id[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int64_t e = e0 + (int64_t)u * blockDim.x;
+            sc[u] = e < ncand ? cs[e] : 0.0f;
+            id[u] = e < ncand ? ci[e] : ID_NONE;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (id[u] == ID_NONE || better(tau_s, tau_i, sc[u], id[u])) continue;
+            const int pos = atomicAdd(&surv_n, 1);
+            if (pos < SURV_MAX) { sv_s[pos] = sc[u]; sv_i[pos] = id[u]; }
+        }
     }
     __syncthreads();
     int nsel = 0;
     const bool fast = surv_n <= SURV_MAX;
     if (fast) {
-        nsel = min(p.kk, surv_n);
+        nsel = min(ksel, surv_n);
         for (int e = tid; e < surv_n; e += blockDim.x) {
             int rank = 0;
             for (int o = 0; o < surv_n; o++) rank += better(sv_s[o], sv_i[o], sv_s[e], sv_i[e]) ? 1 : 0;
-            if (rank < p.kk) sel_i[rank] = sv_i[e];
+            if (rank < ksel) sel_i[rank] = sv_i[e];
         }
         __syncthreads();
     }
     // General path (more survivors than the buffer holds): round r takes the best candidate worse than round r-1's.
     float prev_s = __builtin_huge_valf();
     int prev_i = -1;
-    for (int r = 0; !fast && r < p.kk; r++) {
+    for (int r = 0; !fast && r < ksel; r++) {
         float bs = -__builtin_huge_valf();
         int bi = ID_NONE;
         for (int64_t e = tid; e < ncand; e += blockDim.x) {
@@ -884,7 +893,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
                 tl_key_slot(p.dim, p.bits, id & 15, d, base, bit);
                 vals[warp][d] = T[d * levels + tl_read_bits(rec + base, bit, p.bits)];
             }
-            nrm = reinterpret_cast<const float*>(rec + ksec)[id & 15];
+            nrm = *reinterpret_cast<const float*>(rec + ksec + tl_norm_offset(0, 0, id & 15));
         } else {
             const uint8_t* row = p.packed + (int64_t)id * pd;
             for (int d = lane; d < p.dim; d += 32) {
@@ -963,7 +972,7 @@ static inline size_t s_align(size_t v) { return (v + 255) / 256 * 256; }
 static ScanPlan plan_scan(int nq, int64_t n, int dim, int bits, int k) {
     ScanPlan pl{};
     pl.mma = (dim == 64 || dim == 128) && bits >= 2 && bits <= 4;
-    pl.kk = k + SCAN_MARGIN;
+    pl.kk = scan_kk(k);
     pl.lists = sm_count() * SCAN_WARPS;
     pl.ngroups = (nq + QG - 1) / QG;
     size_t off = 0;
@@ -1012,7 +1021,7 @@ static bool rec_combine(int kk) { return 16 * kk <= 1024; }
 static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
     ScanPlan pl{};
     pl.mma = true;
-    pl.kk = k + SCAN_MARGIN;
+    pl.kk = scan_kk(k);
     pl.lists = sm_count() * (rec_combine(pl.kk) ? 1 : 16);
     pl.ngroups = (nq + QG - 1) / QG;
     size_t off = 0;
@@ -1036,7 +1045,7 @@ static int launch_scan_records(const ScanParams& p, int ngroups, int grid_x, cud
     const size_t worst = (C::KBYTE ? 2 * 65536 : C::LUT_BYTES + 4096) + C::FIXED + lists + 256;
     const size_t tail = worst < (size_t)C::DYN ? (size_t)C::DYN - worst : 0;
     const size_t stages = tail / C::STAGE + (C::KBYTE ? (65536 - 4096) / C::STAGE : 0);
-    if (stages < 2)
+    if (stages < 2 || worst >= (size_t)C::DYN)
         return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: k = %d leaves no room for the pipeline in shared memory", p.k);
     auto kern = scan_records_kernel<D, BITS>;
     TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
@@ -1192,7 +1201,7 @@ extern "C" int tqb_topk_merge(const float* scores, const int64_t* ids, int nq, i
 // every call before they are read.  Calls that may overlap on the device (different streams, different
 // host threads) race on the array and must be serialised by the caller; calls on one stream are safe.
 namespace tqb {
-constexpr size_t SCAN_STATIC_BYTES = (size_t)4 << 20;          // 4 MiB: e.g. up to 16 queries per call at k = 10
+constexpr size_t SCAN_STATIC_BYTES = (size_t)4 << 20;          // 4 MiB: whatever tqb_scan_topk_workspace_bytes says fits
 constexpr int SCAN_STATIC_MAX_DEVICES = 64;
 static __device__ __align__(256) unsigned char g_scan_scratch[SCAN_STATIC_BYTES];
 static void* g_scan_scratch_ptr[SCAN_STATIC_MAX_DEVICES] = {};
@@ -1226,8 +1235,9 @@ extern "C" int tqb_scan_topk_static(const float* queries, int nq, const uint8_t*
     using namespace tqb;
     TQB_REQUIRE(nq >= 0 && n >= 0, "scan_topk_static: negative size");
     if (nq == 0) return TQB_OK;
-    TQB_REQUIRE(dim > 0 && k >= 1 && k <= TQB_SCAN_MAX_K, "scan_topk_static: dim must be positive and k in 1..%d, got dim %d, k %d",
-                TQB_SCAN_MAX_K, dim, k);
+    TQB_REQUIRE(dim > 0 && k >= 1, "scan_topk_static: dim and k must be positive, got dim %d, k %d", dim, k);
+    if (k > TQB_SCAN_MAX_K)      // (the code tqb_scan_topk returns for the same request)
+        return fail(TQB_ERR_UNSUPPORTED, "scan_topk_static: k = %d exceeds the limit %d", k, TQB_SCAN_MAX_K);
     const size_t need = tqb_scan_topk_workspace_bytes(nq, n, dim, bits, k);
     if (need == 0 || need > SCAN_STATIC_BYTES)
         return fail(TQB_ERR_WORKSPACE,

@@ -8,11 +8,16 @@
 //
 // Tokens are grouped in tiles of 16.  One RECORD holds one tile of one (sequence, KV head):
 //
-//   [ key section : 32 lanes x KL bytes ][ value section : 32 lanes x VL bytes ][ 16 key norms f32 ][ 16 value norms f32 ]
+//   [ key section : 32 lanes x KL bytes ][ value section : 32 lanes x VL bytes ][ norm section : 32 floats ]
 //      KL = D*KB/16                          VL = D*VB/16                          record = 2*D*(KB+VB) + 128 bytes
 //
+// Norm section: 8 groups of 16 bytes, group g = { key norm of token g, key norm of token g+8, value norm
+// of token g, value norm of token g+8 } -- what MMA lane 4g+t needs of the record's norms, in one
+// 128-bit shared load (tl_norm_offset).
+//
 // The search index uses the same records without the value half (VB = 0): 16 database rows per record,
-// [ key section ][ 16 norms ], record = 2*D*KB + 64 bytes -- the upstream 68 bytes per row at D = 128, 4 bits.
+// [ key section ][ 16 norms: 8 pairs { row g, row g+8 } ], record = 2*D*KB + 64 bytes -- the upstream
+// 68 bytes per row at D = 128, 4 bits.
 //
 // Lane = 4*g + t is the mma.sync lane that consumes the bytes (g = lane/4, t = lane%4).
 //
@@ -44,6 +49,11 @@ TQB_HD int tl_val_lane_bytes(int D, int VB) { return D * VB / 16; }
 TQB_HD int tl_record_bytes(int D, int KB, int VB) { return 2 * D * (KB + VB) + (VB ? 128 : 64); }
 TQB_HD int tl_key_section(int D, int KB) { return 32 * tl_key_lane_bytes(D, KB); }
 TQB_HD int tl_val_section(int D, int VB) { return 32 * tl_val_lane_bytes(D, VB); }
+
+// Byte offset, inside the norm section, of the norm of token row r (which = 0: key, 1: value).
+TQB_HD int tl_norm_offset(int VB, int which, int r) {
+    return VB ? 16 * (r & 7) + 8 * which + 4 * (r >> 3) : 8 * (r & 7) + 4 * (r >> 3);
+}
 
 // A lane's key chunk is stored in one piece, except 32-byte chunks (D = 128, 4 bits), which are stored as
 // two 16-byte planes (the token-g half of all 32 lanes, then the token-g+8 half) so that each of the two
@@ -163,7 +173,7 @@ __device__ __forceinline__ void tiled_store_row(uint8_t* store, int which, int k
             tl_atomic_write(reinterpret_cast<uint32_t*>(rec + ksec), base * 8 + bit, vb, code[q]);
         }
     }
-    if (lane == 0) reinterpret_cast<float*>(rec + ksec + vsec)[(which == 1 ? 0 : 16) + r] = nrm;
+    if (lane == 0) *reinterpret_cast<float*>(rec + ksec + vsec + tl_norm_offset(vb, which - 1, r)) = nrm;
 }
 #endif  // __CUDACC__
 

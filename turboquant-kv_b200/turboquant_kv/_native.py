@@ -73,8 +73,6 @@ def lib():
                                            c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                            c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p,
                                            c_int, c_void_p]
-        L.tqb_debug_decode_phases.restype = None
-        L.tqb_debug_decode_phases.argtypes = [c_int]
         L.tqb_decode_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
                                       c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                       c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p,

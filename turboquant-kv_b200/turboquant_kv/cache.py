@@ -15,7 +15,7 @@ Additions for serving (none changes upstream behaviour):
     sequence and silently drops ``key[1:]``, cache.py:157-160 -- still the behaviour when
     ``batch_size`` is left at None);
   * ``decode_attention(layer, query)``: the fused one-token decode step (scores, softmax, values,
-    grouped-query heads) in three kernel launches;
+    grouped-query heads) in one kernel launch;
   * per-layer sequence lengths also live on the device so the decode path never synchronises.
 
 Prod mode: upstream allocates ``key_bits`` planes per token but ``quantize_prod`` returns
@@ -294,7 +294,7 @@ class QuantizedKVCache:
 
     def decode_step(self, layer_id: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                     scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``append`` of one token per sequence followed by ``decode_attention``, in three launches.
+        """``append`` of one token per sequence followed by ``decode_attention``, in one launch.
 
         query: (batch, q_heads, head_dim); key / value: (batch, num_heads, head_dim) or
         (batch, num_heads, 1, head_dim).  Same result as the two separate calls."""
@@ -319,7 +319,7 @@ class QuantizedKVCache:
         return res.unsqueeze(2) if squeeze else res
 
     def decode_status(self) -> int:
-        """0 when every bounded device-side wait of the last decode_attention completed (synchronises)."""
+        """Status bits raised by decode calls since the last query (kvstore.PackedKVStore.status); 0 = all good."""
         return 0 if self._kv is None else self._kv.status()
 
     # ------------------------------------------------------------------------------------------

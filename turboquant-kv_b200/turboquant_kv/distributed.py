@@ -63,6 +63,14 @@ class DistributedQuantizedKVCache:
                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.cache.decode_attention(layer_id, query, scale=scale, out=out)
 
+    def decode_step(self, layer_id: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                    scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Append the local heads' new token and attend, in one launch (QuantizedKVCache.decode_step)."""
+        return self.cache.decode_step(layer_id, query, key, value, scale=scale, out=out)
+
+    def decode_status(self) -> int:
+        return self.cache.decode_status()
+
     @property
     def seq_lens(self) -> torch.Tensor:
         return self.cache.seq_lens

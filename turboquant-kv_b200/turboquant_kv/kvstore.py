@@ -18,6 +18,9 @@ from . import _native as N
 from .reference import lloyd_max_codebook, make_rotation_matrix
 
 
+STATUS_WAIT_EXPIRED, STATUS_NO_SMEM, STATUS_UNIT_FULL, STATUS_LEN_CLAMPED = 1, 2, 4, 8   # TQB_DECODE_* of tqb200.h
+
+
 def pad16(n: int) -> int:
     return (n + 15) // 16 * 16
 
@@ -113,8 +116,7 @@ class PackedKVStore:
                    L.tqb_decode_attention_workspace_bytes(B, HQ, kv_heads, D, max(reserve_len, max_len)))
         if need == 0:
             raise RuntimeError(f"decode_attention: {HQ} query heads do not fit {kv_heads} KV heads")
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self._reserve_workspace(need)
         res = out if out is not None else torch.empty_like(q)
         paged = block_tables is not None
         with torch.cuda.device(self.device):
@@ -130,7 +132,7 @@ class PackedKVStore:
     def decode_step(self, store: torch.Tensor, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                     kv_heads: int, seq_lens: torch.Tensor, max_len: int, pitch: int, scale: Optional[float] = None,
                     out: Optional[torch.Tensor] = None, reserve_len: int = 0) -> torch.Tensor:
-        """Append one token per sequence and attend to it and everything before it, fused.
+        """Append one token per sequence and attend to it and everything before it, in one launch.
 
         query (batch, q_heads, head_dim); key / value (batch, kv_heads, head_dim), same dtype as the query.
         ``seq_lens`` (device int32) gives the write position and is advanced by one on the device;
@@ -149,8 +151,7 @@ class PackedKVStore:
                    L.tqb_decode_attention_workspace_bytes(B, HQ, kv_heads, D, max(reserve_len, max_len)))
         if need == 0:
             raise RuntimeError(f"decode_step: {HQ} query heads do not fit {kv_heads} KV heads")
-        if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self._reserve_workspace(need)
         res = out if out is not None else torch.empty_like(q)
         with torch.cuda.device(self.device):
             N.check(L.tqb_decode_step(
@@ -162,6 +163,22 @@ class PackedKVStore:
                 N.ptr(self._workspace), self._workspace.numel(), N.ptr(res), N.dtype_code(res.dtype), N.stream_of(q)))
         return res
 
+    def _reserve_workspace(self, need: int) -> None:
+        """The decode workspace starts zeroed (status word, arrival counters); the kernel keeps it clean."""
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
+
     def status(self) -> int:
-        """0 when every bounded device-side wait of the last decode completed (synchronises)."""
-        return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
+        """Status bits raised by the decode calls since the last status() (synchronises, then clears them):
+        0 = all good; STATUS_WAIT_EXPIRED / STATUS_NO_SMEM = results invalid (the workspace is re-zeroed here);
+        STATUS_UNIT_FULL = a fused step found a full unit and dropped its token; STATUS_LEN_CLAMPED = a
+        sequence length outside the announced bounds was clamped."""
+        if self._workspace is None:
+            return 0
+        word = self._workspace[:4].view(torch.int32)
+        value = int(word.item())
+        if value & (STATUS_WAIT_EXPIRED | STATUS_NO_SMEM):
+            self._workspace.zero_()
+        elif value:
+            word.zero_()
+        return value
