@@ -14,19 +14,21 @@
 //                   scale * log2(e), written as mma.sync B fragments (fp16) into one of two
 //                   shared-memory slots; for a fused step it also quantises the unit's new key and value
 //                   and stores them into the record store before the producer copies that record (the
-//                   item that holds the write position does this).  The CTA's first item is prepared by
-//                   all warps together before the roles split, so the start-up costs one round trip.
+//                   item that holds the write position does this).  The CTA's first item is prepared
+//                   before the roles split, by four warps while the others build the lookup tables.
+//                   It also speaks for the consumer warps: once all of them have stored their partial
+//                   of an item it bumps the unit's arrival counter (one fence for the lot); the helper
+//                   whose arrival completes a unit queues the unit for its CTA's tail phase.
 //   consumer warps  two groups take alternate stages, four records per warp.  Per record: scores =
 //                   K-codes x q on tensor cores (codes -> fp16 centroids through a 256-entry
 //                   shared-memory table indexed by one byte = 2 codes), online softmax in the log2
 //                   domain with a lazy running maximum, P^T via movmatrix, O^T += V^T-codes x P^T on
 //                   tensor cores, all in ROTATED space.  One (m, l, acc) partial per (item, warp).
-//   tail phase      every warp that writes a partial bumps its unit's arrival counter; the warp that
-//                   completes a unit queues it, and once the CTA's own items are done its consumer warps
-//                   merge the queued units: combine the partials of a (unit, query head), divide by l,
-//                   apply the inverse value rotation acc @ R_v (reference.py:362) and write the output.
-//                   No warp ever waits for another CTA.  The CTA that leaves last (exit counter)
-//                   publishes the advanced sequence lengths of a fused step.
+//   tail phase      once the CTA's own items are done its consumer warps merge the queued units: combine
+//                   the partials of a (unit, query head), divide by l, apply the inverse value rotation
+//                   acc @ R_v (reference.py:362) and write the output.  No warp ever waits for another
+//                   CTA.  The CTA that leaves last (exit counter) publishes the advanced sequence
+//                   lengths of a fused step.
 //
 // HBM traffic per token and KV head is the packed K row + packed V row + two float norms; everything
 // else lives in L2 / shared memory.
@@ -40,25 +42,6 @@
 #include "pipe.cuh"
 #include "tiled_layout.cuh"
 
-#ifdef TQB_DECODE_TRACE
-// Development aid, compiled only with -DTQB_DECODE_TRACE (never in the shipped library): wall-clock
-// timestamps of the phases of every CTA.
-__device__ unsigned long long g_decode_trace[256][16];
-__device__ __forceinline__ unsigned long long trace_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TQB_TRACE(slot) do { g_decode_trace[blockIdx.x][slot] = trace_now(); } while (0)
-#define TQB_TRACE_ADD(slot, v) do { g_decode_trace[blockIdx.x][slot] += (unsigned long long)(v); } while (0)
-extern "C" int tqb_debug_decode_trace(unsigned long long* host, int clear) {
-    if (clear) { static unsigned long long z[256 * 16]; return (int)cudaMemcpyToSymbol(g_decode_trace, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(host, g_decode_trace, sizeof(unsigned long long) * 256 * 16);
-}
-#else
-#define TQB_TRACE(slot) do {} while (0)
-#define TQB_TRACE_ADD(slot, v) do {} while (0)
-#endif
 
 namespace tqb {
 
@@ -67,7 +50,8 @@ constexpr float NEG_INF = -__builtin_huge_valf();
 constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score exceeds m + 4 (log2)
 constexpr int TILE = 16;                // tokens per MMA tile
 constexpr int QSLOTS = 2;               // query-fragment slots (the helper warp works one item ahead)
-constexpr int TODO_MAX = 64;            // completed units a CTA queues for its tail phase
+constexpr int DSLOTS = 4;               // "every consumer warp has stored its partial" barriers, one per item in flight
+constexpr int TODO_MAX = 60;            // completed units a CTA queues for its tail phase
 constexpr int LEN_ROOM = 1 << 30;       // flag in an encoded length: this step appends a token to the sequence
 constexpr int LEN_MASK = LEN_ROOM - 1;
 constexpr int64_t MAX_LEN_LIMIT = (int64_t)1 << 30;
@@ -91,7 +75,8 @@ struct DecodeParams {
     float scale;
     void* out; int out_dtype;
     // workspace views
-    int* status; int* done; int* unit_cnt;
+    int* status; int* done;                           // header words: status bits, exit counter
+    int* unit_cnt;                                    // per unit: arrivals of its chunks
     float* part_m; float* part_l; float* part_acc;
 };
 
@@ -105,6 +90,23 @@ __device__ __forceinline__ float load_in(const void* base, int dtype, int64_t id
     if (dtype == TQB_F32) return reinterpret_cast<const float*>(base)[idx];
     if (dtype == TQB_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+// Read-only 128-bit load that asks L1 to keep the line / not to allocate one.
+__device__ __forceinline__ float4 ldg_keep(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::evict_last.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ldg_stream(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
 }
 // Four consecutive elements (idx a multiple of 4, rows 8-byte aligned at least) as float4.
 __device__ __forceinline__ float4 load_in4(const void* base, int dtype, int64_t idx) {
@@ -183,16 +185,20 @@ struct DecodeCfg {
     static constexpr int STAGE = SR * REC;
     static constexpr int STAGE_TOKENS = SR * 16;
     static constexpr int THREADS = (WARPS + 2) * 32;                // consumer warps + producer warp + helper warp
+    // head_dim 64: the first four warps prepare the CTA's first item while the others build the lookup tables
+    // (one thread per row of R_k and R_v); head_dim 128 has too few warps for that and does one after the other.
+    static constexpr int PREP_WARPS = D == 64 ? 4 : 0;
     // Shared-memory plan (dynamic, the whole opt-in maximum):  [ring A | aligned tables | misc | ring B]
     static constexpr int DYN = 227 * 1024;
     static constexpr int LENS_MAX = 256;
     static constexpr int QFRAG = MT * 256;                          // one slot of query fragments: MT x 32 lanes x 8 B
     // misc: centroids (256) | barriers and stage headers (8*(8+8+16) = 256) | helper barriers (64) |
     //       boundaries (128) | unit vectors of the new key / value (2*D*4) | their codes (2*D) and norms (16) |
-    //       tail-phase queue (16 + 4*TODO_MAX) | lengths | query-fragment slots
-    static constexpr int OFF_BARS = 256, OFF_QBARS = OFF_BARS + 256, OFF_BND = OFF_QBARS + 64;
+    //       the unit's queries as float32 (8*D*4) | tail-phase queue (16 + 4*TODO_MAX) | lengths |
+    //       query-fragment slots
+    static constexpr int OFF_BARS = 256, OFF_QBARS = OFF_BARS + 256, OFF_BND = OFF_QBARS + 128;
     static constexpr int OFF_UNIT = OFF_BND + 128, OFF_CODES = OFF_UNIT + 2 * D * 4, OFF_NRM = OFF_CODES + 2 * D;
-    static constexpr int OFF_TODO = OFF_NRM + 16, OFF_LENS = OFF_TODO + 16 + 4 * TODO_MAX;
+    static constexpr int OFF_QVEC = OFF_NRM + 16, OFF_TODO = OFF_QVEC + 8 * D * 4, OFF_LENS = OFF_TODO + 16 + 4 * TODO_MAX;
     static constexpr int OFF_QFRAG = (OFF_LENS + LENS_MAX * 4 + 127) / 128 * 128;
     static constexpr int MISC_FIXED = OFF_QFRAG + QSLOTS * QFRAG;
     static constexpr int MISC = SMALL_K + SMALL_V + MISC_FIXED;
@@ -280,36 +286,43 @@ struct StageCursor {
 // =================================================================================================
 // item preparation: query fragments, and the new token of a fused step
 // =================================================================================================
-// Shared-memory scratch of the preparation (DecodeCfg::OFF_*), as generic pointers.
+// Shared-memory scratch of the preparation (DecodeCfg::OFF_*).
 struct PrepScratch {
     const float* bnd;                // [2][16] boundaries (keys, values), +inf beyond the last
+    float* qvec;                     // [8][D]  the unit's queries as float32
     float* unit;                     // [2][D]  unit vector of the new key / value
+    uint32_t qvec_addr, unit_addr;   //         shared addresses of qvec and unit
     uint8_t* codes;                  // [2][D]
     float* nrm;                      // [2]
 };
 
-// Prepares one item with `nthreads` threads (`tid` = 0..nthreads-1): a whole CTA (CTA_WIDE, barriers are
-// __syncthreads) or one warp.  Writes the B fragments of the unit's rotated queries into `qslot`:
-// element (ks, lane = 4n+t, half) of head n holds the rotated query coordinates (16ks + 8half + 2t, +1)
-// times scale * log2(e) as fp16 (11 significant bits whatever the magnitude; the products stay far inside
-// fp16's range); the columns of heads >= group stay zero.
+// Prepares one item with `nthreads` threads (`tid` = 0..nthreads-1): one warp (barriers are __syncwarp), or a
+// group of warps that meets on named barrier 2.  Writes the B fragments of the unit's rotated queries into
+// `qslot`: element (ks, lane = 4n+t, half) of head n holds the rotated query coordinates (16ks + 8half + 2t,
+// +1) times scale * log2(e) as fp16 (11 significant bits whatever the magnitude; the products stay far
+// inside fp16's range); the columns of heads >= group stay zero.
 //
 // With `append` it first quantises the unit's new key and value and stores them at position `pos`.  The
 // code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums and a
 // butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
 // code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
 // The stores are followed by a proxy fence: the producer copies that record with the TMA engine.
-template <int D, int KB, int VB, bool CTA_WIDE>
+template <int D, int KB, int VB, bool ONE_WARP>
 __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bool append, int pos,
                                              uint16_t* qslot, const PrepScratch& sc, int tid, int nthreads) {
     constexpr int NQ = D / 32;
     const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
     const int warp = tid >> 5, lane = tid & 31;
-    auto sync = [&]() { if (CTA_WIDE) __syncthreads(); else __syncwarp(); };
+    auto sync = [&]() {
+        if (ONE_WARP) __syncwarp();
+        else asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+    };
+    const int64_t q0 = ((int64_t)b * p.q_heads + h * p.group) * D;
+    for (int e = 4 * tid; e < p.group * D; e += 4 * nthreads)      // the unit's queries -> float32 in shared memory
+        *reinterpret_cast<float4*>(sc.qvec + e) = load_in4(p.query, p.in_dtype, q0 + e);
     if (append) {
         // norm and unit vector of the key (which = 0) and the value (1): one warp each, or one after the other
-        for (int which = CTA_WIDE ? warp : 0; which < 2; which += CTA_WIDE ? 2 : 1) {
-            if (CTA_WIDE && warp >= 2) break;
+        for (int which = ONE_WARP ? 0 : warp; which < 2; which += ONE_WARP ? 1 : 2) {
             const void* x = which ? p.value : p.key;
             const int64_t x0 = (int64_t)unit * p.kv_stride;
             float v[NQ], ss = 0.0f;
@@ -328,10 +341,11 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
     sync();
     // One thread per ROW of a rotation matrix: row j of R_k serves the unit's `group` queries and its new key
     // (the row is fetched once for all of them), row j of R_v the new value.  A row is fetched in batches of
-    // eight 128-bit loads that are all in flight together; the sums run over k ascending.
+    // eight 128-bit loads that are all in flight together; the loads ask L1 to keep the lines (evict-last):
+    // under a saturated memory system a round trip to L2 takes microseconds, and R_k is re-read for every
+    // item.  The sums run over k ascending.
     const float fold = p.scale * LOG2E;
     const int ntasks = append ? 2 * D : D;
-    const int64_t q0 = ((int64_t)b * p.q_heads + h * p.group) * D;
     for (int task = tid; task < ntasks; task += nthreads) {
         const int which = task / D, j = task - which * D;           // 0: R_k row (queries, key), 1: R_v row (value)
         const float4* row = reinterpret_cast<const float4*>((which ? p.rot_v : p.rot_k) + (int64_t)j * D);
@@ -339,18 +353,18 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
 #pragma unroll
         for (int n = 0; n < 8; n++) aq[n] = 0.0f;
 #pragma unroll 1
-        for (int k8 = 0; k8 < D / 4; k8 += 8) {
+        for (int kb = 0; kb < D / 4; kb += 8) {
             float4 r[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = __ldg(row + k8 + i);
+            for (int i = 0; i < 8; i++) r[i] = ldg_keep(row + kb + i);
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const int k0 = 4 * (k8 + i);
+                const int k0 = 4 * (kb + i);
                 if (which == 0) {
 #pragma unroll
                     for (int n = 0; n < 8; n++) {
                         if (n < p.group) {
-                            const float4 x = load_in4(p.query, p.in_dtype, q0 + (int64_t)n * D + k0);
+                            const float4 x = lds128f(sc.qvec_addr + (n * D + k0) * 4);
                             aq[n] = fmaf(x.x, r[i].x, aq[n]);
                             aq[n] = fmaf(x.y, r[i].y, aq[n]);
                             aq[n] = fmaf(x.z, r[i].z, aq[n]);
@@ -359,7 +373,7 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
                     }
                 }
                 if (append) {
-                    const float4 u = *reinterpret_cast<const float4*>(sc.unit + which * D + k0);
+                    const float4 u = lds128f(sc.unit_addr + (which * D + k0) * 4);
                     ax = fmaf(u.x, r[i].x, ax);
                     ax = fmaf(u.y, r[i].y, ax);
                     ax = fmaf(u.z, r[i].z, ax);
@@ -383,8 +397,7 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
     }
     sync();
     if (append) {
-        for (int which = CTA_WIDE ? warp : 0; which < 2; which += CTA_WIDE ? 2 : 1) {
-            if (CTA_WIDE && warp >= 2) break;
+        for (int which = ONE_WARP ? 0 : warp; which < 2; which += ONE_WARP ? 1 : 2) {
             uint32_t code[NQ];
 #pragma unroll
             for (int qq = 0; qq < NQ; qq++) code[qq] = sc.codes[which * D + lane + 32 * qq];
@@ -533,8 +546,18 @@ __device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int 
     constexpr int NQ = D / 32;
     const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
     const int64_t pbase = (int64_t)unit * p.nchunks * (D == 64 ? 16 : 8) * p.group + n;
+    // The kernel is a chain of round trips to L2; every phase keeps as many loads in flight as it can.
     float M = NEG_INF;
-    for (int c = lane; c < nparts; c += 32) M = fmaxf(M, __ldcg(p.part_m + pbase + (int64_t)c * p.group));
+    for (int c0 = 0; c0 < nparts; c0 += 128) {
+        float mv[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int c = c0 + 32 * k + lane;
+            mv[k] = c < nparts ? __ldcg(p.part_m + pbase + (int64_t)c * p.group) : NEG_INF;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) M = fmaxf(M, mv[k]);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     float L = 0.0f, acc[NQ];
@@ -542,24 +565,38 @@ __device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int 
     for (int i = 0; i < NQ; i++) acc[i] = 0.0f;
     for (int c0 = 0; c0 < nparts; c0 += 32) {
         const int c = c0 + lane;
+        const int cn = min(32, nparts - c0);                        // (a multiple of 8: 8 or 16 partials per chunk)
+        // the first sixteen partial rows of the block are requested together with its maxima and sums
+        float v[16][NQ];
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+            const float* row = p.part_acc + (pbase + (int64_t)(c0 + cc) * p.group) * D + lane;
+#pragma unroll
+            for (int i = 0; i < NQ; i++) v[cc][i] = cc < cn ? __ldcg(row + 32 * i) : 0.0f;
+        }
         float w = 0.0f;
         if (c < nparts) {
             const float m = __ldcg(p.part_m + pbase + (int64_t)c * p.group);
+            const float l = __ldcg(p.part_l + pbase + (int64_t)c * p.group);
             w = (m == NEG_INF) ? 0.0f : exp2f(m - M);
-            L = fmaf(__ldcg(p.part_l + pbase + (int64_t)c * p.group), w, L);
+            L = fmaf(l, w, L);
         }
-        const int cn = min(32, nparts - c0);                        // (a multiple of 8: 8 or 16 partials per chunk)
-        for (int cb = 0; cb < cn; cb += 8) {                        // eight partial rows in flight together
-            float v[8][NQ];
 #pragma unroll
-            for (int cc = 0; cc < 8; cc++) {
-                const float* row = p.part_acc + (pbase + (int64_t)(c0 + cb + cc) * p.group) * D + lane;
+        for (int cc = 0; cc < 16; cc++) {
+            const float wc = __shfl_sync(0xffffffffu, w, cc);
 #pragma unroll
-                for (int i = 0; i < NQ; i++) v[cc][i] = __ldcg(row + 32 * i);
+            for (int i = 0; i < NQ; i++) acc[i] = fmaf(wc, v[cc][i], acc[i]);
+        }
+        if (cn > 16) {
+#pragma unroll
+            for (int cc = 0; cc < 16; cc++) {
+                const float* row = p.part_acc + (pbase + (int64_t)(c0 + 16 + cc) * p.group) * D + lane;
+#pragma unroll
+                for (int i = 0; i < NQ; i++) v[cc][i] = 16 + cc < cn ? __ldcg(row + 32 * i) : 0.0f;
             }
 #pragma unroll
-            for (int cc = 0; cc < 8; cc++) {
-                const float wc = __shfl_sync(0xffffffffu, w, cb + cc);
+            for (int cc = 0; cc < 16; cc++) {
+                const float wc = __shfl_sync(0xffffffffu, w, 16 + cc);
 #pragma unroll
                 for (int i = 0; i < NQ; i++) acc[i] = fmaf(wc, v[cc][i], acc[i]);
             }
@@ -571,20 +608,21 @@ __device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int 
     float y[NQ], out[NQ];
 #pragma unroll
     for (int i = 0; i < NQ; i++) { y[i] = acc[i] * inv; out[i] = 0.0f; }
-    // out_k = sum_j y_j Rv[j][k]  (x = y @ R, reference.py:362); lane holds k = lane + 32 i
+    // out_k = sum_j y_j Rv[j][k]  (x = y @ R, reference.py:362); lane holds k = lane + 32 i.  R_v is read
+    // through L1: the warps of a CTA that merge at the same time share its lines.
 #pragma unroll
     for (int ij = 0; ij < NQ; ij++) {
 #pragma unroll 1
-        for (int jb = 0; jb < 32; jb += 8) {                        // eight rows of R_v in flight together
-            float r[8][NQ];
+        for (int jb = 0; jb < 32; jb += 16) {                       // sixteen rows of R_v in flight together
+            float r[16][NQ];
 #pragma unroll
-            for (int jj = 0; jj < 8; jj++) {
+            for (int jj = 0; jj < 16; jj++) {
                 const float* row = p.rot_v + (int64_t)(32 * ij + jb + jj) * D + lane;
 #pragma unroll
                 for (int i = 0; i < NQ; i++) r[jj][i] = __ldg(row + 32 * i);
             }
 #pragma unroll
-            for (int jj = 0; jj < 8; jj++) {
+            for (int jj = 0; jj < 16; jj++) {
                 const float yj = __shfl_sync(0xffffffffu, y[ij], jb + jj);
 #pragma unroll
                 for (int i = 0; i < NQ; i++) out[i] = fmaf(yj, r[jj][i], out[i]);
@@ -603,6 +641,7 @@ template <int D, int KB, int VB, bool PAGED>
 __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KB, VB>;
     constexpr int WARPS = C::WARPS, NS = C::NS, SR = C::SR, RPW = C::RPW, GROUPS = C::GROUPS, WPG = C::WPG;
+    constexpr int PREP_WARPS = C::PREP_WARPS;
     constexpr uint32_t F_FIRST = 1u << 16, F_LAST = 1u << 17, F_END = 1u << 18;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -630,6 +669,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     const uint32_t meta_addr = empty_addr + 8 * 8;               // one uint4 per stage: {unit, chunk, tiles | flags, valid tokens}
     const uint32_t qfull_addr = misc + C::OFF_QBARS;             // qfull[q]: the item's query fragments are in slot q
     const uint32_t qempty_addr = qfull_addr + 8 * QSLOTS;        // qempty[q]: every consumer warp has taken them
+    const uint32_t done_addr = qempty_addr + 8 * QSLOTS;         // done[d]: every consumer warp has stored its partial of the item
+    const uint32_t hdone_addr = done_addr + 8 * DSLOTS;          // the helper warp has announced all of the CTA's items
     const uint32_t qfrag_addr = misc + C::OFF_QFRAG;
     ringB = (misc + C::MISC_FIXED + 127u) & ~127u;
     const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
@@ -641,16 +682,19 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
-    int* const todo = reinterpret_cast<int*>(smem_gen + misc + C::OFF_TODO);     // [0] count, [1] exit flag, [4..] units
+    // [0] units queued for the tail phase  [1] this CTA leaves last  [4..] the queued units
+    volatile int* const todo = reinterpret_cast<volatile int*>(smem_gen + misc + C::OFF_TODO);
     PrepScratch scratch;
     scratch.bnd = reinterpret_cast<const float*>(smem_gen + misc + C::OFF_BND);
     scratch.unit = reinterpret_cast<float*>(smem_gen + misc + C::OFF_UNIT);
+    scratch.qvec = reinterpret_cast<float*>(smem_gen + misc + C::OFF_QVEC);
+    scratch.qvec_addr = misc + C::OFF_QVEC;
+    scratch.unit_addr = misc + C::OFF_UNIT;
     scratch.codes = smem_gen + misc + C::OFF_CODES;
     scratch.nrm = reinterpret_cast<float*>(smem_gen + misc + C::OFF_NRM);
     pdl_trigger();
-    if (threadIdx.x == 0) TQB_TRACE(0);
 
-    // ---- constants: centroids, boundaries, barriers, empty query slots, lookup tables ----
+    // ---- constants: centroids, boundaries, barriers, empty query slots ----
     if (threadIdx.x < 16) {
         float* cf = reinterpret_cast<float*>(smem_gen + cent_addr);
         cf[threadIdx.x] = threadIdx.x < (1 << KB) ? p.cent_k[threadIdx.x] : 0.0f;
@@ -669,20 +713,55 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         mbar_init(qfull_addr + threadIdx.x * 8, 1);
         mbar_init(qempty_addr + threadIdx.x * 8, WARPS);
     }
-    if (threadIdx.x == 0) { todo[0] = 0; todo[1] = 0; }
+    if (threadIdx.x < DSLOTS) mbar_init(done_addr + threadIdx.x * 8, WARPS);
+    if (threadIdx.x == 0) { mbar_init(hdone_addr, 1); todo[0] = 0; todo[1] = 0; }
     for (int i = threadIdx.x; i < QSLOTS * C::QFRAG / 4; i += blockDim.x)
         reinterpret_cast<uint32_t*>(smem_gen + qfrag_addr)[i] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    {
+
+    // ---- lookup tables (constants only), and -- by the first PREP_WARPS warps, at the same time, when
+    // PREP_WARPS > 0 -- the sequence lengths and the CTA's first item (the caller's tensors) ----
+    const bool lens_in_smem = p.batch <= C::LENS_MAX;
+    Lens lens;
+    lens.sm = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + misc + C::OFF_LENS) : nullptr;
+    StageCursor<SR, GROUPS> cur;
+    // lengths clamped to what the host announced; CTA 0 reports and clears the outputs of empty sequences
+    auto load_lens = [&](int tid, int nthreads) {
+        if (!lens_in_smem && blockIdx.x != 0) return;
+        for (int i = tid; i < p.batch; i += nthreads) {
+            int flag;
+            const int e = encode_len(p, p.lens_in[i], flag);
+            if (lens_in_smem) reinterpret_cast<int32_t*>(smem_gen + misc + C::OFF_LENS)[i] = e;
+            if (blockIdx.x == 0) {
+                if (flag) atomicOr(p.status, flag);
+                if ((e & LEN_MASK) == 0)            // nothing to attend to: the output rows are zero
+                    for (int k = 0; k < p.q_heads * D; k++) store_out(p.out, p.out_dtype, (int64_t)i * p.q_heads * D + k, 0.0f);
+            }
+        }
+    };
+    auto first_item = [&](int tid, int nthreads) {   // (every thread of the preparing group takes the same path)
+        cur.start(p, lens);
+        if (cur.valid())
+            prepare_item<D, KB, VB, false>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                           reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch, tid, nthreads);
+    };
+    const bool prep_group = PREP_WARPS > 0 && warp < PREP_WARPS;
+    if (prep_group) {
+        pdl_wait();
+        load_lens(threadIdx.x, PREP_WARPS * 32);
+        asm volatile("bar.sync 2, %0;" ::"n"(PREP_WARPS > 0 ? PREP_WARPS * 32 : 32) : "memory");
+        first_item(threadIdx.x, PREP_WARPS * 32);
+    } else {
         const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
         constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
-        for (int x = warp; x < C::LUTK_ENTRIES; x += WARPS + 2) {
+        constexpr int TW = WARPS + 2 - PREP_WARPS;                 // warps that build the tables
+        for (int x = warp - PREP_WARPS; x < C::LUTK_ENTRIES; x += TW) {
             int clo, chi;
             tl_key_field_codes((uint32_t)x, KB, clo, chi);
             *reinterpret_cast<uint32_t*>(smem_gen + tabK_base + x * KSTR + lane * 4) = pack_half2(cf[clo], cf[chi]);
         }
-        for (int x = warp; x < C::LUTV_ENTRIES; x += WARPS + 2) {
+        for (int x = warp - PREP_WARPS; x < C::LUTV_ENTRIES; x += TW) {
             if (C::VQUAD) {
                 int ag, bg, ag8, bg8;
                 tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
@@ -694,42 +773,20 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                 *reinterpret_cast<uint32_t*>(smem_gen + tabV_base + x * VSTR + lane * 4) = pack_half2(cf[16 + ca], cf[16 + cb]);
             }
         }
-    }
-    // everything above depends on constants only; from here on the caller's tensors and the workspace are used
-    if (threadIdx.x == 0) TQB_TRACE(1);
-    pdl_wait();
-
-    // ---- sequence lengths (clamped to what the host announced); CTA 0 reports and clears empty sequences ----
-    const bool lens_in_smem = p.batch <= C::LENS_MAX;
-    Lens lens;
-    lens.sm = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + misc + C::OFF_LENS) : nullptr;
-    if (lens_in_smem || blockIdx.x == 0) {
-        for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
-            int flag;
-            const int e = encode_len(p, p.lens_in[i], flag);
-            if (lens_in_smem) reinterpret_cast<int32_t*>(smem_gen + misc + C::OFF_LENS)[i] = e;
-            if (blockIdx.x == 0) {
-                if (flag) atomicOr(p.status, flag);
-                if ((e & LEN_MASK) == 0)            // nothing to attend to: the output rows are zero
-                    for (int k = 0; k < p.q_heads * D; k++) store_out(p.out, p.out_dtype, (int64_t)i * p.q_heads * D + k, 0.0f);
-            }
-        }
+        // everything above depends on constants only; from here on the caller's tensors and the workspace are used
+        pdl_wait();
     }
     __syncthreads();
-
-    // ---- the CTA's first item is prepared by all warps together ----
-    if (threadIdx.x == 0) TQB_TRACE(2);
-    StageCursor<SR, GROUPS> cur;
-    cur.start(p, lens);
-    if (cur.valid()) {                                // (uniform over the CTA)
-        prepare_item<D, KB, VB, true>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
-                                      reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch,
-                                      threadIdx.x, blockDim.x);
+    if (PREP_WARPS == 0) {                            // all warps together, one phase after the other
+        load_lens(threadIdx.x, blockDim.x);
         __syncthreads();
-        if (threadIdx.x == 0)
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
+        first_item(threadIdx.x, blockDim.x);
+        __syncthreads();
+    } else if (!prep_group) {
+        cur.start(p, lens);
     }
-    if (threadIdx.x == 0) TQB_TRACE(3);
+    if (threadIdx.x == 0 && cur.valid())
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
     const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
     const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
 
@@ -803,61 +860,64 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                 (void)mbar_wait(full_addr + 8 * (i % NS), (i / NS) & 1);   // (padding stages complete at once)
         }
     } else if (warp == WARPS + 1) {
-        // ---- helper warp: prepares the CTA's second, third, ... item while the previous one streams ----
-        for (;;) {
+        // ---- helper warp: prepares the CTA's second, third, ... item while earlier ones stream, and speaks
+        // for the CTA's consumer warps: once all of them have stored their partial of an item (done barrier)
+        // it bumps the unit's arrival counter with one fence for the lot.  The helper that completes a unit
+        // (one arrival per chunk) owns its merge and queues it for its CTA's tail phase.  No warp ever waits
+        // for another CTA.
+        StageCursor<SR, GROUPS> told = cur;            // the next item to announce
+        bool ok = true;
+        auto announce = [&]() {
+            if (lane == 0) ok = mbar_wait(done_addr + 8 * (told.seq % DSLOTS), (told.seq / DSLOTS) & 1);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) return;
+            int merge_here = 0;
+            const int u = told.unit;
+            const int S = lens.get(p, told.b) & LEN_MASK;
+            if (lane == 0) {
+                __threadfence();                                  // the consumers' partials before the count
+                if (atomicAdd(p.unit_cnt + u, 1) + 1 == (S + p.chunk - 1) / p.chunk) {
+                    atomicExch(p.unit_cnt + u, 0);                // clean for the next call
+                    __threadfence();                              // (acquire side: the partials are read after this)
+                    const int slot = todo[0];
+                    if (slot < TODO_MAX) { todo[4 + slot] = u; todo[0] = slot + 1; }
+                    else merge_here = 1;                          // queue full: merge right here
+                }
+            }
+            if (__shfl_sync(0xffffffffu, merge_here, 0)) {
+                const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
+                for (int nh = 0; nh < p.group; nh++) merge_head<D>(p, u, nh, nparts, lane);
+            }
+            told.next_item(p, lens);
+        };
+        while (ok) {
             cur.next_item(p, lens);
             if (!cur.valid()) break;
             const int q = cur.seq % QSLOTS, use = cur.seq / QSLOTS;
-            bool ok = true;
             if (use >= 1) {                         // the slot's previous fragments have been taken by every consumer warp
                 if (lane == 0) ok = mbar_wait(qempty_addr + 8 * q, (use - 1) & 1);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
             }
-            if (!ok) {
-                if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
-                break;
-            }
-#ifdef TQB_DECODE_TRACE
-            const unsigned long long tp0 = trace_now();
-#endif
-            prepare_item<D, KB, VB, false>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
-                                           reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr + q * C::QFRAG), scratch, lane, 32);
+            prepare_item<D, KB, VB, true>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                          reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr + q * C::QFRAG), scratch, lane, 32);
             __syncwarp();
-#ifdef TQB_DECODE_TRACE
-            if (lane == 0) { TQB_TRACE_ADD(8, trace_now() - tp0); TQB_TRACE_ADD(9, 1); }
-#endif
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr + 8 * q) : "memory");
+            // The item two behind the one just prepared was finished by the consumers before they could take
+            // this slot's previous fragments, so its announcement never waits long; and because it comes before
+            // the next item is handed over, the done barriers (DSLOTS in rotation) can never be lapped.
+            if (cur.seq >= 2) announce();
         }
+        while (ok && told.valid()) announce();
+        if (!ok && lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(hdone_addr) : "memory");
     } else {
     // ---- consumers: group (warp / WPG) takes every GROUPS-th stage; its warp i takes records RPW*i .. RPW*i+RPW-1 ----
     WarpState<C::MT> st;
     int unit = 0, chunk_idx = 0, seq = -1;
-    int owed = -1;                                    // unit whose arrival this warp still has to announce
     st.m0 = st.m1 = st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
     const int r0 = RPW * (warp % WPG);
-    // Arrival of this warp's partial of unit u: the warp that brings the unit's count to (its chunks) x
-    // (consumer warps) owns the merge and queues the unit for the tail phase.
-    auto announce = [&](int u) {
-        __threadfence();
-        __syncwarp();
-        int merge_here = 0;
-        if (lane == 0) {
-            const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
-            const int expected = ((S + p.chunk - 1) / p.chunk) * WARPS;
-            if (atomicAdd(p.unit_cnt + u, 1) + 1 == expected) {
-                atomicExch(p.unit_cnt + u, 0);                    // clean for the next call
-                __threadfence();
-                const int slot = atomicAdd(todo, 1);
-                if (slot < TODO_MAX) todo[4 + slot] = u;
-                else merge_here = 1;                              // queue full: merge right here
-            }
-        }
-        if (__shfl_sync(0xffffffffu, merge_here, 0)) {
-            const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
-            const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
-            for (int nh = 0; nh < p.group; nh++) merge_head<D>(p, u, nh, nparts, lane);
-        }
-    };
     for (uint32_t n = warp / WPG;; n += GROUPS) {
         const int s = n % NS;
         bool ok = mbar_wait(full_addr + 8 * s, (n / NS) & 1);
@@ -867,14 +927,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                          : "=r"(meta.x), "=r"(meta.y), "=r"(meta.z), "=r"(meta.w) : "r"(meta_addr + s * 16));
         if (ok && (meta.z & F_FIRST) && !(meta.z & F_END)) {      // this group's first stage of an item
             seq++;
-#ifdef TQB_DECODE_TRACE
-            const unsigned long long tq0 = trace_now();
-            if (threadIdx.x == 0 && seq == 0) TQB_TRACE(4);
-#endif
             ok = mbar_wait(qfull_addr + 8 * (seq % QSLOTS), (seq / QSLOTS) & 1);
-#ifdef TQB_DECODE_TRACE
-            if (threadIdx.x == 0) TQB_TRACE_ADD(10, trace_now() - tq0);
-#endif
         }
         if (!__all_sync(0xffffffffu, ok)) {           // a copy or the helper warp never arrived: flag it and stop
             if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
@@ -920,15 +973,6 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr + 8 * s) : "memory");
 
         if (meta.z & F_LAST) {                        // this group's last stage of the item: the warp's partial
-            // The arrival of the PREVIOUS item is announced first: its partial was stored an item ago, so the
-            // fence that orders those stores before the counter finds nothing left to wait for.
-#ifdef TQB_DECODE_TRACE
-            const unsigned long long ta0 = trace_now();
-#endif
-            if (owed >= 0) announce(owed);
-#ifdef TQB_DECODE_TRACE
-            if (threadIdx.x == 0) TQB_TRACE_ADD(11, trace_now() - ta0);
-#endif
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
                 st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, o);
@@ -953,30 +997,32 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                     p.part_acc[(pbase + h1) * D + dg8] = st.O[mt][3];
                 }
             }
-            owed = unit;
+            // tell the helper warp (no fence, no wait: it publishes the CTA's partials of this item in one go)
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(done_addr + 8 * (seq % DSLOTS)) : "memory");
         }
     }
-    if (threadIdx.x == 0) TQB_TRACE(5);
-    if (owed >= 0) announce(owed);
 
-    // ---- tail phase (consumer warps only: named barrier 1) ----
-    asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
-    if (threadIdx.x == 0) { TQB_TRACE(6); TQB_TRACE_ADD(12, todo[0]); }
+    // ---- tail phase: the consumer warps merge the units this CTA's helper warp completed ----
     {
-        const int queued = min(todo[0], TODO_MAX);
+        bool ok = true;                               // every item of this CTA has been announced, the queue is final
+        if (lane == 0) ok = mbar_wait(hdone_addr, 0);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok && lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
+    }
+    {
+        const int queued = __shfl_sync(0xffffffffu, (int)todo[0], 0);
         for (int task = warp; task < queued * p.group; task += WARPS) {
-            const int u = todo[4 + task / p.group], nh = task % p.group;
+            const int u = __shfl_sync(0xffffffffu, (int)todo[4 + task / p.group], 0), nh = task % p.group;
             const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
-            const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
-            merge_head<D>(p, u, nh, nparts, lane);
+            merge_head<D>(p, u, nh, min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS), lane);
         }
     }
-    if (threadIdx.x == 0) TQB_TRACE(7);
     }   // consumers
 
     // ---- the CTA that leaves last publishes the new lengths of a fused step ----
     if (p.step) {
-        __syncthreads();                              // every read of the lengths in this CTA (all roles) is over
+        __syncthreads();                              // every role of this CTA is done (no read of the lengths after this)
         if (threadIdx.x == 0) {
             __threadfence();
             const int last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;

@@ -6,7 +6,14 @@
 
 namespace tqb {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 20;   // polls of one bounded mbarrier wait
+// One bounded mbarrier wait gives up after this much wall-clock time (a poll may itself block for a
+// hardware-defined while, so the bound is kept in time, not in polls).
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+__device__ __forceinline__ unsigned long long wall_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -29,9 +36,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = wall_ns();
+    for (;;) {
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (wall_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
 }
 // TMA bulk copy global -> this CTA's shared memory, completion counted on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16.  No multicast.

@@ -38,7 +38,6 @@ constexpr int SCAN_WARPS = 8;
 constexpr int QG = 4;                   // queries per tensor-core pass
 constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
 constexpr float QUERY_SCALE = 16.0f;
-constexpr uint32_t SCAN_WAIT_LIMIT = 1u << 20;
 constexpr int ID_NONE = 0x7fffffff;
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -48,18 +47,7 @@ __device__ __forceinline__ void s_mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void s_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool s_mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SCAN_WAIT_LIMIT; i++) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
+__device__ __forceinline__ bool s_mbar_wait(uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity); }
 __device__ __forceinline__ void s_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
