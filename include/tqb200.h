@@ -87,6 +87,12 @@ int tqb_quantize_mse(const void* x, int dtype, int64_t n, int dim, int64_t x_str
 
 /* Replaces reference.dequantize_mse (reference.py:320-367) and turboquant::dequantize_vectors
  * (csrc/core/turboquant_core.cpp:345-401).  out: (n, dim) of out_dtype. */
+/* Large calls (dim 64 / 128, 2-4 bits, at least 512 rows, 16-byte aligned rows) run on the tensor cores
+ * (csrc/quantize_tc.cu: tcgen05.mma with bf16 operand splits, exact re-quantisation of rows near a decision
+ * boundary), with the same codes and norms as the FFMA kernel.  Its waits are bounded; tqb_quantize_status
+ * reads and clears the error word one of them would raise (0 = all good; non-zero = the outputs of the
+ * quantise calls since the last query are not to be trusted).  Synchronises `stream`.  No upstream counterpart. */
+int tqb_quantize_status(void* stream);
 int tqb_dequantize_mse(const uint8_t* packed, const float* norms, int64_t n, int dim,
                        const float* rotation, const float* centroids, int bits, void* out,
                        int out_dtype, void* stream);

@@ -303,8 +303,8 @@ struct PrepScratch {
 // inside fp16's range); the columns of heads >= group stay zero.
 //
 // With `append` it first quantises the unit's new key and value and stores them at position `pos`.  The
-// code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums and a
-// butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
+// code selection repeats quantize.cu's arithmetic exactly (norm by per-lane partial sums over consecutive
+// elements and a butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
 // code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
 // The stores are followed by a proxy fence: the producer copies that record with the TMA engine.
 template <int D, int KB, int VB, bool ONE_WARP>
@@ -328,13 +328,13 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
             float v[NQ], ss = 0.0f;
 #pragma unroll
             for (int qq = 0; qq < NQ; qq++) {
-                v[qq] = load_in(x, p.in_dtype, x0 + lane + 32 * qq);
+                v[qq] = load_in(x, p.in_dtype, x0 + lane * NQ + qq);         // (the norm's summation order of quantize.cu)
                 ss = fmaf(v[qq], v[qq], ss);
             }
             const float n = sqrtf(warp_sum(ss));
             const float den = fmaxf(n, 1e-10f);
 #pragma unroll
-            for (int qq = 0; qq < NQ; qq++) sc.unit[which * D + lane + 32 * qq] = v[qq] / den;
+            for (int qq = 0; qq < NQ; qq++) sc.unit[which * D + lane * NQ + qq] = v[qq] / den;
             if (lane == 0) sc.nrm[which] = n;
         }
     }

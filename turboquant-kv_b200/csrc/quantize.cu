@@ -4,7 +4,11 @@
 //
 // Arithmetic follows upstream turboquant_kv/reference.py:293-317 (MSE) and :429-469 (Prod) in
 // float32.  Work decomposition: a warp owns RW = 8 consecutive rows; lane l owns the rotated
-// coordinates j = l + 32 q.  The transposed rotation T[k][j] = R[j][k] sits in shared memory, so a
+// coordinates j = l + 32 q.  The NORM of a row is summed in one fixed order that every quantising kernel
+// of this library shares (this one, the tensor-core kernel, the decode step's append), so that they all
+// store the same norm and select the same codes: when dim is a multiple of 32, lane l squares and adds
+// the dim/32 CONSECUTIVE elements starting at l * dim/32 (fused multiply-add chain), else the elements
+// l + 32 q; then a butterfly over the lanes.  The transposed rotation T[k][j] = R[j][k] sits in shared memory, so a
 // k step costs NQ conflict-free LDS.32 (T row) + 2 broadcast LDS.128 (the 8 rows' k-th unit
 // coordinate) for 8*NQ FMAs per lane.  Codes are packed with one __ballot_sync per (plane, q):
 // the ballot of 32 lanes is exactly one 32-bit word of a bit-plane after a bit reversal.
@@ -18,6 +22,11 @@
 namespace tqb {
 
 constexpr int MAX_BND = 16;     // boundaries / centroids staged in shared memory
+
+// quantize_tc.cu: the tensor-core kernel for large MSE calls (dim 64 / 128, 2-4 bits).  TQB_ERR_UNSUPPORTED
+// means "not a shape for that path" and sends the call to the kernel below.
+int quantize_tc_try(const void* x, int dtype, int64_t n, int dim, int64_t x_stride, const float* rot, const float* bnd,
+                    int bits, uint8_t* packed, float* norms, const RowMap& map, int tiled, int kb, int vb, cudaStream_t st);
 
 struct QuantArgs {
     const void* x;              // (n, dim) rows, x_stride elements apart
@@ -87,10 +96,12 @@ __global__ void __launch_bounds__(256) quantize_kernel(QuantArgs a0, QuantArgs a
         for (int i = 0; i < RW; i++) {
             const int64_t r = row0 + i;
             float v[NQ], ss = 0.0f;
+            const bool blocked = (dim & 31) == 0;             // lane owns dim/32 consecutive elements
+            const int per_lane = dim >> 5;
 #pragma unroll
             for (int q = 0; q < NQ; q++) {
-                const int j = lane + 32 * q;
-                v[q] = (r < a.n && j < dim) ? to_f32<T>(x[r * a.x_stride + j]) : 0.0f;
+                const int j = blocked ? lane * per_lane + q : lane + 32 * q;
+                v[q] = (r < a.n && j < dim && (!blocked || q < per_lane)) ? to_f32<T>(x[r * a.x_stride + j]) : 0.0f;
                 ss = fmaf(v[q], v[q], ss);
             }
             nrm[i] = sqrtf(warp_sum(ss));
@@ -106,7 +117,10 @@ __global__ void __launch_bounds__(256) quantize_kernel(QuantArgs a0, QuantArgs a
                 for (int q = 0; q < NQ; q++) v[q] = v[q] / den2;
             }
 #pragma unroll
-            for (int q = 0; q < NQ; q++) ub[(lane + 32 * q) * RW + i] = v[q];
+            for (int q = 0; q < NQ; q++) {
+                const int j = blocked ? lane * per_lane + q : lane + 32 * q;
+                if (j < DP && (!blocked || q < per_lane)) ub[j * RW + i] = v[q];
+            }
         }
         __syncwarp();
 
@@ -268,6 +282,9 @@ extern "C" int tqb_quantize_mse(const void* x, int dtype, int64_t n, int dim, in
     tqb::QuantArgs a{};
     a.x = x; a.n = n; a.x_stride = x_stride; a.rot = rotation; a.bnd = boundaries; a.mse_bits = bits;
     a.packed = packed; a.norms = norms; a.map = tqb::make_rowmap(map);
+    const int rc = tqb::quantize_tc_try(x, dtype, n, dim, x_stride, rotation, boundaries, bits, packed, norms, a.map, 0, 0, 0,
+                                        (cudaStream_t)stream);
+    if (rc != TQB_ERR_UNSUPPORTED) return rc;
     return tqb::dispatch_dtype<false>(dtype, a, a, 1, dim, (cudaStream_t)stream);
 }
 
@@ -290,6 +307,13 @@ extern "C" int tqb_kv_append(const void* key, const void* value, int dtype, int6
     a.packed = store; a.norms = nullptr; a.map = tqb::make_rowmap(map); a.tiled = 1; a.kb = kbits; a.vb = vbits;
     b = a;
     b.x = value; b.rot = rot_v; b.bnd = bnd_v; b.mse_bits = vbits; b.tiled = 2;
+    // large calls: keys, then values, through the tensor-core kernel
+    int rc = tqb::quantize_tc_try(key, dtype, n, dim, x_stride, rot_k, bnd_k, kbits, store, nullptr, a.map, 1, kbits, vbits,
+                                  (cudaStream_t)stream);
+    if (rc == TQB_OK && vbits)
+        rc = tqb::quantize_tc_try(value, dtype, n, dim, x_stride, rot_v, bnd_v, vbits, store, nullptr, a.map, 2, kbits, vbits,
+                                  (cudaStream_t)stream);
+    if (rc != TQB_ERR_UNSUPPORTED) return rc;
     return tqb::dispatch_dtype<false>(dtype, a, b, vbits ? 2 : 1, dim, (cudaStream_t)stream);
 }
 

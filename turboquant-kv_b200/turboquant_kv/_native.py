@@ -51,6 +51,7 @@ def lib():
         L.tqb_unpack_codes.argtypes = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]
         L.tqb_quantize_mse.argtypes = [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_void_p, c_int,
                                        c_void_p, c_void_p, ctypes.POINTER(RowMap), c_void_p]
+        L.tqb_quantize_status.argtypes = [c_void_p]
         L.tqb_dequantize_mse.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int,
                                          c_void_p, c_int, c_void_p]
         L.tqb_quantize_prod.argtypes = [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p,
