@@ -39,10 +39,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = wall_ns();
     for (;;) {
+#pragma unroll 1
         for (int i = 0; i < 32; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (wall_ns() - t0 > WAIT_LIMIT_NS) return false;
     }
+}
+// try_wait that lets the hardware keep the thread suspended for up to `ns` nanoseconds (a hint; the thread
+// resumes as soon as the phase completes).
+__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait for kernels with many wait sites and many waiting warps: the polling loop is a function of its
+// own (one copy per kernel image instead of one per wait site, so the hot loops stay small in the instruction
+// cache) and each poll may sleep in the barrier unit, so that waiting warps leave the issue slots to the others.
+static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = wall_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; i++)
+            if (mbar_try_wait_for(bar, parity, 20000u)) return true;
+        if (wall_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+}
+__device__ __forceinline__ bool mbar_wait_compact(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_poll(bar, parity);
 }
 // TMA bulk copy global -> this CTA's shared memory, completion counted on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16.  No multicast.
