@@ -505,26 +505,11 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         torch.cuda.empty_cache()
     res["decode_context_sweep"] = sweep
 
-    # ---- paged decode, Llama-3-8B geometry, ONE layer on random codes (kernel-level figure) ----
-    def timed_events(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(10):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / 10
-
-    ms, nbytes, status, finite = paged_layer(torch, device, kvh, qh, 32768, timed_events)
-    ms = sync_max(ms)
-    res["paged_decode_layer"] = {
-        "geometry": "head_dim 128, K4/V3, 16-token pages, batch 64, context 32768, %d KV heads x 4 query heads per GPU" % kvh,
-        "ms_per_layer_call": ms, "hbm_gbs_per_gpu": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-        "tokens_per_s_if_32_layers": 64 / (32 * ms * 1e-3), "status": status, "finite": finite,
-        "note": "one layer on random codes, eager launches; the 32-layer figure is an extrapolation, not a measurement"}
+    # ---- paged decode, Llama-3-8B geometry: all 32 layers resident, prefill quantisation timed apart ----
+    try:
+        res["paged_decode_llama3_8b"] = paged_model(torch, dist, args, rank, world, device, peaks, sync_max)
+    except Exception as exc:
+        res["paged_decode_llama3_8b"] = {"error": repr(exc)}
     torch.cuda.empty_cache()
 
     # ---- quantise: MSE 4-bit round trip (65,536 unit vectors, d = 128) and Prod 3-bit estimator ----
@@ -556,6 +541,9 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         ms_q = timed_ms(lambda: quantize_mse(x, 4, rotation=rot, codebook=cb4))
         pk, nm = quantize_mse(x, 4, rotation=rot, codebook=cb4)
         ms_d = timed_ms(lambda: dequantize_mse(pk, nm, 4, 128, rotation=rot, codebook=cb4))
+        xl = torch.randn(1 << 22, 128, generator=g0, device=device)             # 2 GB of rows: beyond the L2
+        ms_q4m = timed_ms(lambda: quantize_mse(xl, 4, rotation=rot, codebook=cb4), reps=5)
+        del xl
         mse = float(((dequantize_mse(pk, nm, 4, 128, rotation=rot, codebook=cb4) - x) ** 2).sum(-1).mean())
         # Prod: rows with per-coordinate variances log-uniform in [0.1, 10], L2-normalised (shared variance vector)
         g1 = torch.Generator(device=device).manual_seed(1)
@@ -571,12 +559,16 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         slope = float((est * exact).sum() / (exact * exact).sum())
         res["quantize"] = {
             "mse_4bit_d128_vectors_per_s": 65536 / (ms_q * 1e-3), "mse_4bit_quantize_ms": ms_q,
-            "mse_4bit_dequantize_ms": ms_d, "mse_4bit_tflops_fp32": 2 * 128 * 128 * 65536 / (ms_q * 1e-3) / 1e12,
+            "mse_4bit_dequantize_ms": ms_d, "mse_4bit_rotation_tflops": 2 * 128 * 128 * 65536 / (ms_q * 1e-3) / 1e12,
+            "mse_4bit_hbm_frac": 65536 * (512 + 68) / (ms_q * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "mse_4bit_4m_rows_ms": ms_q4m, "mse_4bit_4m_rows_vectors_per_s": (1 << 22) / (ms_q4m * 1e-3),
+            "mse_4bit_4m_rows_hbm_frac": (1 << 22) * (512 + 68) / (ms_q4m * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "mse_4bit_per_vector_squared_error": mse,
             "prod_3bit_d128_vectors_per_s": 1_000_000 / (ms_p * 1e-3),
             "prod_3bit_estimator_bias": float((est - exact).mean()), "prod_3bit_estimator_slope": slope,
-            "note": "rank 0 only; the rotation is an fp32 FMA contraction (codes must match float32 upstream "
-                    "arithmetic bit for bit), so the tensor pipe is idle in these kernels"}
+            "note": "rank 0 only; MSE calls of 512 rows and more run the rotation on tcgen05 (bf16 operand splits, "
+                    "float32 accumulation in tensor memory, rows fed by TMA bulk copies), with the codes of the float32 "
+                    "FMA kernel; Prod mode and short calls run the float32 FMA kernel"}
         del db, x, est, exact
         torch.cuda.empty_cache()
 
@@ -633,6 +625,9 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     torch.cuda.synchronize()
     ms_host = sync_max((time.perf_counter() - t0) * 1e3)
     passes = math.ceil(nq / 4)
+    scan_parity = None
+    if world == 1 and not args.no_cpu and args.scan_parity_queries > 0:
+        scan_parity = scan_reference_check(torch, index.local, queries[:args.scan_parity_queries], sc, ids, k)
     res["index_scan"] = {
         "rows": n_total, "rows_per_gpu": rows_local, "dim": dim, "bits": 4, "k": k, "queries": nq,
         "single_query_pass_ms": ms1, "single_query_hbm_gbs_per_gpu": rows_local * row_bytes / (ms1 * 1e-3) / 1e9,
@@ -643,7 +638,170 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         "batched_hbm_gbs_per_gpu": passes * rows_local * row_bytes / (msq * 1e-3) / 1e9,
         "add_vectors_per_s_per_gpu": rows_local / (t_add * 1e-3), "gpu_launches": launches,
         "ids_checksum": int(ids.sum().item()) if rank == 0 else None,
+        "parity_vs_upstream_core": scan_parity if scan_parity is not None else
+        "run at 1 GPU only: the merged ids are the same at every shard count (ids_checksum)",
     }
+    return res
+
+
+def scan_reference_check(torch, index, queries, scores, ids, k: int) -> dict:
+    """The first queries of the batch again on the host, over ALL rows, with the upstream project's own C++
+    core (turboquant::search_packed, compiled in place into oracle/_ref) on the index's exported rows: id
+    identity except for tied scores, and the CPU's queries/s on this machine's cores."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    if orc.ref_lib() is None:
+        return {"unavailable": "oracle/_ref/libtq_ref.so is not built on this machine"}
+    nq = queries.shape[0]
+    packed = index._packed_codes.cpu().numpy()
+    norms = index._norms.cpu().numpy()
+    rot = orc.make_rotation_matrix(index.dim, 42)
+    _, cent = orc.lloyd_max_codebook(index.bit_width, index.dim)
+    cores = os.cpu_count() or 1
+    orc.set_num_threads(cores)
+    t0 = time.perf_counter()
+    r_sc, r_ids = orc.ref_search_packed(queries.cpu().numpy(), packed, norms, rot, cent, index.bit_width, k)
+    dt = time.perf_counter() - t0
+    g_sc, g_ids = scores[:nq].cpu().numpy(), ids[:nq].cpu().numpy()
+    same = g_ids == r_ids
+    # a differing id is explained by a tie when the two rows carry the same score at that rank
+    tie = (~same) & (g_sc == r_sc)
+    rel = np.abs(g_sc - r_sc) / np.maximum(np.abs(r_sc), 1e-30)
+    return {"queries": nq, "rows": int(packed.shape[0]), "ids_identical": bool(same.all()),
+            "id_mismatches": int((~same).sum()), "tie_explained": int(tie.sum()),
+            "unexplained": int(((~same) & ~tie).sum()), "scores_bit_equal": bool((g_sc == r_sc).all()),
+            "score_max_rel_diff": float(rel.max()), "cpu_reference_qps": nq / dt, "cpu_reference_seconds": dt,
+            "cores": cores, "against": "upstream turboquant::search_packed (csrc/core/turboquant_core.cpp) on the exported rows"}
+
+
+def paged_model(torch, dist, args, rank: int, world: int, device, peaks, sync_max) -> dict:
+    """The paged Llama-3-8B configuration as a whole: 32 layers, 32 query / 8 KV heads (sharded over the ranks),
+    head_dim 128, K4/V3, 16-token pages scattered over the pool, batch 64, context 32768.
+
+    prefill   all 64 x 32768 tokens of ONE layer are quantised into the pages through append_slots from bf16
+              K/V resident in HBM (timed per call with CUDA events); the other layers receive copies of these
+              pages, so every layer holds real records
+    decode    one step = for each of the 32 layers: append_slots of the new token of every sequence, then
+              paged_decode_attention over the whole context (2 launches per layer, eager)
+    parity    the first layer's output for two sequences against dequantise-then-attend on the CPU
+    """
+    import numpy as np
+
+    from turboquant_kv.vllm_plugin import TurboQuantKVCacheConfig, TurboQuantPagedKVCache
+
+    layers, batch, ctx, dim, bs, kv_heads, q_heads = 32, 64, args.paged_ctx, 128, 16, 8, 32
+    kvh, qh = kv_heads // world, q_heads // world
+    K, W = max(3, min(args.steps, 10)), 3
+    per_seq = ctx // bs + (K + W + bs) // bs + 1           # pages of a sequence, with room for the appended tokens
+    pages = batch * per_seq
+    cfg = TurboQuantKVCacheConfig(key_bits=4, value_bits=3, block_size=bs, num_gpu_blocks=pages, seed=42)
+    pool = TurboQuantPagedKVCache(cfg, num_layers=layers, num_heads=kvh, head_dim=dim, dtype=torch.bfloat16, device=str(device))
+    gen = torch.Generator(device=device).manual_seed(11)
+    tables = torch.randperm(pages, device=device, generator=gen).to(torch.int32).view(batch, per_seq)
+
+    # ---- prefill quantisation of one layer, in calls of 4 sequences (131,072 tokens) ----
+    scale = torch.ones(kvh, dim, device=device)
+    for h in range(kvh):
+        scale[h, torch.randperm(dim, generator=gen, device=device)[:4]] = 20.0
+    group, t_q, keep = 4, 0.0, None
+    tok = torch.arange(ctx, device=device)
+    for b0 in range(0, batch, group):
+        k = (torch.randn(group * ctx, kvh, dim, generator=gen, device=device) * scale).bfloat16()
+        v = torch.randn(group * ctx, kvh, dim, generator=gen, device=device).bfloat16()
+        slots = torch.cat([tables[b].long()[tok // bs] * bs + tok % bs for b in range(b0, b0 + group)])
+        if b0 == 0:
+            keep = (k[:2 * ctx].float().cpu().numpy(), v[:2 * ctx].float().cpu().numpy())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        pool.append_slots(0, k, v, slots)
+        e1.record()
+        torch.cuda.synchronize()
+        t_q += e0.elapsed_time(e1)
+        del k, v, slots
+    t_q = sync_max(t_q)
+    vectors = 2 * batch * ctx * kvh
+    q_bytes = batch * ctx * kvh * (2 * dim * 2 + (64 + 4) + (48 + 4))
+    for layer in range(1, layers):
+        pool._pools[layer].copy_(pool._pools[0])
+
+    # ---- decode steps ----
+    q = torch.randn(layers, batch, qh, dim, generator=gen, device=device).bfloat16()
+    kn = (torch.randn(layers, batch, kvh, dim, generator=gen, device=device) * scale).bfloat16()
+    vn = torch.randn(layers, batch, kvh, dim, generator=gen, device=device).bfloat16()
+    out = torch.empty_like(q)
+    lens = [torch.full((batch,), ctx + i + 1, dtype=torch.int32, device=device) for i in range(K + W + 1)]
+    slot = [tables[:, (ctx + i) // bs].long() * bs + (ctx + i) % bs for i in range(K + W + 1)]
+
+    def step(i):
+        for layer in range(layers):
+            pool.append_slots(layer, kn[layer], vn[layer], slot[i])
+            pool.paged_decode_attention(layer, q[layer], tables, lens[i], max_seq_len=ctx + K + W + 1, out=out[layer])
+
+    from turboquant_kv import _native
+
+    step(0)
+    torch.cuda.synchronize()
+    first = out[0, :2].float().cpu().numpy()
+    for i in range(1, W):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches0 = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(W, W + K):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = sync_max(e0.elapsed_time(e1) / K)
+    launches = (_native.launch_count() - launches0) // K
+    status = pool.kv.status()
+    d_bytes = layers * batch * kvh * (ctx + W + K // 2) * (64 + 48 + 8)
+    res = {
+        "geometry": "32 layers, head_dim 128, K4/V3, 16-token pages (scattered), batch 64, context %d, "
+                    "%d KV heads x 4 query heads per GPU" % (ctx, kvh),
+        "decode_ms_per_step": ms, "decode_tokens_per_s": batch / (ms * 1e-3), "launches_per_step": launches,
+        "decode_hbm_gbs_per_gpu": d_bytes / (ms * 1e-3) / 1e9, "decode_hbm_frac": d_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "packed_kv_bytes_per_gpu": layers * batch * kvh * ctx * 120, "status": status,
+        "prefill_quantize_ms_per_layer": t_q, "prefill_quantize_ms_32_layers": 32 * t_q,
+        "prefill_quantize_vectors_per_layer": vectors, "prefill_quantize_vectors_per_s": vectors / (t_q * 1e-3),
+        "prefill_quantize_hbm_gbs_per_gpu": q_bytes / (t_q * 1e-3) / 1e9,
+        "prefill_quantize_hbm_frac": q_bytes / (t_q * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "note": "every layer resident (one layer quantised from bf16 K/V, timed; the others are copies of its pages); "
+                "decode launched eagerly, timed over %d steps with CUDA events, max over ranks" % K}
+    # ---- parity of the first layer's first step for two sequences (their KV heads on this rank) ----
+    if not args.no_cpu:
+        from oracle import build as obuild
+
+        obuild.build_oracle()
+        from oracle import oracle as orc
+
+        orc.set_num_threads(max(1, (os.cpu_count() or 1) // world))
+        rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+        bk, ck = orc.lloyd_max_codebook(4, dim)
+        bv, cv = orc.lloyd_max_codebook(3, dim)
+        n = ctx + 1
+        kk = np.concatenate([keep[0].reshape(2, ctx, kvh, dim), kn[0, :2].float().cpu().numpy()[:, None]], axis=1)
+        vv = np.concatenate([keep[1].reshape(2, ctx, kvh, dim), vn[0, :2].float().cpu().numpy()[:, None]], axis=1)
+        kp, knm = orc.quantize_mse(np.ascontiguousarray(kk.transpose(0, 2, 1, 3)).reshape(-1, dim), 4, rk, bk)
+        vp, vnm = orc.quantize_mse(np.ascontiguousarray(vv.transpose(0, 2, 1, 3)).reshape(-1, dim), 3, rv, bv)
+        ref = orc.decode_attention(q[0, :2].float().cpu().numpy(), kp.reshape(2, kvh, n, -1), knm.reshape(2, kvh, n),
+                                   vp.reshape(2, kvh, n, -1), vnm.reshape(2, kvh, n), np.full(2, n, np.int32),
+                                   rk, ck, 4, rv, cv, 3)
+        cos = float((first * ref).sum() / np.sqrt((first * first).sum() * (ref * ref).sum()))
+        worst = [float(np.abs(first - ref).max()), -cos]
+        if world > 1:
+            t = torch.tensor(worst, device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            worst = [float(t[0].item()), float(t[1].item())]
+        res["parity"] = {"max_abs": worst[0], "cosine": -worst[1], "tolerance": "1e-2 max-abs, cosine >= 0.9999",
+                         "against": "CPU port, dequantise-then-attend over 2 sequences x %d KV heads x %d tokens of "
+                                    "layer 0 (worst rank)" % (kvh, n)}
+    del pool
     return res
 
 
@@ -765,6 +923,9 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary figures")
     ap.add_argument("--scan-rows", type=int, default=10_000_000)
     ap.add_argument("--scan-queries", type=int, default=10_000)
+    ap.add_argument("--scan-parity-queries", type=int, default=32,
+                    help="queries searched again with the upstream C++ core over all rows (1 GPU only; 0 = skip)")
+    ap.add_argument("--paged-ctx", type=int, default=32768, help="context of the paged 32-layer configuration")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

@@ -97,6 +97,45 @@ def test_tensor_core_append_writes_the_same_records(dim, kb, vb):
     assert torch.equal(big, small)
 
 
+@pytest.mark.parametrize("heads", [8, 4, 2, 1, 3])
+@pytest.mark.parametrize("dim,kb,vb", [(128, 4, 3), (64, 3, 2), (128, 2, 4)])
+def test_tensor_core_paged_append_writes_the_same_records(dim, kb, vb, heads):
+    """append_slots of thousands of tokens (rows = token x head, pages scattered over the pool): whole pages
+    are written as whole records by the tensor-core kernel, ragged starts, skipped tokens (slot -1) and head
+    counts that do not tile a 128-row tile go row by row; either way the pool equals the one filled by appends
+    of a few dozen tokens at a time (FFMA kernel)."""
+    from turboquant_kv.vllm_plugin import TurboQuantKVCacheConfig, TurboQuantPagedKVCache
+
+    bs, lens, starts = 16, [1500, 333, 2048, 40], [0, 5, 16, 0]      # tokens per sequence, position of the first one
+    nblocks = sum((st + l + bs - 1) // bs for l, st in zip(lens, starts)) + 3
+    gen = torch.Generator().manual_seed(heads * 100 + dim + kb)
+    perm = torch.randperm(nblocks, generator=gen)
+    pools = []
+    for _ in range(2):
+        cfg = TurboQuantKVCacheConfig(key_bits=kb, value_bits=vb, block_size=bs, num_gpu_blocks=nblocks, seed=42)
+        pools.append(TurboQuantPagedKVCache(cfg, num_layers=1, num_heads=heads, head_dim=dim, device="cuda"))
+    slots, nxt = [], 0
+    for l, st in zip(lens, starts):
+        nb = (st + l + bs - 1) // bs
+        blocks = perm[nxt:nxt + nb].to(torch.int64)
+        nxt += nb
+        t = torch.arange(st, st + l)
+        slots.append(blocks[t // bs] * bs + t % bs)
+    slots = torch.cat(slots)
+    slots[777] = -1                                                   # padding tokens are skipped
+    slots[1000:1003] = -1
+    T = slots.numel()
+    k = _rows(T * heads, dim, torch.bfloat16, seed=5).view(T, heads, dim)
+    v = _rows(T * heads, dim, torch.bfloat16, seed=6, outliers=False).view(T, heads, dim)
+    pools[0].append_slots(0, k, v, slots)                             # T x heads rows at once
+    assert _status() == 0
+    step = max(1, 200 // heads)
+    for lo in range(0, T, step):                                      # at most 200 rows per call
+        pools[1].append_slots(0, k[lo:lo + step].contiguous(), v[lo:lo + step].contiguous(), slots[lo:lo + step])
+    torch.cuda.synchronize()
+    assert torch.equal(pools[0]._pools[0], pools[1]._pools[0])
+
+
 def test_tensor_core_quantise_strided_rows(orc):
     """Rows that are not contiguous (x_stride > dim) go through one TMA copy per row."""
     from turboquant_kv import _native as N

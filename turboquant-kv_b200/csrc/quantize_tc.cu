@@ -57,6 +57,7 @@ struct TcArgs {
     uint8_t* packed; float* norms;           // upstream rows (tiled == 0)
     RowMap map;
     int tiled, kb, vb;                       // 1 / 2: key / value section of the tiled KV store
+    int heads;                               // tiled: units interleaved in the row order (row = token * heads + unit)
     int* error;                              // device word: set non-zero when a bounded wait expired
 };
 
@@ -182,6 +183,84 @@ static __device__ __noinline__ uint32_t exact_code(const T* xr, const float* rro
     return c;
 }
 
+// ---- whole records of the tiled store, assembled from a tile's code bytes -----------------------------
+// A 128-row tile whose rows are 16 consecutive, aligned token slots of each of 8 units (one unit after the
+// other, or `H` units interleaved row by row) holds exactly 8 records of the tiled layout.  Record w of the
+// tile is then built by one warp: lane (g, t) gathers the codes of its chunk from the tile's code bytes in
+// shared memory (cb: [128 rows][stride], one byte per code) and writes the chunk with wide stores, 512 or
+// more contiguous bytes per warp instruction, instead of one bit field at a time.
+__device__ __forceinline__ int tile_row(int w, int tok, int H) { return ((w / H) * 16 + tok) * H + (w % H); }
+
+template <int NW>
+__device__ __forceinline__ void put_bits(uint32_t (&W)[NW], int bit, int nbits, uint32_t v) {
+    W[bit >> 5] |= v << (bit & 31);
+    if ((bit & 31) + nbits > 32) W[(bit >> 5) + 1 < NW ? (bit >> 5) + 1 : NW - 1] |= v >> (32 - (bit & 31));
+}
+template <int NW>
+__device__ __forceinline__ void store_chunk(uint8_t* dst, const uint32_t (&W)[NW]) {
+    if (NW % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 4; i++) reinterpret_cast<uint4*>(dst)[i] = make_uint4(W[4 * i], W[4 * i + 1], W[4 * i + 2], W[4 * i + 3]);
+    } else if (NW % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 2; i++) reinterpret_cast<uint2*>(dst)[i] = make_uint2(W[2 * i], W[2 * i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW; i++) reinterpret_cast<uint32_t*>(dst)[i] = W[i];
+    }
+}
+// Key section (tl_key_slot): the lane's chunk = token g's fields, then token g+8's; field e = codes of the
+// dims 8e + 2t and 8e + 2t + 1.
+template <int D, int KB>
+__device__ __forceinline__ void assemble_key_chunk(const uint8_t* cb, int stride, int w, int H, int lane, uint8_t* rec) {
+    constexpr int KL = D * KB / 16, NW = KL / 4;
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t W[NW];
+#pragma unroll
+    for (int i = 0; i < NW; i++) W[i] = 0;
+#pragma unroll
+    for (int second = 0; second < 2; second++) {
+        const uint8_t* row = cb + tile_row(w, g + 8 * second, H) * stride + 2 * t;
+#pragma unroll
+        for (int e = 0; e < D / 8; e++) {
+            const uint32_t x = *reinterpret_cast<const uint16_t*>(row + 8 * e);
+            put_bits<NW>(W, second * KL * 4 + e * 2 * KB, 2 * KB, (x & 0xffu) | ((x >> 8) << KB));
+        }
+    }
+    if (KL == 32) {              // two planes of 16-byte pieces (tl_key_piece_offset)
+        reinterpret_cast<uint4*>(rec)[lane] = make_uint4(W[0], W[1], W[2 % NW], W[3 % NW]);
+        reinterpret_cast<uint4*>(rec + 512)[lane] = make_uint4(W[4 % NW], W[5 % NW], W[6 % NW], W[7 % NW]);
+    } else {
+        store_chunk<NW>(rec + lane * KL, W);
+    }
+}
+// Value section (tl_val_slot): the lane's chunk holds tokens {2t, 2t+1, 2t+8, 2t+9} x dims {16 mt + g, + 8}.
+template <int D, int VB>
+__device__ __forceinline__ void assemble_val_chunk(const uint8_t* cb, int stride, int w, int H, int lane, uint8_t* vsec) {
+    constexpr int VL = D * VB / 16, NW = VL / 4;
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t W[NW];
+#pragma unroll
+    for (int i = 0; i < NW; i++) W[i] = 0;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const uint8_t* ra = cb + tile_row(w, 2 * t + 8 * half, H) * stride + g;
+        const uint8_t* rb = cb + tile_row(w, 2 * t + 8 * half + 1, H) * stride + g;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            if (VB == 2) {
+                const uint32_t v = ra[16 * mt] | (rb[16 * mt] << 2) | (ra[16 * mt + 8] << 4) | (rb[16 * mt + 8] << 6);
+                put_bits<NW>(W, (2 * mt + half) * 8, 8, v);
+            } else {
+#pragma unroll
+                for (int sft = 0; sft < 2; sft++)
+                    put_bits<NW>(W, (2 * (2 * mt + half) + sft) * 2 * VB, 2 * VB, ra[16 * mt + 8 * sft] | ((uint32_t)rb[16 * mt + 8 * sft] << VB));
+            }
+        }
+    }
+    store_chunk<NW>(vsec + lane * VL, W);
+}
+
 // ---- configuration ------------------------------------------------------------------------------------
 template <typename T> struct TcTerms;                         // bf16 terms that add up to a value of type T
 template <> struct TcTerms<__nv_bfloat16> { static constexpr int NA = 1; };
@@ -204,7 +283,8 @@ struct TcLayout {
     static constexpr int OFF_BAR = OFF_CELLS + TC_CELLS * 8;                    // mbarriers
     static constexpr int NBAR = 2 * NSTAGE + 2 * ABUF + 4 + 1;                  // stage full/empty, a_ready/a_free, acc full/free x2, spare
     static constexpr int OFF_LIST = (OFF_BAR + NBAR * 8 + 8 + 15) / 16 * 16;    // [NEPI][32] guarded coordinates of a warp
-    static constexpr int OFF_CODES = OFF_LIST + 8 * 32 * 4;                     // tiled output: [128 rows][D] code bytes
+    static constexpr int OFF_SLOTS = OFF_LIST + 8 * 32 * 4;                     // tiled output: the rows' slots (int64)
+    static constexpr int OFF_CODES = OFF_SLOTS + TC_TILE * 8;                   // tiled output: [128 rows][D + 8]: code bytes, norm
     static constexpr int CODE_STRIDE = D + 8;                                   // padded: the 8-byte stores of 16 rows hit 16 bank pairs
     static constexpr int CODES = TC_TILE * CODE_STRIDE;
     static constexpr int TOTAL_ROWS = OFF_CODES + 1024;                         // + slack for the 1024-byte alignment
@@ -595,21 +675,41 @@ __global__ void __launch_bounds__(TcCfg<T, D>::THREADS, 1) quantize_tc_kernel(co
                 }
             }
             if (a.tiled) {
-                // code bytes of the quarter's 32 rows (both halves) -> the record layout, one row at a time with
-                // lane = dimension; the two warps of the quarter meet on a named barrier and share the rows
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + ew) : "memory");
-                for (int i = half * 16; i < half * 16 + 16; i++) {
-                    const int64_t ri = tile * TC_TILE + ew * 32 + i;
-                    const float nrm_i = __shfl_sync(0xffffffffu, nrm, i);   // (the norm buffer may already belong to a later tile)
-                    if (ri >= a.n) continue;
-                    const int64_t orow = a.map(ri);
-                    if (orow < 0) continue;
-                    uint32_t code[NQ];
-#pragma unroll
-                    for (int q = 0; q < NQ; q++) code[q] = sm[C::OFF_CODES + (ew * 32 + i) * C::CODE_STRIDE + lane + 32 * q];
-                    tiled_store_row<NQ>(a.packed, a.tiled, a.kb, a.vb, orow, code, nrm_i, lane, D);
+                // The tile's code bytes are in shared memory.  Warp w of the epilogue takes the w-th group of
+                // sixteen rows that may form a record: written whole when their slots are sixteen consecutive,
+                // aligned ones, else row by row.
+                uint8_t* const cb0 = sm + C::OFF_CODES;
+                int64_t* const slot_s = reinterpret_cast<int64_t*>(sm + C::OFF_SLOTS);
+                if (half == 0) {
+                    *reinterpret_cast<float*>(cb0 + row * C::CODE_STRIDE + D) = nrm;     // (the row's padding)
+                    slot_s[row] = r < a.n ? a.map(r) : -1;
                 }
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + ew) : "memory");   // the code bytes may be overwritten
+                asm volatile("bar.sync 1, %0;" ::"n"(C::NEPI * 32) : "memory");
+                const int H = a.heads > 0 ? a.heads : 1, w = warp - C::EPI_WARP0;
+                const int myrow = tile_row(w, lane & 15, H);
+                const int64_t s_mine = slot_s[myrow], s_first = __shfl_sync(0xffffffffu, s_mine, 0);
+                const bool whole = __all_sync(0xffffffffu, s_first >= 0 && (s_first & 15) == 0 && s_mine == s_first + (lane & 15));
+                const int ksec = tl_key_section(D, a.kb), vsec = tl_val_section(D, a.vb);
+                if (whole) {
+                    uint8_t* rec = a.packed + (s_first >> 4) * (int64_t)tl_record_bytes(D, a.kb, a.vb);
+                    if (a.tiled == 1) assemble_key_chunk<D, BITS>(cb0, C::CODE_STRIDE, w, H, lane, rec);
+                    else assemble_val_chunk<D, BITS>(cb0, C::CODE_STRIDE, w, H, lane, rec + ksec);
+                    if (lane < 16)
+                        *reinterpret_cast<float*>(rec + ksec + vsec + tl_norm_offset(a.vb, a.tiled - 1, lane)) =
+                            *reinterpret_cast<const float*>(cb0 + myrow * C::CODE_STRIDE + D);
+                } else {
+                    for (int tok = 0; tok < 16; tok++) {
+                        const int rw = tile_row(w, tok, H);
+                        const int64_t orow = slot_s[rw];
+                        if (orow < 0) continue;
+                        uint32_t code[NQ];
+#pragma unroll
+                        for (int q = 0; q < NQ; q++) code[q] = cb0[rw * C::CODE_STRIDE + lane + 32 * q];
+                        tiled_store_row<NQ>(a.packed, a.tiled, a.kb, a.vb, orow, code,
+                                            *reinterpret_cast<const float*>(cb0 + rw * C::CODE_STRIDE + D), lane, D);
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(C::NEPI * 32) : "memory");          // the code bytes may be overwritten
             }
         }
         if (!ok && lane == 0) give_up();
@@ -668,6 +768,8 @@ int quantize_tc_try(const void* x, int dtype, int64_t n, int dim, int64_t x_stri
     TcArgs a{};
     a.x = x; a.n = n; a.x_stride = x_stride; a.rot = rot; a.bnd = bnd; a.bits = bits; a.packed = packed; a.norms = norms;
     a.map = map; a.tiled = tiled; a.kb = kb; a.vb = vb;
+    const int64_t units = map.slots ? map.inner : 1;       // paged appends walk the heads of a token first
+    a.heads = (units == 1 || units == 2 || units == 4 || units == 8) ? (int)units : 0;
 #define TQB_TC(T) (dim == 64 ? tc_dispatch_bits<T, 64>(a, st) : tc_dispatch_bits<T, 128>(a, st))
     switch (dtype) {
         case TQB_F32: return TQB_TC(float);
