@@ -27,7 +27,10 @@ One JSON line is printed by rank 0:
             pair per launch
   cpu_baseline  the CPU checker (oracle/, an OpenMP port of the upstream dequantise-then-attend path)
             timed on this machine's cores on a sample of the same workload
-  extra     secondary figures: shorter contexts, and the 4-bit index scan (QPS and HBM GB/s)
+  extra     secondary figures: shorter contexts; the paged Llama-3-8B configuration as a whole (32 layers
+            resident, decode step and prefill quantisation timed apart, parity against the CPU port); the
+            quantiser; the 4-bit index scan over 10 M rows (QPS, HBM GB/s, and the first queries again with
+            the upstream C++ core over all rows)
 
 --impl reference times only the CPU port, on a bounded sample per step, and prints the same line shape.
 """
@@ -51,11 +54,13 @@ LAYERS, Q_HEADS, KV_HEADS, HEAD_DIM, BATCH = 16, 32, 8, 64, 32
 KEY_BITS, VALUE_BITS = 4, 2
 BYTES_PER_TOKEN_HEAD = KEY_BITS * HEAD_DIM // 8 + 4 + VALUE_BITS * HEAD_DIM // 8 + 4   # 56
 METRIC, UNIT = "decode_attention_tokens_per_s", "tokens/s"
-# DRAM traffic of one decode_partial_kernel launch from an ncu capture of a full-size launch of this
-# workload (dram__bytes_read.sum 235.18 MB + dram__bytes_write.sum 14.09 MB against 234.88 MB of
-# algorithmic bytes); traffic grows in proportion to the tokens, so other sizes are scaled by the ratio.
-NCU_TRAFFIC_RATIO = (235.18 + 14.09) / 234.88
-NCU_TRAFFIC_SOURCE = "profiles/decode_partial_kernel_c4_ctx16384.md (ncu dram__bytes_read.sum + dram__bytes_write.sum)"
+# DRAM traffic of one decode_fused_kernel launch, cited from an ncu capture of a full-size launch of this
+# workload (dram__bytes_read.sum 244.27 MB + dram__bytes_write.sum 14.87 MB against 234.88 MB of algorithmic
+# bytes); traffic grows in proportion to the tokens, so other sizes are scaled by the ratio.  It is a
+# citation of that capture, not a live measurement: counters cannot be read inside the timed run.
+NCU_TRAFFIC_RATIO = (244.27 + 14.87) / 234.88
+NCU_TRAFFIC_SOURCE = ("cited from profiles/decode_fused_kernel_c4_ctx16384.md (ncu dram__bytes_read.sum + "
+                      "dram__bytes_write.sum of one launch), scaled by the bytes of this launch")
 
 
 def workload_config(ctx: int, world: int) -> dict:
