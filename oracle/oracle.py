@@ -335,6 +335,23 @@ def ref_search_packed(queries, packed, norms, rotation, centroids, bits: int, k:
     return sc, ids
 
 
+def ref_index_build_save(vectors, bits: int, seed: int, path: str):
+    """Upstream C++ ``TurboQuantIndex``: add the vectors, ``save(path)`` (csrc/core/turboquant_core.cpp:523-581).
+    Returns the rows the core holds: (packed (n, bits * ceil(dim / 8)), norms (n,))."""
+    lib = ref_lib()
+    if lib is None:
+        raise RuntimeError("oracle/_ref/libtq_ref.so was not built (no upstream checkout)")
+    x = _f32(vectors)
+    n, dim = x.shape
+    packed = np.empty((n, packed_dim(dim, bits)), dtype=np.uint8)
+    norms = np.empty(n, dtype=np.float32)
+    lib.tqr_index_build_save.restype = ctypes.c_int
+    got = lib.tqr_index_build_save(_p(x, _f32p), n, dim, bits, seed, path.encode(), _p(packed, _u8p), _p(norms, _f32p))
+    if got != n:
+        raise RuntimeError("the upstream core failed to build or save the index")
+    return packed, norms
+
+
 def ref_quantize(x, bits: int, rotation, boundaries, centroids):
     """Upstream ``turboquant::quantize_vectors`` (csrc/core/turboquant_core.cpp:277-343)."""
     lib = ref_lib()

@@ -11,6 +11,7 @@
  */
 #include <cstdint>
 #include <cstring>
+#include <string>
 
 #include "turboquant_core.h"
 
@@ -71,6 +72,24 @@ __attribute__((visibility("default"))) void tqr_dequantize(
     cb.scaled_boundaries.assign(cb.n_levels - 1, 0.0f);
     cb.scaled_centroids.assign(centroids, centroids + cb.n_levels);
     turboquant::dequantize_vectors(packed, norms, n, dim, rotation, cb, out);
+}
+
+/* turboquant::TurboQuantIndex add() + save(), csrc/core/turboquant_core.cpp:523-581: builds an index with
+ * the core's OWN rotation and codebook (drawn from `seed` by its generators) and writes it in the core's
+ * file layout; the rows the core holds are returned for comparison.  Used to produce the file fixture. */
+__attribute__((visibility("default"))) int tqr_index_build_save(
+    const float* vectors, int n, int dim, int bits, int seed, const char* path, uint8_t* out_packed,
+    float* out_norms) {
+    try {
+        turboquant::TurboQuantIndex idx(dim, bits, seed);
+        idx.add(vectors, n);
+        idx.save(path);
+        std::memcpy(out_packed, idx.packed_codes().data(), idx.packed_codes().size());
+        std::memcpy(out_norms, idx.norms().data(), idx.norms().size() * sizeof(float));
+        return idx.n_vectors();
+    } catch (...) {
+        return -1;
+    }
 }
 
 }  // extern "C"

@@ -21,6 +21,11 @@ Files written (all small):
                   (MSE mode only: in Prod mode the upstream cache allocates key_bits planes,
                   cache.py:84-85, but quantize_prod returns key_bits-1, so append raises)
   search.npz      TurboQuantIndex.add / search, MSE and Prod               (search.py:126-252)
+  hf_prod.npz     TurboQuantCache(mode="prod").update over two calls       (hf_integration.py:82-236, 339-390)
+  index_files.npz index files as upstream writes them: TurboQuantIndex.save() in MSE and Prod mode
+                  (search.py:254-277) and -- when oracle/_ref/libtq_ref.so is built -- the C++ core's
+                  save() (csrc/core/turboquant_core.cpp:559-581), each with the search results / rows
+                  upstream holds for it
 """
 from __future__ import annotations
 
@@ -193,6 +198,49 @@ def main() -> None:
             srch[f"signs_b{bits}_{mode}"] = idx._qjl_signs.numpy()
             srch[f"res_norms_b{bits}_{mode}"] = idx._residual_norms.numpy()
     save("search.npz", **srch)
+
+    # ------------------------------------------------------------------ HF cache, Prod mode
+    from turboquant_kv.hf_integration import TurboQuantCache
+
+    hf = {}
+    g = torch.Generator().manual_seed(321)
+    cache = TurboQuantCache(key_bits=3, value_bits=4, mode="prod", seed=42)
+    for step, t in enumerate((7, 1)):
+        k = torch.randn(2, 2, t, 64, generator=g)
+        v = torch.randn(2, 2, t, 64, generator=g)
+        ko, vo = cache.update(k, v, 0)
+        hf[f"k{step}"], hf[f"v{step}"] = k.numpy(), v.numpy()
+        hf[f"keys_out{step}"], hf[f"values_out{step}"] = ko.numpy(), vo.numpy()
+    save("hf_prod.npz", **hf)
+
+    # ------------------------------------------------------------------ index files written by upstream
+    import tempfile
+
+    files = {}
+    small = db[:400]
+    with tempfile.TemporaryDirectory() as tmp:
+        for bits, mode in ((4, "mse"), (3, "prod")):
+            idx = TurboQuantIndex(dim=128, bit_width=bits, mode=mode, seed=42)
+            assert not idx._use_cpp
+            idx.add(torch.from_numpy(small))
+            path = os.path.join(tmp, f"{mode}.idx")
+            idx.save(path)
+            scores, ids = idx.search(torch.from_numpy(qs), k=10)
+            files[f"file_{mode}"] = np.frombuffer(open(path, "rb").read(), dtype=np.uint8)
+            files[f"scores_{mode}"], files[f"ids_{mode}"] = scores.numpy(), ids.numpy()
+        try:
+            sys.path.insert(0, os.path.dirname(os.path.dirname(here)))
+            from oracle import oracle as orc
+
+            if orc.ref_lib() is not None:
+                path = os.path.join(tmp, "core.tqix")
+                packed, norms = orc.ref_index_build_save(small, 4, 42, path)
+                files["file_core"] = np.frombuffer(open(path, "rb").read(), dtype=np.uint8)
+                files["core_packed"], files["core_norms"] = packed, norms
+        except Exception as exc:  # the C++ core is optional
+            print("C++ core file skipped:", exc)
+    files["queries"] = qs.astype(np.uint8)
+    save("index_files.npz", **files)
 
 
 if __name__ == "__main__":

@@ -79,3 +79,38 @@ def test_c_abi_reports_errors_without_raising_across_the_boundary():
     assert L.tqb_pack_codes(N.ptr(torch.zeros(4, 64, dtype=torch.uint8, device="cuda")), 4, 64, 1, N.ptr(y), None) == 0
     assert N.launch_count() == before + 1
     torch.cuda.synchronize()
+
+
+def test_hf_cache_prod_mode_matches_upstream_fixture(orc, golden):
+    """TurboQuantCache(mode="prod") (upstream hf_integration.py:82-236): update() returns the Algorithm-2
+    reconstruction of the old tokens and the new tokens exactly; compared with the outputs of the upstream
+    class on the same inputs and with the CPU checker's quantize_prod / dequantize_prod."""
+    from turboquant_kv import TurboQuantCache
+
+    g = golden("hf_prod")
+    cache = TurboQuantCache(key_bits=3, value_bits=4, mode="prod", seed=42)
+    seen = 0
+    for step in (0, 1):
+        k, v = torch.from_numpy(g[f"k{step}"]).cuda(), torch.from_numpy(g[f"v{step}"]).cuda()
+        ko, vo = cache.update(k, v, 0)
+        assert ko.shape == tuple(g[f"keys_out{step}"].shape) and vo.shape == ko.shape
+        assert torch.equal(ko[:, :, seen:], k) and torch.equal(vo[:, :, seen:], v)       # new tokens exact
+        np.testing.assert_allclose(ko.cpu().numpy(), g[f"keys_out{step}"], atol=3e-5)
+        np.testing.assert_allclose(vo.cpu().numpy(), g[f"values_out{step}"], atol=3e-5)
+        seen += k.shape[2]
+    assert cache.get_seq_length(0) == 8
+    # the stored rows against the checker
+    st = cache._layer_stores[0]
+    for which, bits, seed in (("key", 3, 42), ("value", 4, 43)):
+        x = np.concatenate([g[f"{which[0]}0"], g[f"{which[0]}1"]], axis=2).reshape(-1, 64)
+        rot = orc.make_rotation_matrix(64, seed)
+        bnd, cent = orc.lloyd_max_codebook(bits - 1, 64)
+        S = orc.make_qjl_matrix(64, 64, seed)
+        mp, sg, rn, nr = orc.quantize_prod(x, bits, rot, bnd, cent, S)
+        got = [t.reshape((-1,) + tuple(t.shape[3:])).cpu().numpy() for t in st.export(which)]
+        assert np.array_equal(got[0], mp) and np.array_equal(got[1], sg)
+        np.testing.assert_allclose(got[2], rn, rtol=1e-5)
+        np.testing.assert_allclose(got[3], nr, rtol=2e-6)
+    assert cache.memory_bytes() == 2 * 2 * 8 * ((2 * 8 + 8 + 8) + (3 * 8 + 8 + 8))
+    with pytest.raises(RuntimeError):
+        cache.decode_attention(torch.zeros(2, 2, 64, device="cuda"), 0)

@@ -273,3 +273,55 @@ def test_index_records_hold_exactly_the_upstream_rows(dim, bits):
     rc = L.tqb_kv_export(store.data_ptr(), n, dim, bits, 0, None, back_c.data_ptr(), back_n.data_ptr(),
                          back_c.data_ptr(), None, st)
     assert rc != 0 and "key-only" in L.tqb_last_error().decode()
+
+
+@pytest.mark.parametrize("mode,bits", [("mse", 4), ("prod", 3)])
+def test_load_reads_files_written_by_upstream_save(tmp_path, golden, orc, mode, bits):
+    """An index file written by the upstream Python ``TurboQuantIndex.save()`` (search.py:254-277; the bytes
+    are part of the fixture) loads here and searches like the upstream index it came from."""
+    from turboquant_kv import TurboQuantIndex
+
+    g = golden("index_files")
+    p = str(tmp_path / f"upstream_{mode}.idx")
+    g[f"file_{mode}"].tofile(p)
+    idx = TurboQuantIndex.load(p, seed=42)
+    assert (idx.mode, idx.bit_width, idx.dim, idx.n_vectors) == (mode, bits, 128, 400)
+    qs = g["queries"].astype(np.float32)
+    sc, ids = idx.search(torch.from_numpy(qs), k=10)
+    # all scores of the upstream index's rows, for the tie rule
+    rot = orc.make_rotation_matrix(128, 42)
+    packed, norms = idx._packed_codes.cpu().numpy(), idx._norms.cpu().numpy()
+    if mode == "prod":
+        _, cent = orc.lloyd_max_codebook(bits - 1, 128)
+        _, _, allsc = orc.search_prod(qs, packed, idx._qjl_signs.cpu().numpy(), idx._residual_norms.cpu().numpy(), norms,
+                                      rot, cent, orc.make_qjl_matrix(128, 128, 42), bits, 10, return_all=True)
+    else:
+        _, cent = orc.lloyd_max_codebook(bits, 128)
+        _, _, allsc = orc.search_mse(qs, packed, norms, rot, cent, bits, 10, return_all=True)
+    topk_ids_match(ids.numpy(), g[f"ids_{mode}"], allsc)
+    np.testing.assert_allclose(sc.numpy(), g[f"scores_{mode}"], rtol=2e-5)
+    # and a file written here is byte-identical to upstream's for the same index
+    q = str(tmp_path / f"again_{mode}.idx")
+    idx.save(q)
+    assert np.array_equal(np.fromfile(q, dtype=np.uint8), g[f"file_{mode}"])
+
+
+def test_load_reads_a_file_written_by_the_upstream_cpp_core(tmp_path, golden):
+    """A file written by the upstream C++ core's ``save()`` (csrc/core/turboquant_core.cpp:559-581): header and
+    rows are read as the core holds them, and writing them back reproduces the file.  (The core draws its
+    rotation and codebook from its own generators, so searching such rows needs the core's constants; the
+    layout is what is checked here.)"""
+    from turboquant_kv import TurboQuantIndex
+
+    g = golden("index_files")
+    if "file_core" not in g:
+        pytest.skip("the fixture was generated without the C++ core")
+    p = str(tmp_path / "core.tqix")
+    g["file_core"].tofile(p)
+    idx = TurboQuantIndex.load(p)
+    assert (idx.mode, idx.bit_width, idx.dim, idx.n_vectors, idx.seed) == ("mse", 4, 128, 400, 42)
+    assert np.array_equal(idx._packed_codes.cpu().numpy(), g["core_packed"])
+    assert np.array_equal(idx._norms.cpu().numpy(), g["core_norms"])
+    q = str(tmp_path / "again.tqix")
+    idx.save(q, format="tqix")
+    assert np.array_equal(np.fromfile(q, dtype=np.uint8), g["file_core"])

@@ -212,3 +212,41 @@ def test_upstream_cpp_core_agrees_with_oracle(orc, golden):
     np.testing.assert_allclose(sc, rsc, rtol=1e-6)
     p, n = orc.ref_quantize(g["db"].astype(np.float32), 4, rot, bnd, cent)
     assert (p != g["packed_b4_mse"]).mean() < 1e-4
+
+
+def test_hf_prod_cache_fixture_is_algorithm_2_on_every_head(orc, golden):
+    """The upstream HF cache in Prod mode (hf_integration.py:82-236): what update() returns for the OLD tokens
+    is dequantize_prod(quantize_prod(.)) per head with the layer's constants (keys: seed, values: seed + 1),
+    the NEW tokens come back exactly."""
+    g = golden("hf_prod")
+    for which, bits, seed in (("k", 3, 42), ("v", 4, 43)):
+        rot = orc.make_rotation_matrix(64, seed)
+        bnd, cent = orc.lloyd_max_codebook(bits - 1, 64)
+        S = orc.make_qjl_matrix(64, 64, seed)
+        first = g[f"{which}0"]                                        # (batch, heads, 7, 64)
+        out1 = g["keys_out1" if which == "k" else "values_out1"]      # (batch, heads, 8, 64)
+        assert np.array_equal(out1[:, :, 7:], g[f"{which}1"])
+        mp, sg, rn, nr = orc.quantize_prod(first.reshape(-1, 64), bits, rot, bnd, cent, S)
+        rec = orc.dequantize_prod(mp, sg, rn, nr, bits, 64, rot, cent, S).reshape(first.shape)
+        np.testing.assert_allclose(out1[:, :, :7], rec, atol=3e-5)
+
+
+def test_upstream_index_files_have_the_documented_layout(orc, golden):
+    """Files written by upstream save() (search.py:254-277) and by the C++ core (turboquant_core.cpp:559-581):
+    header fields and section sizes as the loader of this repository assumes them."""
+    import struct
+
+    g = golden("index_files")
+    for mode, bits in (("mse", 4), ("prod", 3)):
+        blob = g[f"file_{mode}"].tobytes()
+        bw, dim, n = struct.unpack_from("<BII", blob, 0)               # bit width (u8), dim, rows; then a mode byte
+        assert (bw, dim, n, blob[9]) == (bits, 128, 400, 0 if mode == "mse" else 1)
+        per_row = (bits if mode == "mse" else bits - 1) * 16 + 4 + (16 + 4 if mode == "prod" else 0)
+        assert len(blob) == 10 + 400 * per_row
+    if "file_core" in g:
+        blob = g["file_core"].tobytes()
+        magic, version, dim, bits, seed, n = struct.unpack_from("<6I", blob, 0)
+        assert (magic, version, dim, bits, seed, n) == (0x54514958, 1, 128, 4, 42, 400)
+        assert len(blob) == 24 + 400 * (64 + 4)
+        assert np.array_equal(np.frombuffer(blob, np.uint8, 400 * 64, 24).reshape(400, 64), g["core_packed"])
+        assert np.array_equal(np.frombuffer(blob, np.float32, 400, 24 + 400 * 64), g["core_norms"])

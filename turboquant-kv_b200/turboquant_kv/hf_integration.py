@@ -37,8 +37,6 @@ class _LayerQuantStore:
     """Packed keys and values of one layer for a whole batch; capacity doubles as tokens arrive."""
 
     def __init__(self, tq_config: TurboQuantConfig, batch: int, num_heads: int, head_dim: int, device):
-        if tq_config.mode != "mse":
-            raise RuntimeError("TurboQuantCache (B200 build) implements mode='mse'")
         self.tq_config, self.batch, self.num_heads, self.head_dim = tq_config, batch, num_heads, head_dim
         self.device = torch.device(device)
         self.seq_len = 0
@@ -99,6 +97,101 @@ class _LayerQuantStore:
         return self.batch * self.num_heads * self.seq_len * per_token
 
 
+class _LayerProdStore:
+    """Prod-mode keys and values of one layer for a whole batch (upstream hf_integration.py:82-143, 210-236):
+    both are quantised with Algorithm 2 (MSE codes at bits - 1, one QJL residual sign per dimension, the
+    residual norm, the norm) and kept as upstream-layout rows -- (batch, heads, capacity, ...) tensors that
+    double as tokens arrive, instead of upstream's per-append chunk lists.  One ``tqb_quantize_prod`` /
+    ``tqb_dequantize_prod`` launch serves all heads and sequences (they share rotation, codebook and S)."""
+
+    FIELDS = ("packed", "signs", "res", "norms")
+
+    def __init__(self, tq_config: TurboQuantConfig, batch: int, num_heads: int, head_dim: int, device):
+        from .reference import _make_qjl_matrix, lloyd_max_codebook, make_rotation_matrix
+
+        if min(tq_config.key_bits, tq_config.value_bits) < 2:
+            raise ValueError("mode='prod' needs at least 2 bits (1 MSE bit + 1 sign bit)")
+        self.tq_config, self.batch, self.num_heads, self.head_dim = tq_config, batch, num_heads, head_dim
+        self.device = torch.device(device)
+        self.seq_len = 0
+        self.capacity = 0
+        self._side = {}
+        for name, bits, seed in (("key", tq_config.key_bits, tq_config.seed), ("value", tq_config.value_bits, tq_config.seed + 1)):
+            self._side[name] = {
+                "bits": bits,
+                "rotation": make_rotation_matrix(head_dim, seed=seed, method=tq_config.rotation).to(self.device),
+                "codebook": tuple(t.to(self.device) for t in lloyd_max_codebook(bits - 1, head_dim)),
+                "S": _make_qjl_matrix(head_dim, head_dim, seed, self.device),
+                "packed": None, "signs": None, "res": None, "norms": None,
+            }
+
+    def _reserve(self, need: int) -> None:
+        if need <= self.capacity:
+            return
+        cap = max(256, self.capacity)
+        while cap < need:
+            cap *= 2
+        B, H, D = self.batch, self.num_heads, self.head_dim
+        for side in self._side.values():
+            shapes = {"packed": ((side["bits"] - 1) * ((D + 7) // 8), torch.uint8), "signs": ((D + 7) // 8, torch.uint8),
+                      "res": (None, torch.float32), "norms": (None, torch.float32)}
+            for f, (last, dt) in shapes.items():
+                new = torch.zeros((B, H, cap) + ((last,) if last else ()), dtype=dt, device=self.device)
+                if side[f] is not None:
+                    new[:, :, : self.seq_len] = side[f][:, :, : self.seq_len]
+                side[f] = new
+        self.capacity = cap
+
+    def append(self, key: torch.Tensor, value: torch.Tensor) -> None:
+        """key / value: (batch, heads, new, head_dim)."""
+        from .reference import quantize_prod
+
+        B, H, T, D = key.shape
+        self._reserve(self.seq_len + T)
+        lo, hi = self.seq_len, self.seq_len + T
+        for name, x in (("key", key), ("value", value)):
+            side = self._side[name]
+            mp, sg, rn, nr = quantize_prod(x.reshape(B * H * T, D), side["bits"], dim=D, rotation=side["rotation"],
+                                           codebook=side["codebook"], S_matrix=side["S"])
+            side["packed"][:, :, lo:hi] = mp.view(B, H, T, -1)
+            side["signs"][:, :, lo:hi] = sg.view(B, H, T, -1)
+            side["res"][:, :, lo:hi] = rn.view(B, H, T)
+            side["norms"][:, :, lo:hi] = nr.view(B, H, T)
+        self.seq_len = hi
+
+    def _dense(self, which: str, dtype) -> torch.Tensor:
+        from .reference import dequantize_prod
+
+        B, H, S, D = self.batch, self.num_heads, self.seq_len, self.head_dim
+        if S == 0:
+            return torch.zeros(B, H, 0, D, dtype=dtype, device=self.device)
+        side = self._side[which]
+        rows = [side[f][:, :, :S].reshape((B * H * S,) + tuple(side[f].shape[3:])) for f in self.FIELDS]
+        out = dequantize_prod(rows[0], rows[1], rows[2], rows[3], side["bits"], D, rotation=side["rotation"],
+                              codebook=side["codebook"], S_matrix=side["S"])
+        return out.view(B, H, S, D).to(dtype)
+
+    def get_keys(self, dtype=torch.float32) -> torch.Tensor:
+        return self._dense("key", dtype)
+
+    def get_values(self, dtype=torch.float32) -> torch.Tensor:
+        return self._dense("value", dtype)
+
+    def export(self, which: str = "key"):
+        """Upstream-layout rows of one side: mse_packed (B, H, S, .), signs (B, H, S, .), residual norms, norms."""
+        S = self.seq_len
+        return tuple(self._side[which][f][:, :, :S] for f in self.FIELDS)
+
+    def decode_attention(self, query: torch.Tensor, scale: Optional[float]) -> torch.Tensor:
+        raise RuntimeError("TurboQuantCache(mode='prod') has no fused decode kernel in this build: use update(), "
+                           "which returns the dequantised history as upstream does")
+
+    def packed_bytes(self) -> int:
+        D = self.head_dim
+        per_token = sum((s["bits"] - 1) * ((D + 7) // 8) + (D + 7) // 8 + 8 for s in self._side.values())
+        return self.batch * self.num_heads * self.seq_len * per_token
+
+
 class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
     """``DynamicCache`` whose layers hold TurboQuant codes instead of fp16 tensors."""
 
@@ -119,7 +212,8 @@ class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
             if not like.is_cuda:
                 raise RuntimeError("TurboQuantCache (B200 build) needs CUDA key/value states; there is no CPU path")
             B, H, _, D = like.shape
-            st = _LayerQuantStore(self.tq_config, B, H, D, like.device)
+            cls = _LayerProdStore if self.tq_config.mode == "prod" else _LayerQuantStore
+            st = cls(self.tq_config, B, H, D, like.device)
             self._layer_stores[layer_idx] = st
         return st
 
