@@ -174,10 +174,19 @@ def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice
         kp, kn, vp, vn = (np.ascontiguousarray(a[:, heads]) for a in (kp, kn, vp, vn))
         q = np.ascontiguousarray(q[:, heads.start * group:heads.stop * group])
 
-    def one_step():
-        orc.quantize_mse(newk, KEY_BITS, rk, bk)       # the appended token of this layer
-        orc.quantize_mse(newk, VALUE_BITS, rv, bv)
-        return orc.decode_attention(q, kp, kn, vp, vn, lens, rk, ck, KEY_BITS, rv, cv, VALUE_BITS)
+    # the timed arm: the upstream project's own OpenMP kernels (csrc/cpu/quant_cpu.cpp compiled in place into
+    # oracle/_ref) when that library travelled here, else the port
+    use_ref = orc.ref_cpu_lib() is not None and not os.environ.get("TQB_BENCH_CPU_PORT")
+    if use_ref:
+        def one_step():
+            orc.ref_cpu_quantize(newk, KEY_BITS, rk, bk)
+            orc.ref_cpu_quantize(newk, VALUE_BITS, rv, bv)
+            return orc.ref_cpu_decode_attention(q, kp, kn, vp, vn, lens, rk, ck, KEY_BITS, rv, cv, VALUE_BITS, threads=cores)
+    else:
+        def one_step():
+            orc.quantize_mse(newk, KEY_BITS, rk, bk)       # the appended token of this layer
+            orc.quantize_mse(newk, VALUE_BITS, rv, bv)
+            return orc.decode_attention(q, kp, kn, vp, vn, lens, rk, ck, KEY_BITS, rv, cv, VALUE_BITS)
 
     out = None
     for _ in range(warmup):
@@ -189,23 +198,32 @@ def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice
     full_step = dt * LAYERS * BATCH / sample_seqs
     desc = (f"{sample_seqs} of {BATCH} sequences x {KV_HEADS} KV heads of 1 of {LAYERS} layers at context {ctx}, "
             f"scaled by {LAYERS * BATCH // sample_seqs}")
-    data = dict(q=q, kp=kp, kn=kn, vp=vp, vn=vn, out=out)
+    data = dict(q=q, kp=kp, kn=kn, vp=vp, vn=vn, out=out, kind="reference" if use_ref else "port")
     return BATCH / full_step, dt, cores, desc, data
+
+
+CPU_NOTE = {
+    "reference": "the upstream project's own OpenMP kernels (csrc/cpu/quant_cpu.cpp: rotate_and_quantize_cpu, "
+                 "attention_scores_packed_cpu, attention_values_packed_cpu), compiled in place into oracle/_ref and "
+                 "driven per (sequence, KV head) as the upstream cache does, units spread over the host threads",
+    "port": "CPU port of the upstream dequantise-then-attend path (oracle/tq_oracle.c, OpenMP): the library of the "
+            "upstream CPU kernels (oracle/_ref/libtq_ref_cpu.so) is not on this machine",
+}
 
 
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
-    value, dt, cores, desc, _ = cpu_sample(args.ctx, args.cpu_seqs, args.steps, args.warmup)
+    value, dt, cores, desc, data = cpu_sample(args.ctx, args.cpu_seqs, args.steps, args.warmup)
+    kind = data["kind"]
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * BATCH / value,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args.ctx, world),
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc,
                              "sample_step_s": dt},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "note": "CPU port of the upstream dequantise-then-attend path (oracle/tq_oracle.c, OpenMP); the upstream "
-                    "CPU kernels need torch headers and its Python path needs the upstream checkout, neither travels"}
+            "note": CPU_NOTE[kind]}
     print(json.dumps(line), flush=True)
 
 
@@ -411,8 +429,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
 
     if rank == 0 and world == 1 and not args.no_cpu:
         value, dt, cores, desc, data = cpu_sample(ctx, args.cpu_seqs, 1, 0)
-        line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
-                                "sample_step_s": dt}
+        line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cores, "kind": data["kind"], "sample": desc,
+                                "sample_step_s": dt, "note": CPU_NOTE[data["kind"]]}
         line["parity"] = parity_check(torch, data, device)
     elif world > 1 and not args.no_cpu:
         # every rank checks ITS head slice (2 sequences x its KV heads x the full context) against the CPU port
@@ -444,8 +462,9 @@ def parity_check(torch, data, device) -> dict:
     got = cache.decode_attention(0, torch.from_numpy(data["q"]).to(device)).float().cpu().numpy()
     ref = data["out"]
     cos = float((got * ref).sum() / np.sqrt((got * got).sum() * (ref * ref).sum()))
+    against = ("the upstream CPU kernels (csrc/cpu/quant_cpu.cpp)" if data.get("kind") == "reference" else "CPU port, dequantise-then-attend")
     return {"max_abs": float(np.abs(got - ref).max()), "cosine": cos, "tolerance": "1e-2 max-abs, cosine >= 0.9999",
-            "against": "CPU port, dequantise-then-attend, same packed cache"}
+            "against": against + ", same packed cache"}
 
 
 # ------------------------------------------------------------------------------------------------

@@ -59,6 +59,27 @@ def ref_lib():
     return _REF
 
 
+_REF_CPU = None
+
+
+def ref_cpu_lib():
+    """The upstream CPU kernels (csrc/cpu/quant_cpu.cpp) behind ref_cpu_shim.cpp, or None when never built.
+    The library links against torch: torch is imported first so that its shared objects are loaded."""
+    global _REF_CPU
+    if _REF_CPU is None:
+        path = os.path.join(_HERE, "_ref", "libtq_ref_cpu.so")
+        if not os.path.exists(path):
+            return None
+        import torch  # noqa: F401  (loads libtorch_cpu / libc10 into the process)
+
+        try:
+            _REF_CPU = ctypes.CDLL(path)
+        except OSError:
+            return None
+        _REF_CPU.tqc_num_threads.restype = ctypes.c_int
+    return _REF_CPU
+
+
 def num_threads() -> int:
     return int(_lib().tqo_num_threads())
 
@@ -68,6 +89,8 @@ def set_num_threads(n: int) -> None:
     r = ref_lib()
     if r is not None:
         r.tqr_set_num_threads(int(n))
+    if _REF_CPU is not None:
+        _REF_CPU.tqc_set_num_threads(int(n))
 
 
 def _f32(a):
@@ -281,6 +304,48 @@ def decode_attention(query, k_packed, k_norms, v_packed, v_norms, seq_lens, rot_
                                 _p(_f32(cent_v), _f32p), vbits, ctypes.c_float(scale),
                                 _p(out, _f32p))
     return out
+
+
+def ref_cpu_decode_attention(query, k_packed, k_norms, v_packed, v_norms, seq_lens, rot_k, cent_k, kbits,
+                             rot_v, cent_v, vbits, scale=None, threads: int = 0):
+    """The same decode step with the UPSTREAM CPU kernels (csrc/cpu/quant_cpu.cpp:125-266): per (sequence, KV
+    head) attention_scores_packed_cpu, softmax, attention_values_packed_cpu.  Arguments as decode_attention."""
+    lib = ref_cpu_lib()
+    if lib is None:
+        raise RuntimeError("oracle/_ref/libtq_ref_cpu.so was not built (no upstream checkout)")
+    q = _f32(query)
+    batch, q_heads, dim = q.shape
+    kp, kn, vp, vn = _u8(k_packed), _f32(k_norms), _u8(v_packed), _f32(v_norms)
+    kv_heads, max_seq = kp.shape[1], kp.shape[2]
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    if scale is None:
+        scale = 1.0 / math.sqrt(dim)
+    lib.tqc_set_num_threads(int(threads) if threads else (os.cpu_count() or 1))
+    out = np.empty((batch, q_heads, dim), dtype=np.float32)
+    # attention_values_packed_cpu ends with out = rotated @ M; the inverse of y = R x is x = y @ R
+    rc = lib.tqc_decode_attention(_p(q, _f32p), _p(kp, _u8p), _p(kn, _f32p), _p(vp, _u8p), _p(vn, _f32p),
+                                  _p(sl, _i32p), batch, q_heads, kv_heads, max_seq, dim, kbits, vbits,
+                                  _p(_f32(rot_k), _f32p), _p(_f32(cent_k), _f32p), _p(_f32(rot_v), _f32p),
+                                  _p(_f32(cent_v), _f32p), ctypes.c_float(scale), _p(out, _f32p))
+    if rc != 0:
+        raise RuntimeError("the upstream CPU kernels raised")
+    return out
+
+
+def ref_cpu_quantize(x, bits: int, rotation, boundaries):
+    """Upstream rotate_and_quantize_cpu (csrc/cpu/quant_cpu.cpp:44-119)."""
+    lib = ref_cpu_lib()
+    if lib is None:
+        raise RuntimeError("oracle/_ref/libtq_ref_cpu.so was not built (no upstream checkout)")
+    v = _f32(x)
+    n, dim = v.shape
+    packed = np.empty((n, packed_dim(dim, bits)), dtype=np.uint8)
+    norms = np.empty(n, dtype=np.float32)
+    rc = lib.tqc_rotate_and_quantize(_p(v, _f32p), n, dim, _p(_f32(rotation), _f32p), _p(_f32(boundaries), _f32p), bits,
+                                     _p(packed, _u8p), _p(norms, _f32p))
+    if rc != 0:
+        raise RuntimeError("the upstream CPU kernels raised")
+    return packed, norms
 
 
 def search_mse(queries, packed, norms, rotation, centroids, bits: int, k: int,

@@ -250,3 +250,30 @@ def test_upstream_index_files_have_the_documented_layout(orc, golden):
         assert len(blob) == 24 + 400 * (64 + 4)
         assert np.array_equal(np.frombuffer(blob, np.uint8, 400 * 64, 24).reshape(400, 64), g["core_packed"])
         assert np.array_equal(np.frombuffer(blob, np.float32, 400, 24 + 400 * 64), g["core_norms"])
+
+
+def test_upstream_cpu_kernels_agree_with_oracle(orc):
+    """The upstream OpenMP kernels (csrc/cpu/quant_cpu.cpp, compiled in place into oracle/_ref) on a small
+    cache: their decode step equals the checker's dequantise-then-attend, and rotate_and_quantize_cpu yields
+    the checker's codes (ties aside)."""
+    if orc.ref_cpu_lib() is None:
+        pytest.skip("oracle/_ref/libtq_ref_cpu.so is not built here")
+    rng = np.random.default_rng(12)
+    batch, kvh, group, dim, seq = 3, 2, 4, 64, 300
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(2, dim)
+    k = rng.standard_normal((batch * kvh * seq, dim), dtype=np.float32)
+    v = rng.standard_normal((batch * kvh * seq, dim), dtype=np.float32)
+    kp, kn = orc.quantize_mse(k, 4, rk, bk)
+    vp, vn = orc.quantize_mse(v, 2, rv, bv)
+    r_kp, r_kn = orc.ref_cpu_quantize(k, 4, rk, bk)
+    assert (r_kp != kp).mean() < 1e-4
+    np.testing.assert_allclose(r_kn, kn, rtol=2e-6)
+    q = rng.standard_normal((batch, kvh * group, dim), dtype=np.float32)
+    lens = np.array([seq, 17, 0], np.int32)
+    args = (q, kp.reshape(batch, kvh, seq, -1), kn.reshape(batch, kvh, seq), vp.reshape(batch, kvh, seq, -1),
+            vn.reshape(batch, kvh, seq), lens, rk, ck, 4, rv, cv, 2)
+    want = orc.decode_attention(*args)
+    got = orc.ref_cpu_decode_attention(*args, threads=4)
+    np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)
