@@ -49,10 +49,13 @@ __attribute__((visibility("default"))) int tqc_num_threads() {
 }
 
 __attribute__((visibility("default"))) void tqc_set_num_threads(int n) {
+    // torch's own intra-op pool first (it sets the OpenMP thread count as a side effect), then the count for
+    // the loop over units below: inside that loop torch's operators run on the unit's thread (nested regions
+    // are serial).
+    at::set_num_threads(n > 0 ? n : 1);
 #ifdef _OPENMP
     if (n > 0) omp_set_num_threads(n);
 #endif
-    at::set_num_threads(1);      // softmax and copies inside a unit stay on the unit's thread
 }
 
 /* rotate_and_quantize_cpu, quant_cpu.cpp:44-119: (n, dim) float32 -> packed codes and norms. */

@@ -9,34 +9,38 @@
 // the CTAs.  Warp roles inside a CTA:
 //
 //   producer warp   streams the 16-token records of the CTA's items into a ring of shared-memory
-//                   stages, one TMA bulk copy (cp.async.bulk + mbarrier) of up to 28 KB per stage.
+//                   stages, one TMA bulk copy (cp.async.bulk + mbarrier) of up to 28 KB per stage.  It
+//                   starts as soon as the sequence lengths are known: the ring fills while the other
+//                   warps build the lookup tables and prepare the first item.
 //   helper warp     prepares the items one ahead of the consumers: q_rot = R_k q per head, times
 //                   scale * log2(e), written as mma.sync B fragments (fp16) into one of two
 //                   shared-memory slots; for a fused step it also quantises the unit's new key and value
 //                   and stores them into the record store before the producer copies that record (the
-//                   item that holds the write position does this).  The CTA's first item is prepared
-//                   before the roles split, by four warps while the others build the lookup tables.
+//                   item that holds the write position does this; the producer waits for it only before
+//                   the stage with that record).  The CTA's first item is prepared before the roles
+//                   split, by four warps while the others build the lookup tables.
 //                   It also speaks for the consumer warps: once all of them have stored their partial
-//                   of an item it bumps the unit's arrival counter (one fence for the lot); the helper
-//                   whose arrival completes a unit queues the unit for its CTA's tail phase.
+//                   of an item it counts the chunk into the unit's arrival counter (one fence for the lot).
 //   consumer warps  two groups take alternate stages, four records per warp.  Per record: scores =
 //                   K-codes x q on tensor cores (codes -> fp16 centroids through a 256-entry
 //                   shared-memory table indexed by one byte = 2 codes), online softmax in the log2
 //                   domain with a lazy running maximum, P^T via movmatrix, O^T += V^T-codes x P^T on
 //                   tensor cores, all in ROTATED space.  One (m, l, acc) partial per (item, warp).
-//   tail phase      once the CTA's own items are done its consumer warps merge the queued units: combine
-//                   the partials of a (unit, query head), divide by l, apply the inverse value rotation
-//                   acc @ R_v (reference.py:362) and write the output.  No warp ever waits for another
-//                   CTA.  The CTA that leaves last (exit counter) publishes the advanced sequence
-//                   lengths of a fused step.
+//   tail phase      once the CTA's own items are done its consumer warps take their share of ALL merges
+//                   (task (unit, query head) number t -> CTA t % grid, warp (t / grid) % warps): wait,
+//                   bounded, until the unit's chunks have been counted in, combine the partials, divide
+//                   by l, apply the inverse value rotation acc @ R_v (reference.py:362) and write the
+//                   output.  All CTAs are resident (grid <= SM count, one CTA per SM), so the wait is for
+//                   work in progress.  The CTA that leaves last (exit counter) clears the arrival
+//                   counters and publishes the advanced sequence lengths of a fused step.
 //
 // HBM traffic per token and KV head is the packed K row + packed V row + two float norms; everything
 // else lives in L2 / shared memory.
 //
 // Every wait is bounded: a warp that gives up raises a bit of the status word at the start of the
 // workspace and leaves, so a lost copy cannot hang the device.  The kernel only ever SETS bits of the
-// status word (atomicOr, TQB_DECODE_* in tqb200.h); the arrival counters return to zero by themselves at
-// the end of every call that ran to completion.  The caller zeroes the workspace once before its first
+// status word (atomicOr, TQB_DECODE_* in tqb200.h); the arrival counters are returned to zero at the end
+// of every call that ran to completion.  The caller zeroes the workspace once before its first
 // use and after a status with TQB_DECODE_WAIT_EXPIRED or TQB_DECODE_NO_SMEM set.
 #include "common.cuh"
 #include "pipe.cuh"
@@ -51,7 +55,6 @@ constexpr float RESCALE_SLACK = 4.0f;   // lazy max: rescale only when a score e
 constexpr int TILE = 16;                // tokens per MMA tile
 constexpr int QSLOTS = 2;               // query-fragment slots (the helper warp works one item ahead)
 constexpr int DSLOTS = 4;               // "every consumer warp has stored its partial" barriers, one per item in flight
-constexpr int TODO_MAX = 60;            // completed units a CTA queues for its tail phase
 constexpr int LEN_ROOM = 1 << 30;       // flag in an encoded length: this step appends a token to the sequence
 constexpr int LEN_MASK = LEN_ROOM - 1;
 constexpr int64_t MAX_LEN_LIMIT = (int64_t)1 << 30;
@@ -194,13 +197,22 @@ struct DecodeCfg {
     static constexpr int QFRAG = MT * 256;                          // one slot of query fragments: MT x 32 lanes x 8 B
     // misc: centroids (256) | barriers and stage headers (8*(8+8+16) = 256) | helper barriers (64) |
     //       boundaries (128) | unit vectors of the new key / value (2*D*4) | their codes (2*D) and norms (16) |
-    //       the unit's queries as float32 (8*D*4) | tail-phase queue (16 + 4*TODO_MAX) | lengths |
-    //       query-fragment slots
+    //       the unit's queries as float32 (8*D*4) | exit flags (16) | lengths |
+    //       query-fragment slots | R_k, R_v (head_dim 64)
     static constexpr int OFF_BARS = 256, OFF_QBARS = OFF_BARS + 256, OFF_BND = OFF_QBARS + 128;
     static constexpr int OFF_UNIT = OFF_BND + 128, OFF_CODES = OFF_UNIT + 2 * D * 4, OFF_NRM = OFF_CODES + 2 * D;
-    static constexpr int OFF_QVEC = OFF_NRM + 16, OFF_TODO = OFF_QVEC + 8 * D * 4, OFF_LENS = OFF_TODO + 16 + 4 * TODO_MAX;
+    static constexpr int OFF_QVEC = OFF_NRM + 16, OFF_TODO = OFF_QVEC + 8 * D * 4, OFF_LENS = OFF_TODO + 16;
     static constexpr int OFF_QFRAG = (OFF_LENS + LENS_MAX * 4 + 127) / 128 * 128;
-    static constexpr int MISC_FIXED = OFF_QFRAG + QSLOTS * QFRAG;
+    // head_dim 64: both rotation matrices live in shared memory (rows ROT_STRIDE floats apart: the 128-bit
+    // loads of 32 lanes, one row each, then spread over all banks).  With the whole shared window in use the
+    // L1 that is left (about 24 KB) cannot hold them, and under a saturated memory system every batch of row
+    // loads from L2 took a microsecond or two: an item's preparation took 10-20 us, more than streaming it.
+    // head_dim 128 has no room for 2 x 64 KB and keeps reading the rows from L2.
+    static constexpr bool ROT_SMEM = D == 64;
+    static constexpr int ROT_STRIDE = D + 4;
+    static constexpr int ROT_BYTES = ROT_SMEM ? D * ROT_STRIDE * 4 : 0;      // one matrix
+    static constexpr int OFF_ROT = OFF_QFRAG + QSLOTS * QFRAG;
+    static constexpr int MISC_FIXED = OFF_ROT + 2 * ROT_BYTES;
     static constexpr int MISC = SMALL_K + SMALL_V + MISC_FIXED;
     static constexpr int BASE_MAX = 4096;                           // assumed upper bound of the window offset
     static constexpr int SLOTS_A = NALIGNED ? (65536 - BASE_MAX) / STAGE : 0;
@@ -294,6 +306,7 @@ struct PrepScratch {
     uint32_t qvec_addr, unit_addr;   //         shared addresses of qvec and unit
     uint8_t* codes;                  // [2][D]
     float* nrm;                      // [2]
+    uint32_t rot_addr;               //         shared address of R_k, R_v behind it (DecodeCfg::ROT_SMEM)
 };
 
 // Prepares one item with `nthreads` threads (`tid` = 0..nthreads-1): one warp (barriers are __syncwarp), or a
@@ -317,7 +330,9 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
         if (ONE_WARP) __syncwarp();
         else asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
     };
+    using C = DecodeCfg<D, KB, VB>;
     const int64_t q0 = ((int64_t)b * p.q_heads + h * p.group) * D;
+    const float fold = p.scale * LOG2E;
     for (int e = 4 * tid; e < p.group * D; e += 4 * nthreads)      // the unit's queries -> float32 in shared memory
         *reinterpret_cast<float4*>(sc.qvec + e) = load_in4(p.query, p.in_dtype, q0 + e);
     if (append) {
@@ -341,14 +356,14 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
     sync();
     // One thread per ROW of a rotation matrix: row j of R_k serves the unit's `group` queries and its new key
     // (the row is fetched once for all of them), row j of R_v the new value.  A row is fetched in batches of
-    // eight 128-bit loads that are all in flight together; the loads ask L1 to keep the lines (evict-last):
-    // under a saturated memory system a round trip to L2 takes microseconds, and R_k is re-read for every
-    // item.  The sums run over k ascending.
-    const float fold = p.scale * LOG2E;
+    // eight 128-bit loads that are all in flight together -- from shared memory at head_dim 64, else from
+    // global memory with a request to L1 to keep the lines (evict-last): under a saturated memory system a
+    // round trip to L2 takes microseconds, and R_k is re-read for every item.  The sums run over k ascending.
     const int ntasks = append ? 2 * D : D;
     for (int task = tid; task < ntasks; task += nthreads) {
         const int which = task / D, j = task - which * D;           // 0: R_k row (queries, key), 1: R_v row (value)
         const float4* row = reinterpret_cast<const float4*>((which ? p.rot_v : p.rot_k) + (int64_t)j * D);
+        const uint32_t srow = sc.rot_addr + which * C::ROT_BYTES + j * C::ROT_STRIDE * 4;   // (head_dim 64: the row in shared memory)
         float aq[8], ax = 0.0f;
 #pragma unroll
         for (int n = 0; n < 8; n++) aq[n] = 0.0f;
@@ -356,7 +371,7 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
         for (int kb = 0; kb < D / 4; kb += 8) {
             float4 r[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = ldg_keep(row + kb + i);
+            for (int i = 0; i < 8; i++) r[i] = C::ROT_SMEM ? lds128f(srow + (kb + i) * 16) : ldg_keep(row + kb + i);
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const int k0 = 4 * (kb + i);
@@ -542,7 +557,8 @@ __device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t re
 // partials were written by other warps, possibly of other CTAs, before they bumped the unit's arrival
 // counter: they are read past L1 (ld.global.cg).
 template <int D>
-__device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int n, int nparts, int lane) {
+__device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int n, int nparts, int lane,
+                                           const float* rot_v, int rot_stride) {
     constexpr int NQ = D / 32;
     const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
     const int64_t pbase = (int64_t)unit * p.nchunks * (D == 64 ? 16 : 8) * p.group + n;
@@ -617,9 +633,9 @@ __device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int 
             float r[16][NQ];
 #pragma unroll
             for (int jj = 0; jj < 16; jj++) {
-                const float* row = p.rot_v + (int64_t)(32 * ij + jb + jj) * D + lane;
+                const float* row = rot_v + (int64_t)(32 * ij + jb + jj) * rot_stride + lane;
 #pragma unroll
-                for (int i = 0; i < NQ; i++) r[jj][i] = __ldg(row + 32 * i);
+                for (int i = 0; i < NQ; i++) r[jj][i] = row[32 * i];
             }
 #pragma unroll
             for (int jj = 0; jj < 16; jj++) {
@@ -670,8 +686,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     const uint32_t qfull_addr = misc + C::OFF_QBARS;             // qfull[q]: the item's query fragments are in slot q
     const uint32_t qempty_addr = qfull_addr + 8 * QSLOTS;        // qempty[q]: every consumer warp has taken them
     const uint32_t done_addr = qempty_addr + 8 * QSLOTS;         // done[d]: every consumer warp has stored its partial of the item
-    const uint32_t hdone_addr = done_addr + 8 * DSLOTS;          // the helper warp has announced all of the CTA's items
     const uint32_t qfrag_addr = misc + C::OFF_QFRAG;
+    const uint32_t rot_addr = misc + C::OFF_ROT;
     ringB = (misc + C::MISC_FIXED + 127u) & ~127u;
     const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
     if (slotsA + slotsB < NS) {                      // cannot happen unless the window offset is unusually large
@@ -682,7 +698,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
-    // [0] units queued for the tail phase  [1] this CTA leaves last  [4..] the queued units
+    // [1] this CTA leaves last
     volatile int* const todo = reinterpret_cast<volatile int*>(smem_gen + misc + C::OFF_TODO);
     PrepScratch scratch;
     scratch.bnd = reinterpret_cast<const float*>(smem_gen + misc + C::OFF_BND);
@@ -692,6 +708,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     scratch.unit_addr = misc + C::OFF_UNIT;
     scratch.codes = smem_gen + misc + C::OFF_CODES;
     scratch.nrm = reinterpret_cast<float*>(smem_gen + misc + C::OFF_NRM);
+    scratch.rot_addr = rot_addr;
     pdl_trigger();
 
     // ---- constants: centroids, boundaries, barriers, empty query slots ----
@@ -714,9 +731,17 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         mbar_init(qempty_addr + threadIdx.x * 8, WARPS);
     }
     if (threadIdx.x < DSLOTS) mbar_init(done_addr + threadIdx.x * 8, WARPS);
-    if (threadIdx.x == 0) { mbar_init(hdone_addr, 1); todo[0] = 0; todo[1] = 0; }
+    if (threadIdx.x == 0) { todo[0] = 0; todo[1] = 0; }
     for (int i = threadIdx.x; i < QSLOTS * C::QFRAG / 4; i += blockDim.x)
         reinterpret_cast<uint32_t*>(smem_gen + qfrag_addr)[i] = 0u;
+    if (C::ROT_SMEM) {                               // (constants: no wait for the previous launch needed)
+        constexpr int V4 = D / 4;                    // float4 per row
+        for (int e = threadIdx.x; e < 2 * D * V4; e += blockDim.x) {
+            const int which = e / (D * V4), rem = e - which * D * V4, j = rem / V4, c = rem - j * V4;
+            const float4 v = __ldg(reinterpret_cast<const float4*>(which ? p.rot_v : p.rot_k) + rem);
+            *reinterpret_cast<float4*>(smem_gen + rot_addr + which * C::ROT_BYTES + (j * C::ROT_STRIDE + 4 * c) * 4) = v;
+        }
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
 
@@ -746,44 +771,52 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
             prepare_item<D, KB, VB, false>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
                                            reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch, tid, nthreads);
     };
-    const bool prep_group = PREP_WARPS > 0 && warp < PREP_WARPS;
-    if (prep_group) {
+    // Roles of the prologue.  The PRODUCER loads the lengths (everybody's cursor needs them) and starts
+    // streaming at once: records depend neither on the tables nor on the queries, so the ring fills while
+    // the others work.  The first PREP_WARPS warps (all but the producer when PREP_WARPS == 0) prepare the
+    // CTA's first item; the rest builds the lookup tables, which depend on constants only and so come
+    // before the wait for the previous launch.  Consumers and helper meet on barrier 4 before the stream is
+    // consumed; the producer is not held up by it.
+    const bool prep_group = PREP_WARPS > 0 ? warp < PREP_WARPS : warp != WARPS;
+    constexpr int NPREP = PREP_WARPS > 0 ? PREP_WARPS : WARPS + 1;
+    if (warp == WARPS) {
         pdl_wait();
-        load_lens(threadIdx.x, PREP_WARPS * 32);
-        asm volatile("bar.sync 2, %0;" ::"n"(PREP_WARPS > 0 ? PREP_WARPS * 32 : 32) : "memory");
-        first_item(threadIdx.x, PREP_WARPS * 32);
+        load_lens(lane, 32);
+        __syncwarp();
+        asm volatile("bar.arrive 3, %0;" ::"n"((NPREP + 1) * 32) : "memory");   // the lengths are in shared memory
+        cur.start(p, lens);
     } else {
-        const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
-        constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
-        constexpr int TW = WARPS + 2 - PREP_WARPS;                 // warps that build the tables
-        for (int x = warp - PREP_WARPS; x < C::LUTK_ENTRIES; x += TW) {
-            int clo, chi;
-            tl_key_field_codes((uint32_t)x, KB, clo, chi);
-            *reinterpret_cast<uint32_t*>(smem_gen + tabK_base + x * KSTR + lane * 4) = pack_half2(cf[clo], cf[chi]);
-        }
-        for (int x = warp - PREP_WARPS; x < C::LUTV_ENTRIES; x += TW) {
-            if (C::VQUAD) {
-                int ag, bg, ag8, bg8;
-                tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
-                *reinterpret_cast<uint2*>(smem_gen + tabV_base + x * VSTR + (lane & 15) * 8) =
-                    make_uint2(pack_half2(cf[16 + ag], cf[16 + bg]), pack_half2(cf[16 + ag8], cf[16 + bg8]));
-            } else {
-                int ca, cb;
-                tl_val_pair_codes((uint32_t)x, VB, ca, cb);
-                *reinterpret_cast<uint32_t*>(smem_gen + tabV_base + x * VSTR + lane * 4) = pack_half2(cf[16 + ca], cf[16 + cb]);
+        if (PREP_WARPS == 0 || !prep_group) {
+            const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
+            constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
+            constexpr int TW = WARPS + 1 - PREP_WARPS;                 // warps that build the tables
+            const int tw = (warp > WARPS ? WARPS : warp) - PREP_WARPS;
+            for (int x = tw; x < C::LUTK_ENTRIES; x += TW) {
+                int clo, chi;
+                tl_key_field_codes((uint32_t)x, KB, clo, chi);
+                *reinterpret_cast<uint32_t*>(smem_gen + tabK_base + x * KSTR + lane * 4) = pack_half2(cf[clo], cf[chi]);
+            }
+            for (int x = tw; x < C::LUTV_ENTRIES; x += TW) {
+                if (C::VQUAD) {
+                    int ag, bg, ag8, bg8;
+                    tl_val_quad_codes((uint32_t)x, ag, bg, ag8, bg8);
+                    *reinterpret_cast<uint2*>(smem_gen + tabV_base + x * VSTR + (lane & 15) * 8) =
+                        make_uint2(pack_half2(cf[16 + ag], cf[16 + bg]), pack_half2(cf[16 + ag8], cf[16 + bg8]));
+                } else {
+                    int ca, cb;
+                    tl_val_pair_codes((uint32_t)x, VB, ca, cb);
+                    *reinterpret_cast<uint32_t*>(smem_gen + tabV_base + x * VSTR + lane * 4) = pack_half2(cf[16 + ca], cf[16 + cb]);
+                }
             }
         }
         // everything above depends on constants only; from here on the caller's tensors and the workspace are used
         pdl_wait();
-    }
-    __syncthreads();
-    if (PREP_WARPS == 0) {                            // all warps together, one phase after the other
-        load_lens(threadIdx.x, blockDim.x);
-        __syncthreads();
-        first_item(threadIdx.x, blockDim.x);
-        __syncthreads();
-    } else if (!prep_group) {
-        cur.start(p, lens);
+        if (prep_group) {
+            asm volatile("bar.sync 3, %0;" ::"n"((NPREP + 1) * 32) : "memory");
+            first_item(warp > WARPS ? (int)threadIdx.x - 32 : (int)threadIdx.x, NPREP * 32);
+        }
+        asm volatile("bar.sync 4, %0;" ::"n"((WARPS + 1) * 32) : "memory");
+        if (!prep_group) cur.start(p, lens);
     }
     if (threadIdx.x == 0 && cur.valid())
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
@@ -812,8 +845,9 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                 if (lane == 0) ok = mbar_wait(empty_addr + 8 * s, ((n / NS) - 1) & 1);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
-            if (ok && cur.valid() && cur.append && cur.stage_idx == 0) {
-                // the new token of this item's unit must be in the record store before its record is copied
+            if (ok && cur.valid() && cur.append && cur.tiles_left <= SR) {
+                // the new token of this item's unit (its last position) must be in the record store before the
+                // stage that holds its record is copied; the item's earlier stages do not wait for it
                 if (lane == 0) ok = mbar_wait(qfull_addr + 8 * (cur.seq % QSLOTS), (cur.seq / QSLOTS) & 1);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
@@ -862,31 +896,17 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     } else if (warp == WARPS + 1) {
         // ---- helper warp: prepares the CTA's second, third, ... item while earlier ones stream, and speaks
         // for the CTA's consumer warps: once all of them have stored their partial of an item (done barrier)
-        // it bumps the unit's arrival counter with one fence for the lot.  The helper that completes a unit
-        // (one arrival per chunk) owns its merge and queues it for its CTA's tail phase.  No warp ever waits
-        // for another CTA.
+        // it counts the chunk into the unit's arrival counter, with one fence for the lot.  The merges wait
+        // for these counters in the tail phase.
         StageCursor<SR, GROUPS> told = cur;            // the next item to announce
         bool ok = true;
         auto announce = [&]() {
             if (lane == 0) ok = mbar_wait(done_addr + 8 * (told.seq % DSLOTS), (told.seq / DSLOTS) & 1);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) return;
-            int merge_here = 0;
-            const int u = told.unit;
-            const int S = lens.get(p, told.b) & LEN_MASK;
             if (lane == 0) {
                 __threadfence();                                  // the consumers' partials before the count
-                if (atomicAdd(p.unit_cnt + u, 1) + 1 == (S + p.chunk - 1) / p.chunk) {
-                    atomicExch(p.unit_cnt + u, 0);                // clean for the next call
-                    __threadfence();                              // (acquire side: the partials are read after this)
-                    const int slot = todo[0];
-                    if (slot < TODO_MAX) { todo[4 + slot] = u; todo[0] = slot + 1; }
-                    else merge_here = 1;                          // queue full: merge right here
-                }
-            }
-            if (__shfl_sync(0xffffffffu, merge_here, 0)) {
-                const int nparts = min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS);
-                for (int nh = 0; nh < p.group; nh++) merge_head<D>(p, u, nh, nparts, lane);
+                atomicAdd(p.unit_cnt + told.unit, 1);
             }
             told.next_item(p, lens);
         };
@@ -910,8 +930,6 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         }
         while (ok && told.valid()) announce();
         if (!ok && lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(hdone_addr) : "memory");
     } else {
     // ---- consumers: group (warp / WPG) takes every GROUPS-th stage; its warp i takes records RPW*i .. RPW*i+RPW-1 ----
     WarpState<C::MT> st;
@@ -1003,34 +1021,48 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         }
     }
 
-    // ---- tail phase: the consumer warps merge the units this CTA's helper warp completed ----
+    // ---- tail phase: the merges of all units, dealt to the consumer warps of all CTAs ----
+    // Task (unit, query head) number t goes to CTA t % grid, warp (t / grid) % WARPS: the CTAs finish their
+    // streams at about the same time, so every warp gets at most a task or two whichever CTA streamed the
+    // unit's chunks.  A warp waits (bounded) until the unit's chunks have all been counted in.
     {
-        bool ok = true;                               // every item of this CTA has been announced, the queue is final
-        if (lane == 0) ok = mbar_wait(hdone_addr, 0);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok && lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED);
-    }
-    {
-        const int queued = __shfl_sync(0xffffffffu, (int)todo[0], 0);
-        for (int task = warp; task < queued * p.group; task += WARPS) {
-            const int u = __shfl_sync(0xffffffffu, (int)todo[4 + task / p.group], 0), nh = task % p.group;
+        const int tasks = p.batch * p.kv_heads * p.group;
+        bool ok = true;
+        for (int task = (int)blockIdx.x + (int)gridDim.x * warp; task < tasks && ok; task += (int)gridDim.x * WARPS) {
+            const int u = task / p.group, nh = task - u * p.group;
             const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
-            merge_head<D>(p, u, nh, min(((S + p.chunk - 1) / p.chunk) * WARPS, MERGE_MAX_CHUNKS), lane);
+            if (S == 0) continue;                             // (CTA 0 zeroed the outputs of empty sequences)
+            const int need = (S + p.chunk - 1) / p.chunk;
+            if (lane == 0) {
+                const unsigned long long t0 = wall_ns();
+                int seen;
+                for (;;) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.unit_cnt + u) : "memory");
+                    if (seen >= need) break;
+                    if (wall_ns() - t0 > WAIT_LIMIT_NS) { ok = false; break; }
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED); break; }
+            merge_head<D>(p, u, nh, min(need * WARPS, MERGE_MAX_CHUNKS), lane,
+                          C::ROT_SMEM ? reinterpret_cast<const float*>(smem_gen + rot_addr + C::ROT_BYTES) : p.rot_v,
+                          C::ROT_SMEM ? C::ROT_STRIDE : D);
         }
     }
     }   // consumers
 
-    // ---- the CTA that leaves last publishes the new lengths of a fused step ----
-    if (p.step) {
-        __syncthreads();                              // every role of this CTA is done (no read of the lengths after this)
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const int last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
-            if (last) atomicExch(p.done, 0);
-            todo[1] = last;
-        }
-        __syncthreads();
-        if (todo[1]) {
+    // ---- the CTA that leaves last clears the arrival counters and publishes the new lengths of a fused step ----
+    __syncthreads();                                  // every role of this CTA is done (no read of lengths or counters after this)
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
+        if (last) atomicExch(p.done, 0);
+        todo[1] = last;
+    }
+    __syncthreads();
+    if (todo[1]) {
+        for (int i = threadIdx.x; i < p.batch * p.kv_heads; i += blockDim.x) p.unit_cnt[i] = 0;
+        if (p.step) {
             for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
                 int flag;
                 const int e = encode_len(p, __ldcg(p.lens_in + i), flag);
@@ -1044,19 +1076,23 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Tokens per (unit, chunk) work item of the streaming kernel.  Work items are dealt round-robin to the
-// CTAs (one per SM); small enough that every CTA gets several items, large enough that the per-item
-// partials (consumer warps x group x (D+2) floats) stay a few percent of the streamed bytes.  Every item
-// yields one partial per consumer warp, and the merge handles at most MERGE_MAX_CHUNKS per unit.
+// Tokens per (unit, chunk) work item of the streaming kernel.  Items are dealt round-robin to the CTAs (one
+// per SM).  The estimate of a CTA's load, in tokens: its share of the units' full chunks, each with a fixed
+// cost for switching items (partials, fragments), plus its share of the units' last, shorter chunks, taking
+// every sequence at the host's bound max_len.  Small chunks balance the CTAs, large ones keep the partials
+// (consumer warps x group x (D+2) floats per item) and the merge small; the merge handles at most
+// MERGE_MAX_CHUNKS partials per unit.
 static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets) {
+    const double item_cost = 2048.0;      // measured: an extra item costs a CTA about 5 us, the time of 2,000 tokens
     int best = 0;
     double best_cost = 1e300;
     for (int64_t L = stage_tokens; L <= (int64_t)1 << 30; L *= 2) {
         const int64_t nch = (max_len + L - 1) / L;
         if (nch * sets <= MERGE_MAX_CHUNKS) {
-            const int64_t rounds = (units * nch + ctas - 1) / ctas;
-            const double cost = (double)rounds * ((double)std::min<int64_t>(L, max_len) + stage_tokens);
-            if (cost <= best_cost) { best_cost = cost; best = (int)L; }
+            const int64_t full = nch - 1, rest = max_len - full * L;
+            const double cost = (double)((units * full + ctas - 1) / ctas) * ((double)L + item_cost) +
+                                (double)((units + ctas - 1) / ctas) * ((double)rest + item_cost);
+            if (cost < best_cost) { best_cost = cost; best = (int)L; }
         }
         if (L >= max_len && best) break;
     }
