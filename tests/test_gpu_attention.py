@@ -202,6 +202,34 @@ def test_fused_step_equals_append_then_attend(dim, kb, vb, kv_heads, group, dtyp
             one.decode_step(0, q, k[:, :, 0], v[:, :, 0])
 
 
+@pytest.mark.parametrize("dim,kv_heads,group,batch,ctx", [(64, 8, 4, 60, 12000), (128, 8, 4, 60, 6000)])
+def test_fused_step_with_several_long_items_per_cta(dim, kv_heads, group, batch, ctx):
+    """More than three units per SM, each streamed in many pipeline stages, every one of them receiving a new
+    token: the helper warp runs up to two items ahead of the point where the producer needs a unit's new token
+    in the store (before the unit's LAST stage).  The step must store the same bytes and return the same
+    attention as append + decode_attention, with no bounded wait expiring."""
+    from turboquant_kv import QuantizedKVCache, TurboQuantConfig
+
+    steps = 3
+    k, v = _fill(batch, kv_heads, ctx + steps, dim, seed=23)
+    k, v = k.cuda().bfloat16(), v.cuda().bfloat16()
+    cfg = TurboQuantConfig(key_bits=4, value_bits=2 if dim == 64 else 3, seed=42)
+    cap = ctx + 16
+    two = QuantizedKVCache(cfg, 1, cap, kv_heads, dim, device="cuda", batch_size=batch)
+    one = QuantizedKVCache(cfg, 1, cap, kv_heads, dim, device="cuda", batch_size=batch)
+    for c in (two, one):
+        c.append(0, k[:, :, :ctx], v[:, :, :ctx])
+    gen = torch.Generator().manual_seed(6)
+    for step in range(ctx, ctx + steps):
+        q = torch.randn(batch, kv_heads * group, dim, generator=gen).cuda().bfloat16()
+        two.append(0, k[:, :, step:step + 1], v[:, :, step:step + 1])
+        ref = two.decode_attention(0, q)
+        out = one.decode_step(0, q, k[:, :, step], v[:, :, step])
+        assert one.decode_status() == 0 and two.decode_status() == 0
+        assert torch.equal(one._store[0], two._store[0]), "fused step stored different record bytes"
+        assert torch.equal(out, ref)
+
+
 def test_fused_step_replays_in_a_cuda_graph(orc):
     """A captured step keeps appending at the device-side position when the graph is replayed."""
     from turboquant_kv import QuantizedKVCache, TurboQuantConfig

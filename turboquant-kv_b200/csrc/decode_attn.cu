@@ -320,9 +320,13 @@ struct PrepScratch {
 // elements and a butterfly, unit = x / max(norm, 1e-10), y_j as one fused-multiply-add chain over k ascending,
 // code = number of boundaries below y_j), so the stored codes are those tqb_kv_append would store.
 // The stores are followed by a proxy fence: the producer copies that record with the TMA engine.
-template <int D, int KB, int VB, bool ONE_WARP>
-__device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bool append, int pos,
+template <int D, int KB, int VB, bool ONE_WARP, bool DO_Q = true, bool DO_KV = true>
+__device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bool append_item, int pos,
                                              uint16_t* qslot, const PrepScratch& sc, int tid, int nthreads) {
+    // DO_Q: the query fragments.  DO_KV: the new token of a fused step.  The two halves can be done by
+    // different warps at the same time (they share no scratch), or one after the other.
+    const bool append = DO_KV && append_item;
+    if (!DO_Q && !append) return;
     constexpr int NQ = D / 32;
     const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
     const int warp = tid >> 5, lane = tid & 31;
@@ -333,8 +337,9 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
     using C = DecodeCfg<D, KB, VB>;
     const int64_t q0 = ((int64_t)b * p.q_heads + h * p.group) * D;
     const float fold = p.scale * LOG2E;
-    for (int e = 4 * tid; e < p.group * D; e += 4 * nthreads)      // the unit's queries -> float32 in shared memory
-        *reinterpret_cast<float4*>(sc.qvec + e) = load_in4(p.query, p.in_dtype, q0 + e);
+    if (DO_Q)
+        for (int e = 4 * tid; e < p.group * D; e += 4 * nthreads)  // the unit's queries -> float32 in shared memory
+            *reinterpret_cast<float4*>(sc.qvec + e) = load_in4(p.query, p.in_dtype, q0 + e);
     if (append) {
         // norm and unit vector of the key (which = 0) and the value (1): one warp each, or one after the other
         for (int which = ONE_WARP ? 0 : warp; which < 2; which += ONE_WARP ? 1 : 2) {
@@ -375,7 +380,7 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const int k0 = 4 * (kb + i);
-                if (which == 0) {
+                if (DO_Q && which == 0) {
 #pragma unroll
                     for (int n = 0; n < 8; n++) {
                         if (n < p.group) {
@@ -396,7 +401,7 @@ __device__ __forceinline__ void prepare_item(const DecodeParams& p, int unit, bo
                 }
             }
         }
-        if (which == 0) {
+        if (DO_Q && which == 0) {
             const int ks = j >> 4, half = (j >> 3) & 1, t = (j & 7) >> 1, hi = j & 1;
 #pragma unroll
             for (int n = 0; n < 8; n++)
@@ -698,7 +703,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         return slot < slotsA ? ringA + slot * C::STAGE : ringB + (slot - slotsA) * C::STAGE;
     };
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
-    // [1] this CTA leaves last
+    // [1] this CTA leaves last  [2] items of this CTA whose new token (if any) has been stored
     volatile int* const todo = reinterpret_cast<volatile int*>(smem_gen + misc + C::OFF_TODO);
     PrepScratch scratch;
     scratch.bnd = reinterpret_cast<const float*>(smem_gen + misc + C::OFF_BND);
@@ -731,7 +736,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         mbar_init(qempty_addr + threadIdx.x * 8, WARPS);
     }
     if (threadIdx.x < DSLOTS) mbar_init(done_addr + threadIdx.x * 8, WARPS);
-    if (threadIdx.x == 0) { todo[0] = 0; todo[1] = 0; }
+    if (threadIdx.x == 0) { todo[0] = 0; todo[1] = 0; todo[2] = 0; }
     for (int i = threadIdx.x; i < QSLOTS * C::QFRAG / 4; i += blockDim.x)
         reinterpret_cast<uint32_t*>(smem_gen + qfrag_addr)[i] = 0u;
     if (C::ROT_SMEM) {                               // (constants: no wait for the previous launch needed)
@@ -768,8 +773,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     auto first_item = [&](int tid, int nthreads) {   // (every thread of the preparing group takes the same path)
         cur.start(p, lens);
         if (cur.valid())
-            prepare_item<D, KB, VB, false>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
-                                           reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch, tid, nthreads);
+            prepare_item<D, KB, VB, false, true, PREP_WARPS == 0>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                                                 reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch, tid, nthreads);
     };
     // Roles of the prologue.  The PRODUCER loads the lengths (everybody's cursor needs them) and starts
     // streaming at once: records depend neither on the tables nor on the queries, so the ring fills while
@@ -777,20 +782,35 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     // CTA's first item; the rest builds the lookup tables, which depend on constants only and so come
     // before the wait for the previous launch.  Consumers and helper meet on barrier 4 before the stream is
     // consumed; the producer is not held up by it.
-    const bool prep_group = PREP_WARPS > 0 ? warp < PREP_WARPS : warp != WARPS;
-    constexpr int NPREP = PREP_WARPS > 0 ? PREP_WARPS : WARPS + 1;
+    // SPLIT (head_dim 64): four consumer warps rotate the first item's queries, the helper warp stores its new
+    // token at the same time, the other consumer warps build the tables.  Otherwise all warps but the
+    // producer build the tables, then prepare the first item together.
+    constexpr bool SPLIT = PREP_WARPS > 0;
+    const bool prep_group = SPLIT ? warp < PREP_WARPS : warp != WARPS;
+    constexpr int NPREP = SPLIT ? PREP_WARPS : WARPS + 1;
+    constexpr int COUNT3 = (1 + NPREP + (SPLIT ? 1 : 0)) * 32;         // producer (arrives), preparing warps, helper
+    constexpr int COUNT4 = (SPLIT ? WARPS : WARPS + 1) * 32;           // the warps that wait for tables and fragments
     if (warp == WARPS) {
         pdl_wait();
         load_lens(lane, 32);
         __syncwarp();
-        asm volatile("bar.arrive 3, %0;" ::"n"((NPREP + 1) * 32) : "memory");   // the lengths are in shared memory
+        asm volatile("bar.arrive 3, %0;" ::"n"(COUNT3) : "memory");   // the lengths are in shared memory
         cur.start(p, lens);
+    } else if (SPLIT && warp == WARPS + 1) {
+        pdl_wait();
+        asm volatile("bar.sync 3, %0;" ::"n"(COUNT3) : "memory");
+        cur.start(p, lens);
+        if (cur.valid())
+            prepare_item<D, KB, VB, true, false, true>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
+                                                       reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr), scratch, lane, 32);
+        __syncwarp();
+        if (lane == 0) { __threadfence_block(); todo[2] = 1; }        // the first item's new token is in the store
     } else {
-        if (PREP_WARPS == 0 || !prep_group) {
+        if (!SPLIT || !prep_group) {
             const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
             constexpr int KSTR = C::KBYTE ? 256 : 128, VSTR = C::VBYTE ? 256 : 128;
-            constexpr int TW = WARPS + 1 - PREP_WARPS;                 // warps that build the tables
-            const int tw = (warp > WARPS ? WARPS : warp) - PREP_WARPS;
+            constexpr int TW = SPLIT ? WARPS - PREP_WARPS : WARPS + 1; // warps that build the tables
+            const int tw = SPLIT ? warp - PREP_WARPS : (warp > WARPS ? WARPS : warp);
             for (int x = tw; x < C::LUTK_ENTRIES; x += TW) {
                 int clo, chi;
                 tl_key_field_codes((uint32_t)x, KB, clo, chi);
@@ -812,14 +832,16 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         // everything above depends on constants only; from here on the caller's tensors and the workspace are used
         pdl_wait();
         if (prep_group) {
-            asm volatile("bar.sync 3, %0;" ::"n"((NPREP + 1) * 32) : "memory");
+            asm volatile("bar.sync 3, %0;" ::"n"(COUNT3) : "memory");
             first_item(warp > WARPS ? (int)threadIdx.x - 32 : (int)threadIdx.x, NPREP * 32);
         }
-        asm volatile("bar.sync 4, %0;" ::"n"((WARPS + 1) * 32) : "memory");
+        asm volatile("bar.sync 4, %0;" ::"n"(COUNT4) : "memory");
         if (!prep_group) cur.start(p, lens);
     }
-    if (threadIdx.x == 0 && cur.valid())
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
+    if (threadIdx.x == 0) {
+        if (!SPLIT) { __threadfence_block(); todo[2] = 1; }
+        if (cur.valid()) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr) : "memory");
+    }
     const uint32_t tabK = tabK_base + lane * 4;                    // for BYTE tables "+" is "|": the low 16 bits of the base are 0
     const uint32_t tabV = tabV_base + (C::VQUAD ? (lane & 15) * 8 : lane * 4);
 
@@ -847,8 +869,14 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
             }
             if (ok && cur.valid() && cur.append && cur.tiles_left <= SR) {
                 // the new token of this item's unit (its last position) must be in the record store before the
-                // stage that holds its record is copied; the item's earlier stages do not wait for it
-                if (lane == 0) ok = mbar_wait(qfull_addr + 8 * (cur.seq % QSLOTS), (cur.seq / QSLOTS) & 1);
+                // stage that holds its record is copied; the item's earlier stages do not wait for it.  (A
+                // counter, not a barrier: the helper may be two items ahead of this point.)
+                if (lane == 0) {
+                    const unsigned long long t0 = wall_ns();
+                    while (todo[2] <= cur.seq)
+                        if (wall_ns() - t0 > WAIT_LIMIT_NS) { ok = false; break; }
+                    __threadfence_block();
+                }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
             if (!ok) break;
@@ -919,10 +947,26 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
             }
-            prepare_item<D, KB, VB, true>(p, cur.unit, cur.append, (lens.get(p, cur.b) & LEN_MASK) - 1,
-                                          reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr + q * C::QFRAG), scratch, lane, 32);
+            uint16_t* const qdst = reinterpret_cast<uint16_t*>(smem_gen + qfrag_addr + q * C::QFRAG);
+            const int pos = (lens.get(p, cur.b) & LEN_MASK) - 1;
+            if (SPLIT) {
+                // queries first: the consumers can start on the item while its new token is being stored
+                if (cur.seq == 1) {                 // (the first item's queries were staged in the same scratch)
+                    if (lane == 0) ok = mbar_wait(qfull_addr, 0);
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                }
+                prepare_item<D, KB, VB, true, true, false>(p, cur.unit, cur.append, pos, qdst, scratch, lane, 32);
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr + 8 * q) : "memory");
+                prepare_item<D, KB, VB, true, false, true>(p, cur.unit, cur.append, pos, qdst, scratch, lane, 32);
+            } else {
+                prepare_item<D, KB, VB, true>(p, cur.unit, cur.append, pos, qdst, scratch, lane, 32);
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr + 8 * q) : "memory");
+            }
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_addr + 8 * q) : "memory");
+            if (lane == 0) { __threadfence_block(); todo[2] = cur.seq + 1; }
             // The item two behind the one just prepared was finished by the consumers before they could take
             // this slot's previous fragments, so its announcement never waits long; and because it comes before
             // the next item is handed over, the done barriers (DSLOTS in rotation) can never be lapped.
