@@ -183,7 +183,9 @@ int tqb_kv_import(uint8_t* store, int64_t n, int dim, int kbits, int vbits, cons
  * b * kv_heads + head, `max_seq` = token pitch of a unit (multiple of 16).  Paged cache: block_tables
  * (batch, max_blocks) int32 device, block_size a multiple of 16.
  *
- * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  One kernel launch per call.
+ * dim in {64, 128}, kbits / vbits in 2..4, group <= 8.  One kernel launch per call: a grid of at most one
+ * CTA per SM whose CTAs wait (bounded) for each other's partial results at the end, so it expects to be
+ * resident as a whole -- do not run it beside a kernel that occupies SMs for an unbounded time.
  *
  * workspace: device scratch of at least tqb_decode_attention_workspace_bytes(...) bytes, 256-byte
  * aligned, not shared between calls that may overlap on the device.  The caller ZEROES it once before

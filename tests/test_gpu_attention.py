@@ -230,6 +230,75 @@ def test_fused_step_with_several_long_items_per_cta(dim, kv_heads, group, batch,
         assert torch.equal(out, ref)
 
 
+def test_more_sequences_than_the_kernel_caches_lengths_for(orc):
+    """Beyond 256 sequences the kernel reads lengths from global memory and deals (unit, chunk) items round-robin
+    instead of cutting the flattened tile range into equal pieces: same results, ragged and empty sequences."""
+    from turboquant_kv.kvstore import PackedKVStore
+    from turboquant_kv import _native as N
+
+    batch, kv_heads, group, dim, pitch = 300, 2, 2, 64, 96
+    rng = np.random.default_rng(3)
+    lens = rng.integers(0, 90, size=batch).astype(np.int32)
+    lens[:3] = [0, 89, 16]
+    kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
+    store = kv.alloc(batch * kv_heads, pitch)
+    k, v = _fill(batch, kv_heads, pitch, dim, seed=41)
+    kv.append(store, k.cuda(), v.cuda(), N.RowMap(pitch, pitch, 1, 0, None, 1, None, 1))
+    q = torch.randn(batch, kv_heads * group, dim, generator=torch.Generator().manual_seed(4))
+    seq = torch.from_numpy(lens).cuda()
+    out = kv.decode_attention(store, q.cuda(), kv_heads, seq, int(lens.max()), pitch=pitch).cpu().numpy()
+    assert kv.status() == 0
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(2, dim)
+    kp, kn = orc.quantize_mse(k.reshape(-1, dim).numpy(), 4, rk, bk)
+    vp, vn = orc.quantize_mse(v.reshape(-1, dim).numpy(), 2, rv, bv)
+    ref = orc.decode_attention(q.numpy(), kp.reshape(batch, kv_heads, pitch, -1), kn.reshape(batch, kv_heads, pitch),
+                               vp.reshape(batch, kv_heads, pitch, -1), vn.reshape(batch, kv_heads, pitch), lens,
+                               rk, ck, 4, rv, cv, 2)
+    attention_close(out, ref)
+    assert not out[0].any()                                            # the empty sequence
+
+
+def test_many_long_ragged_sequences_take_equal_pieces_of_the_tile_range(orc):
+    """Several units per SM and long contexts: the CTAs then cut the flattened tile range of all units into equal
+    pieces (a unit's partials come from up to three CTAs).  Ragged lengths, empty sequences and lengths that
+    are no multiple of the tile, against dequantise-then-attend."""
+    from turboquant_kv.kvstore import PackedKVStore
+    from turboquant_kv import _native as N
+
+    batch, kv_heads, group, dim, pitch = 64, 8, 4, 64, 16016
+    rng = np.random.default_rng(9)
+    lens = rng.integers(10000, 16001, size=batch).astype(np.int32)
+    lens[[0, 5, 63]] = [0, 16000, 1]
+    kv = PackedKVStore(dim, 4, 2, 42, "dense_qr", "cuda")
+    store = kv.alloc(batch * kv_heads, pitch)
+    gen = torch.Generator(device="cuda").manual_seed(10)
+    keep = {}
+    for b in range(batch):                                               # one sequence at a time: (heads, tokens, dim)
+        k = torch.randn(kv_heads, pitch, dim, device="cuda", generator=gen)
+        v = torch.randn(kv_heads, pitch, dim, device="cuda", generator=gen)
+        k[:, :, 3] *= 20.0
+        kv.append(store, k, v, N.RowMap(pitch, pitch, 1, b * kv_heads * pitch, None, 1, None, 1))
+        if b in (1, 5, 63):
+            keep[b] = (k.cpu().numpy(), v.cpu().numpy())
+    q = torch.randn(batch, kv_heads * group, dim, generator=torch.Generator().manual_seed(4))
+    out = kv.decode_attention(store, q.cuda(), kv_heads, torch.from_numpy(lens).cuda(), 16000, pitch=pitch).cpu().numpy()
+    assert kv.status() == 0
+    assert not out[0].any()
+    rk, rv = orc.make_rotation_matrix(dim, 42), orc.make_rotation_matrix(dim, 43)
+    bk, ck = orc.lloyd_max_codebook(4, dim)
+    bv, cv = orc.lloyd_max_codebook(2, dim)
+    for b, (k, v) in keep.items():
+        l = int(lens[b])
+        kp, kn = orc.quantize_mse(k[:, :l].reshape(-1, dim), 4, rk, bk)
+        vp, vn = orc.quantize_mse(v[:, :l].reshape(-1, dim), 2, rv, bv)
+        ref = orc.decode_attention(q[b:b + 1].numpy(), kp.reshape(1, kv_heads, l, -1), kn.reshape(1, kv_heads, l),
+                                   vp.reshape(1, kv_heads, l, -1), vn.reshape(1, kv_heads, l), np.array([l], np.int32),
+                                   rk, ck, 4, rv, cv, 2)
+        attention_close(out[b:b + 1], ref)
+
+
 def test_fused_step_replays_in_a_cuda_graph(orc):
     """A captured step keeps appending at the device-side position when the graph is replayed."""
     from turboquant_kv import QuantizedKVCache, TurboQuantConfig

@@ -53,13 +53,11 @@ def test_head_sharded_cache_equals_the_unsharded_cache(orc, tp_size, ctx):
         assert shard.cache.decode_status() == 0
         assert shard.memory_bytes() * tp_size == whole.memory_bytes()
     got = torch.cat(parts, dim=1)
-    if ctx <= 512:
-        # one work item per (sequence, head) whatever the head count: the same partials merged in the same order
-        assert torch.equal(got, want), "a rank's heads must give bit-identical outputs to the unsharded cache"
-    else:
-        # longer contexts are split into chunks by the work per GPU, so the partials merge in another order
-        np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), atol=2e-2, rtol=0)
-        assert (got != want).float().mean() < 0.05                     # bf16 roundings that fell the other way
+    # the CTAs cut the flattened tile range of ALL units into equal pieces, so a shard (fewer units) splits its
+    # sequences at other places than the unsharded cache and the partials merge in another order: the outputs
+    # agree to bf16 rounding, not bit for bit
+    np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), atol=2e-2, rtol=0)
+    assert (got != want).float().mean() < 0.05                         # bf16 roundings that fell the other way
     # and both agree with dequantise-then-attend
     kp, kn, vp, vn = (t.cpu().numpy() for t in whole._export(0, ctx))
     shape = (batch, kv_heads, ctx)

@@ -70,6 +70,7 @@ struct DecodeParams {
     int64_t max_len;                 // host bound of the attended lengths: the work plan covers [0, max_len)
     int batch, q_heads, kv_heads, group, max_blocks, block_size;
     int chunk, nchunks;              // tokens per (unit, chunk) work item
+    int flat;                        // 1: the CTAs take equal pieces of the flattened tile range instead (see StageCursor)
     int step;                        // 1: append the new token of every unit first (tqb_decode_step)
     const void* query; const void* key; const void* value;
     int in_dtype; int64_t kv_stride;
@@ -87,6 +88,7 @@ struct DecodeParams {
 struct DecodeWorkspace {
     size_t off_status, off_cnt, off_m, off_l, off_acc, total;
     int chunk, nchunks;
+    int flat;                           // the CTAs take equal pieces of the flattened tile range
 };
 
 __device__ __forceinline__ float load_in(const void* base, int dtype, int64_t idx) {
@@ -202,7 +204,8 @@ struct DecodeCfg {
     static constexpr int OFF_BARS = 256, OFF_QBARS = OFF_BARS + 256, OFF_BND = OFF_QBARS + 128;
     static constexpr int OFF_UNIT = OFF_BND + 128, OFF_CODES = OFF_UNIT + 2 * D * 4, OFF_NRM = OFF_CODES + 2 * D;
     static constexpr int OFF_QVEC = OFF_NRM + 16, OFF_TODO = OFF_QVEC + 8 * D * 4, OFF_LENS = OFF_TODO + 16;
-    static constexpr int OFF_QFRAG = (OFF_LENS + LENS_MAX * 4 + 127) / 128 * 128;
+    static constexpr int OFF_TPRE = OFF_LENS + LENS_MAX * 4;        // flat partition: LENS_MAX + 1 prefix sums of tiles
+    static constexpr int OFF_QFRAG = (OFF_TPRE + (LENS_MAX + 1) * 4 + 127) / 128 * 128;
     // head_dim 64: both rotation matrices live in shared memory (rows ROT_STRIDE floats apart: the 128-bit
     // loads of 32 lanes, one row each, then spread over all banks).  With the whole shared window in use the
     // L1 that is left (about 24 KB) cannot hold them, and under a saturated memory system every batch of row
@@ -234,6 +237,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // batch fits, else recomputed from the caller's array.
 struct Lens {
     const int32_t* sm;               // null: not cached
+    const int32_t* tpre;             // flat partition: tpre[b] = 16-token tiles of all units of sequences < b; [batch] = total
     __device__ __forceinline__ int get(const DecodeParams& p, int b) const {
         if (sm) return sm[b];
         int flag;
@@ -241,31 +245,76 @@ struct Lens {
     }
 };
 
-// Position of a CTA in its stream of pipeline stages: items (unit, chunk) are dealt round-robin to CTAs;
-// an item is streamed in stages of up to SR records, which the consumer warps share (RPW records each).
-template <int SR, int GROUPS>
+// Position of a CTA in its stream of pipeline stages.  Two ways of dealing the work:
+//   chunks  items (unit, chunk of p.chunk tokens) are dealt round-robin to the CTAs; the host chose the chunk
+//           from its bound on the lengths.  Partials of an item go to slot unit * nchunks + chunk.
+//   flat    (p.flat) the tiles of all units, in unit order, form one range of T tiles (T from the lengths on
+//           the device); CTA c takes tiles [c Q, (c+1) Q), Q = ceil(T / grid): a piece of a unit, whole units,
+//           a piece of the next -- every CTA streams the same number of tokens whatever the number of units.
+//           An item is the part of one unit inside the CTA's range; the pieces of unit u lie in consecutive
+//           CTAs first(u) .. last(u), and the partials of (u, c) go to slot c + u (unique: first(u+1) >= last(u)).
+// An item is streamed in stages of up to SR records, which the consumer warps share (RPW records each).
+template <int SR, int GROUPS, bool FLAT>
 struct StageCursor {
     int item, total_items, stride;     // (the host checks that the item count fits 31 bits)
     int seq;                            // items of this CTA opened so far, minus one
     int tiles_left, tile0;              // tiles of the item not yet taken; index of the next one in its unit
-    int unit, b, h, chunk_idx, tok_end;
+    int unit, b, h, slot, tok_end;
     bool append;                        // this item holds the position a fused step writes its new token to
     int stage_idx, stages;              // position in the item; an item takes at least GROUPS stages (empty ones
                                         // if need be) so that every consumer group sees its start and its end
+    int gpos, gend;                     // flat: next global tile of this CTA, end of its range
+    __device__ __forceinline__ static int flat_quota(const DecodeParams& p, const Lens& lens) {
+        const int T = lens.tpre[p.batch];
+        return max(1, (T + (int)gridDim.x - 1) / (int)gridDim.x);
+    }
     __device__ __forceinline__ void start(const DecodeParams& p, const Lens& lens) {
-        item = blockIdx.x;
-        total_items = p.batch * p.kv_heads * p.nchunks;
-        stride = gridDim.x;
         seq = -1;
         tiles_left = 0;
+        if (FLAT) {
+            const int T = lens.tpre[p.batch], Q = flat_quota(p, lens);
+            const long long g0 = (long long)blockIdx.x * Q;
+            gpos = (int)min((long long)T, g0);
+            gend = (int)min((long long)T, g0 + Q);
+            total_items = 1;
+        } else {
+            item = blockIdx.x;
+            total_items = p.batch * p.kv_heads * p.nchunks;
+            stride = gridDim.x;
+        }
         open(p, lens);
     }
     __device__ __forceinline__ bool valid() const { return item < total_items; }
     __device__ __forceinline__ int tiles_here() const { return min(SR, tiles_left); }
     __device__ __forceinline__ void open(const DecodeParams& p, const Lens& lens) {
+        if (FLAT) {
+            item = 1;
+            if (gpos >= gend) return;
+            int lo = 0, hi = p.batch;                     // tpre[lo] <= gpos < tpre[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (lens.tpre[mid] <= gpos) lo = mid; else hi = mid;
+            }
+            b = lo;
+            const int e = lens.get(p, b);
+            const int S = e & LEN_MASK, tb = (S + TILE - 1) / TILE;      // (tb > 0: the sequence owns tile gpos)
+            const int off = gpos - lens.tpre[b];
+            h = off / tb;
+            tile0 = off - h * tb;
+            unit = b * p.kv_heads + h;
+            tiles_left = min(tb - tile0, gend - gpos);
+            tok_end = min(S, (tile0 + tiles_left) * TILE);
+            stage_idx = 0;
+            stages = max(GROUPS, (tiles_left + SR - 1) / SR);
+            append = (e & LEN_ROOM) && tile0 + tiles_left == tb;
+            slot = (int)blockIdx.x + unit;
+            item = 0;
+            seq++;
+            return;
+        } else {
         while (item < total_items) {
             unit = item / p.nchunks;
-            chunk_idx = item - unit * p.nchunks;
+            const int chunk_idx = item - unit * p.nchunks;
             b = unit / p.kv_heads;
             h = unit - b * p.kv_heads;
             const int e = lens.get(p, b);
@@ -278,22 +327,44 @@ struct StageCursor {
                 stage_idx = 0;
                 stages = max(GROUPS, (tiles_left + SR - 1) / SR);
                 append = (e & LEN_ROOM) && (S - 1) / p.chunk == chunk_idx;
+                slot = item;
                 seq++;
                 return;
             }
             item += stride;
         }
+        }
     }
     __device__ __forceinline__ void next(const DecodeParams& p, const Lens& lens) {
         const int n = tiles_here();
         tiles_left -= n; tile0 += n; stage_idx++;
-        if (stage_idx == stages) { item += stride; open(p, lens); }
+        if (FLAT) gpos += n;
+        if (stage_idx == stages) {
+            if (!FLAT) item += stride;
+            open(p, lens);
+        }
     }
     __device__ __forceinline__ void next_item(const DecodeParams& p, const Lens& lens) {
-        item += stride;
+        if (FLAT) gpos += tiles_left; else item += stride;
         open(p, lens);
     }
 };
+
+// Where the partials of a unit lie and how many items (arrivals) make it complete.
+template <bool FLAT>
+__device__ __forceinline__ void unit_pieces(const DecodeParams& p, const Lens& lens, int unit, int S, int& slot0, int& need) {
+    if (FLAT) {
+        const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
+        const int tb = (S + TILE - 1) / TILE, Q = StageCursor<1, 1, true>::flat_quota(p, lens);
+        const int a = lens.tpre[b] + h * tb;
+        const int first = a / Q, last = (a + tb - 1) / Q;
+        slot0 = first + unit;
+        need = last - first + 1;
+    } else {
+        slot0 = unit * p.nchunks;
+        need = (S + p.chunk - 1) / p.chunk;
+    }
+}
 
 // =================================================================================================
 // item preparation: query fragments, and the new token of a fused step
@@ -562,11 +633,11 @@ __device__ __forceinline__ void process_tiles(WarpState<D / 16>& st, uint32_t re
 // partials were written by other warps, possibly of other CTAs, before they bumped the unit's arrival
 // counter: they are read past L1 (ld.global.cg).
 template <int D>
-__device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int n, int nparts, int lane,
+__device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int slot0, int n, int nparts, int lane,
                                            const float* rot_v, int rot_stride) {
     constexpr int NQ = D / 32;
     const int b = unit / p.kv_heads, h = unit - b * p.kv_heads;
-    const int64_t pbase = (int64_t)unit * p.nchunks * (D == 64 ? 16 : 8) * p.group + n;
+    const int64_t pbase = (int64_t)slot0 * (D == 64 ? 16 : 8) * p.group + n;
     // The kernel is a chain of round trips to L2; every phase keeps as many loads in flight as it can.
     float M = NEG_INF;
     for (int c0 = 0; c0 < nparts; c0 += 128) {
@@ -658,7 +729,7 @@ __device__ __forceinline__ void merge_head(const DecodeParams& p, int unit, int 
 // =================================================================================================
 // the kernel
 // =================================================================================================
-template <int D, int KB, int VB, bool PAGED>
+template <int D, int KB, int VB, bool PAGED, bool FLAT>
 __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KB, VB>;
     constexpr int WARPS = C::WARPS, NS = C::NS, SR = C::SR, RPW = C::RPW, GROUPS = C::GROUPS, WPG = C::WPG;
@@ -755,7 +826,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     const bool lens_in_smem = p.batch <= C::LENS_MAX;
     Lens lens;
     lens.sm = lens_in_smem ? reinterpret_cast<const int32_t*>(smem_gen + misc + C::OFF_LENS) : nullptr;
-    StageCursor<SR, GROUPS> cur;
+    lens.tpre = reinterpret_cast<const int32_t*>(smem_gen + misc + C::OFF_TPRE);
+    StageCursor<SR, GROUPS, FLAT> cur;
     // lengths clamped to what the host announced; CTA 0 reports and clears the outputs of empty sequences
     auto load_lens = [&](int tid, int nthreads) {
         if (!lens_in_smem && blockIdx.x != 0) return;
@@ -794,6 +866,29 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         pdl_wait();
         load_lens(lane, 32);
         __syncwarp();
+        if (FLAT) {
+            // exclusive prefix sums of the units' tiles per sequence (p.flat implies batch <= LENS_MAX): each
+            // lane takes a run of sequences, the runs are scanned across the warp
+            int32_t* tpre = reinterpret_cast<int32_t*>(smem_gen + misc + C::OFF_TPRE);
+            const int per = (p.batch + 31) / 32, b0 = lane * per;
+            int run = 0;
+            for (int i = 0; i < per; i++)
+                if (b0 + i < p.batch) run += p.kv_heads * (((lens.sm[b0 + i] & LEN_MASK) + TILE - 1) / TILE);
+            int incl = run;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            int acc = incl - run;
+            for (int i = 0; i < per; i++)
+                if (b0 + i < p.batch) {
+                    tpre[b0 + i] = acc;
+                    acc += p.kv_heads * (((lens.sm[b0 + i] & LEN_MASK) + TILE - 1) / TILE);
+                }
+            if (lane == 31) tpre[p.batch] = incl;
+            __syncwarp();
+        }
         asm volatile("bar.arrive 3, %0;" ::"n"(COUNT3) : "memory");   // the lengths are in shared memory
         cur.start(p, lens);
     } else if (SPLIT && warp == WARPS + 1) {
@@ -892,7 +987,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
             const int nt = cur.tiles_here();
             const int left = cur.tok_end - cur.tile0 * TILE;
             if (lane == 0)
-                *meta = make_uint4((uint32_t)cur.unit, (uint32_t)cur.chunk_idx,
+                *meta = make_uint4((uint32_t)cur.unit, (uint32_t)cur.slot,
                                    (uint32_t)nt | (cur.stage_idx < GROUPS ? F_FIRST : 0u) |
                                        (cur.stage_idx >= cur.stages - GROUPS ? F_LAST : 0u),
                                    (uint32_t)left);
@@ -926,7 +1021,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         // for the CTA's consumer warps: once all of them have stored their partial of an item (done barrier)
         // it counts the chunk into the unit's arrival counter, with one fence for the lot.  The merges wait
         // for these counters in the tail phase.
-        StageCursor<SR, GROUPS> told = cur;            // the next item to announce
+        StageCursor<SR, GROUPS, FLAT> told = cur;            // the next item to announce
         bool ok = true;
         auto announce = [&]() {
             if (lane == 0) ok = mbar_wait(done_addr + 8 * (told.seq % DSLOTS), (told.seq / DSLOTS) & 1);
@@ -977,7 +1072,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
     } else {
     // ---- consumers: group (warp / WPG) takes every GROUPS-th stage; its warp i takes records RPW*i .. RPW*i+RPW-1 ----
     WarpState<C::MT> st;
-    int unit = 0, chunk_idx = 0, seq = -1;
+    int unit = 0, slot = 0, seq = -1;
     st.m0 = st.m1 = st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
     const int r0 = RPW * (warp % WPG);
     for (uint32_t n = warp / WPG;; n += GROUPS) {
@@ -1001,7 +1096,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
         }
         const int nt = meta.z & 0xffff;
         if (meta.z & F_FIRST) {
-            unit = (int)meta.x; chunk_idx = (int)meta.y;
+            unit = (int)meta.x; slot = (int)meta.y;
             st.m0 = st.m1 = 0.0f; st.l0 = st.l1 = 0.0f; st.thr = NEG_INF;
 #pragma unroll
             for (int mt = 0; mt < C::MT; mt++) { st.O[mt][0] = st.O[mt][1] = st.O[mt][2] = st.O[mt][3] = 0.0f; }
@@ -1041,7 +1136,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
                 st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, o);
             }
             const bool none = st.thr == NEG_INF;      // this warp saw no token of the item
-            const int64_t pbase = (((int64_t)unit * p.nchunks + chunk_idx) * WARPS + warp) * p.group;
+            const int64_t pbase = ((int64_t)slot * WARPS + warp) * p.group;
             const int h0 = 2 * t, h1 = 2 * t + 1;
             if (g == 0) {
                 if (h0 < p.group) { p.part_m[pbase + h0] = none ? NEG_INF : st.m0; p.part_l[pbase + h0] = st.l0; }
@@ -1076,7 +1171,8 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
             const int u = task / p.group, nh = task - u * p.group;
             const int S = lens.get(p, u / p.kv_heads) & LEN_MASK;
             if (S == 0) continue;                             // (CTA 0 zeroed the outputs of empty sequences)
-            const int need = (S + p.chunk - 1) / p.chunk;
+            int slot0, need;
+            unit_pieces<FLAT>(p, lens, u, S, slot0, need);
             if (lane == 0) {
                 const unsigned long long t0 = wall_ns();
                 int seen;
@@ -1088,7 +1184,7 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) atomicOr(p.status, TQB_DECODE_WAIT_EXPIRED); break; }
-            merge_head<D>(p, u, nh, min(need * WARPS, MERGE_MAX_CHUNKS), lane,
+            merge_head<D>(p, u, slot0, nh, need * WARPS, lane,
                           C::ROT_SMEM ? reinterpret_cast<const float*>(smem_gen + rot_addr + C::ROT_BYTES) : p.rot_v,
                           C::ROT_SMEM ? C::ROT_STRIDE : D);
         }
@@ -1126,8 +1222,9 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // every sequence at the host's bound max_len.  Small chunks balance the CTAs, large ones keep the partials
 // (consumer warps x group x (D+2) floats per item) and the merge small; the merge handles at most
 // MERGE_MAX_CHUNKS partials per unit.
-static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets) {
-    const double item_cost = 2048.0;      // measured: an extra item costs a CTA about 5 us, the time of 2,000 tokens
+constexpr double ITEM_COST = 2048.0;      // measured: an extra item costs a CTA about 5 us, the time of 2,000 tokens
+static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets, double* cost_out) {
+    const double item_cost = ITEM_COST;
     int best = 0;
     double best_cost = 1e300;
     for (int64_t L = stage_tokens; L <= (int64_t)1 << 30; L *= 2) {
@@ -1140,6 +1237,7 @@ static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_
         }
         if (L >= max_len && best) break;
     }
+    *cost_out = best_cost;
     return best;
 }
 
@@ -1148,12 +1246,23 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     const int64_t units = (int64_t)batch * kv_heads;
     const int group = q_heads / kv_heads;
     const int sets = dim == 64 ? 16 : 8;
-    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), sm_count(), sets * 32, sets);
+    double chunk_cost = 0.0;
+    w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), sm_count(), sets * 32, sets, &chunk_cost);
     w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
+    // The flat partition needs the lengths in shared memory (batch <= 256) and tile counts that fit an int.
+    const int64_t max_tiles = units * ((std::max<int64_t>(max_len, 1) + TILE - 1) / TILE);
+    // It streams the same number of tokens on every CTA but costs a CTA one more item and a fixed 4,600 tokens'
+    // worth of set-up and merging (measured at two shapes): it is taken where the chunked deal leaves CTAs idle
+    // for longer than that -- several units per CTA and a number of units that the CTAs do not divide.
+    const double per_cta = (double)units / sm_count();
+    const double flat_cost = per_cta * (double)std::max<int64_t>(max_len, 1) + (per_cta + 1.0) * ITEM_COST + 4608.0;
+    w.flat = batch <= 256 && max_tiles + sm_count() < 0x7fffffff && flat_cost < 0.98 * chunk_cost;
     size_t off = 0;
     w.off_status = off; off = align_up(off + 256, 256);                    // status word, exit counter
     w.off_cnt = off;    off = align_up(off + (size_t)units * 4, 256);      // arrival counter per unit
-    const size_t parts = (size_t)units * w.nchunks * sets * group;
+    // partial slots: one per (unit, chunk), or one per (unit, CTA that streams a piece of it): slot = CTA + unit
+    const size_t slots = w.flat ? (size_t)units + sm_count() : (size_t)units * w.nchunks;
+    const size_t parts = slots * sets * group;
     w.off_m = off;   off = align_up(off + parts * 4, 256);
     w.off_l = off;   off = align_up(off + parts * 4, 256);
     w.off_acc = off; off = align_up(off + parts * dim * 4, 256);
@@ -1161,15 +1270,16 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     return w;
 }
 
-template <int D, int KB, int VB, bool PAGED>
+template <int D, int KB, int VB, bool PAGED, bool FLAT>
 static int launch_fused(const DecodeParams& p, cudaStream_t st) {
     using C = DecodeCfg<D, KB, VB>;
-    auto kern = decode_fused_kernel<D, KB, VB, PAGED>;
+    auto kern = decode_fused_kernel<D, KB, VB, PAGED, FLAT>;
     TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
-    const int64_t items = (int64_t)p.batch * p.kv_heads * p.nchunks;
+    const int64_t items = p.flat ? (int64_t)p.batch * p.kv_heads * ((p.max_len + TILE - 1) / TILE)
+                                 : (int64_t)p.batch * p.kv_heads * p.nchunks;
     if (items + sm_count() >= 0x7fffffff)
         return fail(TQB_ERR_UNSUPPORTED, "decode_attention: too many (sequence, head, chunk) work items");
-    const int grid = (int)std::min<int64_t>(sm_count(), items);
+    const int grid = (int)std::min<int64_t>(sm_count(), std::max<int64_t>(items, 1));
     // programmatic dependent launch: the tables are built while the previous kernel of the stream drains
     TQB_CUDA(launch_pdl(1, kern, dim3(grid), dim3(C::THREADS), C::DYN, st, p));
     return check_launch("decode_fused");
@@ -1177,7 +1287,9 @@ static int launch_fused(const DecodeParams& p, cudaStream_t st) {
 
 template <int D, bool PAGED>
 static int dispatch_bits(int kbits, int vbits, const DecodeParams& p, cudaStream_t st) {
-#define TQB_CASE(kb, vb) if (kbits == kb && vbits == vb) return launch_fused<D, kb, vb, PAGED>(p, st);
+#define TQB_CASE(kb, vb)                                                                               \
+    if (kbits == kb && vbits == vb)                                                                    \
+        return p.flat ? launch_fused<D, kb, vb, PAGED, true>(p, st) : launch_fused<D, kb, vb, PAGED, false>(p, st);
     TQB_CASE(4, 2) TQB_CASE(4, 3) TQB_CASE(4, 4)
     TQB_CASE(3, 2) TQB_CASE(3, 3) TQB_CASE(3, 4)
     TQB_CASE(2, 2) TQB_CASE(2, 3) TQB_CASE(2, 4)
@@ -1246,7 +1358,7 @@ static int decode_common(const void* query, int q_dtype, const void* key, const 
     p.lens_in = seq_lens; p.lens_out = lens_mut; p.block_tables = block_tables;
     p.max_seq = paged ? (int64_t)max_blocks * block_size : max_seq; p.max_len = max_len;
     p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = group;
-    p.max_blocks = max_blocks; p.block_size = block_size; p.chunk = w.chunk; p.nchunks = w.nchunks;
+    p.max_blocks = max_blocks; p.block_size = block_size; p.chunk = w.chunk; p.nchunks = w.nchunks; p.flat = w.flat;
     p.step = key != nullptr ? 1 : 0;
     p.query = query; p.key = key; p.value = value; p.in_dtype = q_dtype; p.kv_stride = kv_stride;
     p.rot_k = rot_k; p.rot_v = rot_v; p.bnd_k = bnd_k; p.bnd_v = bnd_v; p.cent_k = cent_k; p.cent_v = cent_v;
