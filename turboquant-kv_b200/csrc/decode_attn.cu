@@ -246,8 +246,9 @@ struct Lens {
 };
 
 // Position of a CTA in its stream of pipeline stages.  Two ways of dealing the work:
-//   chunks  items (unit, chunk of p.chunk tokens) are dealt round-robin to the CTAs; the host chose the chunk
-//           from its bound on the lengths.  Partials of an item go to slot unit * nchunks + chunk.
+//   chunks  items (unit, chunk of p.chunk tokens; a unit's last chunk takes the remainder too, so no item is
+//           tiny) are dealt round-robin to the CTAs; the host chose the chunk from its bound on the lengths.
+//           Partials of an item go to slot unit * nchunks + chunk.
 //   flat    (p.flat) the tiles of all units, in unit order, form one range of T tiles (T from the lengths on
 //           the device); CTA c takes tiles [c Q, (c+1) Q), Q = ceil(T / grid): a piece of a unit, whole units,
 //           a piece of the next -- every CTA streams the same number of tokens whatever the number of units.
@@ -320,14 +321,14 @@ struct StageCursor {
             const int e = lens.get(p, b);
             const int S = e & LEN_MASK;
             const int tok0 = chunk_idx * p.chunk;
-            tok_end = min(S, tok0 + p.chunk);
+            tok_end = chunk_idx == p.nchunks - 1 ? S : min(S, tok0 + p.chunk);     // the last chunk takes the rest
             if (tok0 < tok_end) {
                 tiles_left = (tok_end - tok0 + TILE - 1) / TILE;
                 tile0 = tok0 / TILE;
                 stage_idx = 0;
                 stages = max(GROUPS, (tiles_left + SR - 1) / SR);
-                append = (e & LEN_ROOM) && (S - 1) / p.chunk == chunk_idx;
-                slot = item;
+                append = (e & LEN_ROOM) && min(p.nchunks - 1, (S - 1) / p.chunk) == chunk_idx;
+                slot = unit * p.nchunks + chunk_idx;
                 seq++;
                 return;
             }
@@ -362,7 +363,7 @@ __device__ __forceinline__ void unit_pieces(const DecodeParams& p, const Lens& l
         need = last - first + 1;
     } else {
         slot0 = unit * p.nchunks;
-        need = (S + p.chunk - 1) / p.chunk;
+        need = min(p.nchunks, (S + p.chunk - 1) / p.chunk);
     }
 }
 
@@ -1216,23 +1217,22 @@ __global__ void __launch_bounds__(DecodeCfg<D, KB, VB>::THREADS, 1) decode_fused
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Tokens per (unit, chunk) work item of the streaming kernel.  Items are dealt round-robin to the CTAs (one
-// per SM).  The estimate of a CTA's load, in tokens: its share of the units' full chunks, each with a fixed
-// cost for switching items (partials, fragments), plus its share of the units' last, shorter chunks, taking
-// every sequence at the host's bound max_len.  Small chunks balance the CTAs, large ones keep the partials
-// (consumer warps x group x (D+2) floats per item) and the merge small; the merge handles at most
-// MERGE_MAX_CHUNKS partials per unit.
+// Tokens per (unit, chunk) work item of the streaming kernel.  A unit has floor(max_len / L) chunks of L
+// tokens, the last of which takes the remainder too (an item of a few tokens would cost as much set-up as a
+// long one).  Items are dealt round-robin to the CTAs (one per SM).  The estimate of a CTA's load, in tokens:
+// its number of items times the longest item plus a fixed cost for switching items (preparation, partials,
+// a pipeline bubble), taking every sequence at the host's bound max_len.  Small chunks balance the CTAs, large
+// ones keep the partials (consumer warps x group x (D+2) floats per item) and the merge small; the planner
+// keeps the partials per unit within MERGE_MAX_CHUNKS.
 constexpr double ITEM_COST = 2048.0;      // measured: an extra item costs a CTA about 5 us, the time of 2,000 tokens
 static int choose_chunk(int64_t units, int64_t max_len, int64_t ctas, int stage_tokens, int sets, double* cost_out) {
-    const double item_cost = ITEM_COST;
     int best = 0;
     double best_cost = 1e300;
     for (int64_t L = stage_tokens; L <= (int64_t)1 << 30; L *= 2) {
-        const int64_t nch = (max_len + L - 1) / L;
+        const int64_t nch = std::max<int64_t>(1, max_len / L);
         if (nch * sets <= MERGE_MAX_CHUNKS) {
-            const int64_t full = nch - 1, rest = max_len - full * L;
-            const double cost = (double)((units * full + ctas - 1) / ctas) * ((double)L + item_cost) +
-                                (double)((units + ctas - 1) / ctas) * ((double)rest + item_cost);
+            const int64_t longest = max_len - (nch - 1) * L;
+            const double cost = (double)((units * nch + ctas - 1) / ctas) * ((double)longest + ITEM_COST);
             if (cost < best_cost) { best_cost = cost; best = (int)L; }
         }
         if (L >= max_len && best) break;
@@ -1248,7 +1248,7 @@ static DecodeWorkspace plan_workspace(int batch, int q_heads, int kv_heads, int 
     const int sets = dim == 64 ? 16 : 8;
     double chunk_cost = 0.0;
     w.chunk = choose_chunk(units, std::max<int64_t>(max_len, 1), sm_count(), sets * 32, sets, &chunk_cost);
-    w.nchunks = (int)std::max<int64_t>(1, (max_len + w.chunk - 1) / w.chunk);
+    w.nchunks = (int)std::max<int64_t>(1, max_len / w.chunk);
     // The flat partition needs the lengths in shared memory (batch <= 256) and tile counts that fit an int.
     const int64_t max_tiles = units * ((std::max<int64_t>(max_len, 1) + TILE - 1) / TILE);
     // It streams the same number of tokens on every CTA but costs a CTA one more item and a fixed 4,600 tokens'
