@@ -55,10 +55,10 @@ KEY_BITS, VALUE_BITS = 4, 2
 BYTES_PER_TOKEN_HEAD = KEY_BITS * HEAD_DIM // 8 + 4 + VALUE_BITS * HEAD_DIM // 8 + 4   # 56
 METRIC, UNIT = "decode_attention_tokens_per_s", "tokens/s"
 # DRAM traffic of one decode_fused_kernel launch, cited from an ncu capture of a full-size launch of this
-# workload (dram__bytes_read.sum 244.27 MB + dram__bytes_write.sum 14.87 MB against 234.88 MB of algorithmic
+# workload (dram__bytes_read.sum 236.61 MB + dram__bytes_write.sum 6.72 MB against 234.88 MB of algorithmic
 # bytes); traffic grows in proportion to the tokens, so other sizes are scaled by the ratio.  It is a
 # citation of that capture, not a live measurement: counters cannot be read inside the timed run.
-NCU_TRAFFIC_RATIO = (244.27 + 14.87) / 234.88
+NCU_TRAFFIC_RATIO = (236.61 + 6.72) / 234.88
 NCU_TRAFFIC_SOURCE = ("cited from profiles/decode_fused_kernel_c4_ctx16384.md (ncu dram__bytes_read.sum + "
                       "dram__bytes_write.sum of one launch), scaled by the bytes of this launch")
 
