@@ -184,11 +184,13 @@ class TurboQuantV1Impl(AttentionImpl[TurboQuantV1Metadata]):
         lens = md.seq_lens.to(torch.int32).contiguous()
         if md.max_query_len == 1 and n == md.num_reqs:
             if q.dtype == out.dtype and out.is_contiguous():
+                # (the workspace is sized for the block table's capacity once: a captured graph keeps its address)
                 kv.decode_attention(pool, q, HK, lens, md.max_seq_len, block_tables=bt, block_size=block_size,
-                                    scale=self.scale, out=out)
+                                    scale=self.scale, out=out, reserve_len=bt.shape[1] * block_size)
             else:
                 out.copy_(kv.decode_attention(pool, q, HK, lens, md.max_seq_len, block_tables=bt,
-                                              block_size=block_size, scale=self.scale))
+                                              block_size=block_size, scale=self.scale,
+                                              reserve_len=bt.shape[1] * block_size))
             return output
 
         # 2b. requests with several new tokens (prefill chunks, speculative verification): every query token is
