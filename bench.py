@@ -25,14 +25,15 @@ One JSON line is printed by rank 0:
             K/V rows and norms of one layer; its duration is measured with CUDA events in an extra pass
             of the same steps launched eagerly (events cannot be read inside a captured graph), one event
             pair per launch
-  cpu_baseline  the CPU checker (oracle/, an OpenMP port of the upstream dequantise-then-attend path)
-            timed on this machine's cores on a sample of the same workload
+  cpu_baseline  the upstream project's own OpenMP kernels (compiled in place into oracle/_ref; the CPU port
+            under oracle/ where that library is missing) timed on this machine's cores on a sample of the
+            same workload
   extra     secondary figures: shorter contexts; the paged Llama-3-8B configuration as a whole (32 layers
             resident, decode step and prefill quantisation timed apart, parity against the CPU port); the
             quantiser; the 4-bit index scan over 10 M rows (QPS, HBM GB/s, and the first queries again with
             the upstream C++ core over all rows)
 
---impl reference times only the CPU port, on a bounded sample per step, and prints the same line shape.
+--impl reference times only that CPU arm, on a bounded sample per step, and prints the same line shape.
 """
 from __future__ import annotations
 
@@ -136,7 +137,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU port (the reference arm and the cpu_baseline leg)
+# CPU arm (the reference arm and the cpu_baseline leg)
 # ------------------------------------------------------------------------------------------------
 def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice = slice(0, KV_HEADS), threads: int = 0):
     """Dequantise-then-attend on the host for `sample_seqs` sequences x 8 KV heads of ONE layer.
