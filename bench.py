@@ -582,6 +582,18 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         est = qs @ dequantize_prod(mp, sg, rn, nr, 3, 128, rotation=rot, codebook=cb2, S_matrix=S).t()
         exact = qs @ db[:100_000].t()
         slope = float((est * exact).sum() / (exact * exact).sum())
+        # Prod-mode search over the packed rows (1 M x d128, 3 bits): the scan kernel's Algorithm-2 branch
+        from turboquant_kv import TurboQuantIndex
+
+        pidx = TurboQuantIndex(dim=128, bit_width=3, mode="prod", seed=42, device=device)
+        pidx.add(db)
+        pq = qs[:64].contiguous()
+        pidx.search(pq[:4], 10)
+        ms_ps = timed_ms(lambda: pidx.search(pq, 10), reps=3)
+        ps, pi = pidx.search(pq, 10)
+        exact_top = (pq @ db.t()).topk(10, dim=-1).indices
+        recall = float(torch.tensor([len(set(a.tolist()) & set(b.tolist())) for a, b in zip(pi, exact_top)]).float().mean() / 10)
+        del pidx
         res["quantize"] = {
             "mse_4bit_d128_vectors_per_s": 65536 / (ms_q * 1e-3), "mse_4bit_quantize_ms": ms_q,
             "mse_4bit_dequantize_ms": ms_d, "mse_4bit_rotation_tflops": 2 * 128 * 128 * 65536 / (ms_q * 1e-3) / 1e12,
@@ -591,6 +603,7 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
             "mse_4bit_per_vector_squared_error": mse,
             "prod_3bit_d128_vectors_per_s": 1_000_000 / (ms_p * 1e-3),
             "prod_3bit_estimator_bias": float((est - exact).mean()), "prod_3bit_estimator_slope": slope,
+            "prod_3bit_search_1m_rows_64_queries_qps": 64 / (ms_ps * 1e-3), "prod_3bit_search_top10_overlap_with_exact_search": recall,
             "note": "rank 0 only; MSE calls of 512 rows and more run the rotation on tcgen05 (bf16 operand splits, "
                     "float32 accumulation in tensor memory, rows fed by TMA bulk copies), with the codes of the float32 "
                     "FMA kernel; Prod mode and short calls run the float32 FMA kernel"}

@@ -256,6 +256,19 @@ int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, 
                           void* workspace, size_t workspace_bytes, float* out_scores, int64_t* out_ids,
                           void* stream);
 
+/* Prod-mode search (Algorithm 2 rows): replaces TurboQuantIndex._search_prod (turboquant_kv/search.py:229-252),
+ * which dequantises every row (dequantize_prod, reference.py:472-533) and multiplies by the queries.  The scan
+ * computes the same inner product from the packed rows, without the dense reconstruction:
+ *     <q, x~> = norm * ( <R q, c[codes]> + sqrt(pi/2)/dim * ||r|| * <S q, signs> ),   sign = 2 * bit - 1
+ * mse_packed (n, (bits-1) * ceil(dim/8)), signs (n, ceil(dim/8)), res_norms (n), norms (n); S (dim, dim) the QJL
+ * matrix; `bits` is the index's bit width (MSE codes use bits - 1).  Outputs as tqb_scan_topk; scores agree
+ * with upstream's float32 matrix product to rounding (its summation order is the BLAS library's). */
+size_t tqb_scan_topk_prod_workspace_bytes(int nq, int64_t n, int dim, int bits, int k);
+int tqb_scan_topk_prod(const float* queries, int nq, const uint8_t* mse_packed, const uint8_t* signs,
+                       const float* res_norms, const float* norms, int64_t n, int dim, int bits,
+                       const float* rotation, const float* centroids, const float* S, int k, int64_t id_offset,
+                       void* workspace, size_t workspace_bytes, float* out_scores, int64_t* out_ids, void* stream);
+
 /* The same scan for callers that cannot allocate a workspace (no counterpart in the reference): the
  * scratch is a fixed 4 MiB array inside the library's device image, so the call reaches no allocating
  * routine.  Meant for hosts that have already handed all free device memory to pools of their own,

@@ -27,6 +27,7 @@
 #include "pipe.cuh"
 #include "tiled_layout.cuh"
 
+#include <cmath>
 #include <mutex>
 
 namespace tqb {
@@ -78,6 +79,9 @@ struct ScanParams {
     int combine;                        // record scan: one merged candidate list per CTA instead of one per warp
     int dim, bits, nq, k, kk;           // kk = scan_kk(k) candidates kept per list
     const float* rot; const float* cent; const float* queries;
+    // Prod-mode rows (Algorithm 2): `packed` holds the MSE codes at `bits` (= bit_width - 1), plus one QJL sign
+    // per dimension, the residual norm, and the query projected by the QJL matrix (qsign = S q).  Null: MSE rows.
+    const uint8_t* signs; const float* res_norms; const float* qsign; float sign_coef;
     int64_t id_offset;
     int lists_per_query;                // candidate lists written per query (= warps in the grid)
     // workspace views
@@ -703,10 +707,14 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) scan_generic_kernel(const Sca
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int levels = 1 << p.bits, bpp = (p.dim + 7) >> 3, pd = p.bits * bpp;
     float* T = reinterpret_cast<float*>(smem_raw);                    // dim * levels
-    float* lists_s = T + p.dim * levels;
+    const bool prod = p.signs != nullptr;
+    float* Ts = T + p.dim * levels;                                   // Prod: the query projected by S, dim floats
+    float* lists_s = Ts + (prod ? p.dim : 0);
     int* lists_i = reinterpret_cast<int*>(lists_s + SCAN_WARPS * p.kk);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = blockIdx.y;
+    if (prod)
+        for (int e = threadIdx.x; e < p.dim; e += blockDim.x) Ts[e] = p.qsign[(int64_t)q * p.dim + e];
     float* ls = lists_s + warp * p.kk;
     int* li = lists_i + warp * p.kk;
     for (int e = threadIdx.x; e < p.dim * levels; e += blockDim.x)
@@ -735,7 +743,22 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) scan_generic_kernel(const Sca
                     dot = __fadd_rn(dot, T[(8 * m + t) * levels + c]);
                 }
             }
-            sc = __fmul_rn(dot, p.norms[r]);
+            if (prod) {
+                // <q, x~> = norm * ( <R q, c[codes]> + sqrt(pi/2)/d * ||r|| * <S q, signs> ),  sign = 2 bit - 1
+                const uint8_t* srow = p.signs + r * bpp;
+                float ds = 0.0f;
+                for (int m = 0; m < bpp; m++) {
+                    const uint32_t byte = srow[m];
+                    const int lim = min(8, p.dim - 8 * m);
+                    for (int t = 0; t < lim; t++) {
+                        const float v = Ts[8 * m + t];
+                        ds += (byte >> (7 - t)) & 1u ? v : -v;
+                    }
+                }
+                sc = p.norms[r] * fmaf(p.sign_coef * p.res_norms[r], ds, dot);
+            } else {
+                sc = __fmul_rn(dot, p.norms[r]);
+            }
         }
         uint32_t mask = __ballot_sync(0xffffffffu, valid && better(sc, (int)r, thr_s, thr_i));
         while (mask) {
@@ -892,11 +915,21 @@ __global__ void __launch_bounds__(MERGE_THREADS) scan_merge_kernel(const ScanPar
             }
             nrm = p.norms[id];
         }
+        float ds = 0.0f;
+        if (p.signs) {                                  // Prod rows: the sign term, summed across the warp
+            const uint8_t* srow = p.signs + (int64_t)id * bpp;
+            for (int d = lane; d < p.dim; d += 32) {
+                const float v = p.qsign[(int64_t)q * p.dim + d];
+                ds += (srow[d >> 3] >> (7 - (d & 7))) & 1u ? v : -v;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
+        }
         __syncwarp();
         if (lane == 0) {
             float dot = 0.0f;
             for (int d = 0; d < p.dim; d++) dot = __fadd_rn(dot, vals[warp][d]);
-            sel_s[e] = __fmul_rn(dot, nrm);
+            sel_s[e] = p.signs ? nrm * fmaf(p.sign_coef * p.res_norms[id], ds, dot) : __fmul_rn(dot, nrm);
         }
         __syncwarp();
     }
@@ -1159,6 +1192,75 @@ extern "C" int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed
         if (int e = check_launch("scan_generic")) return e;
     }
     const size_t msmem = sizeof(float) * (size_t)dim * (1 << bits);
+    TQB_CUDA(cudaFuncSetAttribute(scan_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(msmem, 48 * 1024)));
+    scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
+    return check_launch("scan_merge");
+}
+
+extern "C" size_t tqb_scan_topk_prod_workspace_bytes(int nq, int64_t n, int dim, int bits, int k) {
+    if (nq <= 0 || dim <= 0 || bits < 2 || bits > 5 || k <= 0 || k > TQB_SCAN_MAX_K) return 0;
+    // the MSE scan's workspace plus the queries projected by the QJL matrix
+    return tqb::plan_scan(nq, n, dim, bits - 1, k).total + tqb::s_align((size_t)nq * dim * 4);
+}
+
+extern "C" int tqb_scan_topk_prod(const float* queries, int nq, const uint8_t* mse_packed, const uint8_t* signs,
+                                  const float* res_norms, const float* norms, int64_t n, int dim, int bits,
+                                  const float* rotation, const float* centroids, const float* S, int k,
+                                  int64_t id_offset, void* workspace, size_t workspace_bytes, float* out_scores,
+                                  int64_t* out_ids, void* stream) {
+    using namespace tqb;
+    TQB_REQUIRE(nq >= 0 && n >= 0, "scan_topk_prod: negative size");
+    TQB_REQUIRE(bits >= 2 && bits <= 5, "scan_topk_prod: bit_width must be 2-5 (1-4 MSE bits + the sign bit), got %d", bits);
+    TQB_REQUIRE(k >= 1, "scan_topk_prod: k must be positive, got %d", k);
+    if (k > TQB_SCAN_MAX_K) return fail(TQB_ERR_UNSUPPORTED, "scan_topk_prod: k = %d exceeds the limit %d", k, TQB_SCAN_MAX_K);
+    if (dim < 8 || dim > 512 || (dim & 7))
+        return fail(TQB_ERR_UNSUPPORTED, "scan_topk_prod: dim must be a multiple of 8 in 8..512, got %d", dim);
+    if (n >= 0x7fffffff) return fail(TQB_ERR_UNSUPPORTED, "scan_topk_prod: at most 2^31-2 rows per call (shard the index)");
+    if (nq == 0) return TQB_OK;
+    TQB_REQUIRE(queries && rotation && centroids && S && workspace && out_scores && out_ids, "scan_topk_prod: null pointer");
+    TQB_REQUIRE(n == 0 || (mse_packed && signs && res_norms && norms), "scan_topk_prod: null database");
+    TQB_REQUIRE((uintptr_t)workspace % 256 == 0, "scan_topk_prod: workspace must be 256-byte aligned");
+    const int mb = bits - 1;
+    const ScanPlan pl = plan_scan(nq, n, dim, mb, k);
+    const size_t need = pl.total + s_align((size_t)nq * dim * 4);
+    if (workspace_bytes < need)
+        return fail(TQB_ERR_WORKSPACE, "scan_topk_prod: workspace %zu bytes < required %zu", workspace_bytes, need);
+
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    ScanParams p{};
+    p.packed = mse_packed; p.norms = norms; p.n = n; p.dim = dim; p.bits = mb; p.nq = nq; p.k = k; p.kk = pl.kk;
+    p.rot = rotation; p.cent = centroids; p.queries = queries; p.id_offset = id_offset;
+    p.signs = signs; p.res_norms = res_norms;
+    p.sign_coef = (float)(std::sqrt(M_PI / 2.0) / (double)dim);
+    p.status = reinterpret_cast<int*>(ws + pl.off_status);
+    p.qrot = reinterpret_cast<float*>(ws + pl.off_qrot);
+    p.qfrag = reinterpret_cast<uint32_t*>(ws + pl.off_qfrag);
+    p.qscale = reinterpret_cast<float*>(ws + pl.off_qscale);
+    p.cand_s = reinterpret_cast<float*>(ws + pl.off_cs);
+    p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
+    float* qsign = reinterpret_cast<float*>(ws + pl.total);
+    p.qsign = qsign;
+    p.out_scores = out_scores; p.out_ids = out_ids;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t ntiles = n / SCAN_TILE;
+    const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(sm_count(), ceil_div(ntiles, SCAN_WARPS)));
+    p.lists_per_query = gx * SCAN_WARPS;
+
+    // R q and S q: the same kernel twice (row j of the matrix times the query, float32, k ascending)
+    const size_t psmem = sizeof(float) * (size_t)(1 + 2 * QG) * dim;
+    scan_prepare_kernel<<<pl.ngroups, 128, psmem, st>>>(p, 0);
+    if (int e = check_launch("scan_prepare")) return e;
+    ScanParams ps = p;
+    ps.rot = S; ps.qrot = qsign;
+    scan_prepare_kernel<<<pl.ngroups, 128, psmem, st>>>(ps, 0);
+    if (int e = check_launch("scan_prepare")) return e;
+
+    const size_t smem = sizeof(float) * ((size_t)dim * (1 << mb) + dim) + (size_t)SCAN_WARPS * p.kk * 8;
+    TQB_CUDA(cudaFuncSetAttribute(scan_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(gx, nq);
+    scan_generic_kernel<<<grid, SCAN_WARPS * 32, smem, st>>>(p);
+    if (int e = check_launch("scan_generic")) return e;
+    const size_t msmem = sizeof(float) * (size_t)dim * (1 << mb);
     TQB_CUDA(cudaFuncSetAttribute(scan_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max<size_t>(msmem, 48 * 1024)));
     scan_merge_kernel<<<nq, MERGE_THREADS, msmem, st>>>(p);
     return check_launch("scan_merge");

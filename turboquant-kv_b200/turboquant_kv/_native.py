@@ -78,6 +78,11 @@ def lib():
                                       c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                       c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p,
                                       c_int, c_void_p]
+        L.tqb_scan_topk_prod_workspace_bytes.restype = c_size_t
+        L.tqb_scan_topk_prod_workspace_bytes.argtypes = [c_int, c_int64, c_int, c_int, c_int]
+        L.tqb_scan_topk_prod.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p,
+                                         c_void_p, c_void_p]
         L.tqb_scan_topk.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                     c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
         L.tqb_scan_records_workspace_bytes.restype = c_size_t

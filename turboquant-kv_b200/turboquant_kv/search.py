@@ -11,8 +11,9 @@ Tensors may be passed on the host or on the GPU; results come back on the device
 Results: scores descending, ids int64; equal scores are ordered by ascending id; ``k`` is clipped
 to the number of stored vectors like the upstream Python path.
 
-Prod mode keeps upstream's formulation (reconstruct, then q . x): rows are reconstructed chunk by
-chunk with the dequantize_prod kernel and scored with a dense matmul.
+Prod mode (upstream search.py:229-252 reconstructs every row and multiplies by the queries) runs the same
+scan over the packed Algorithm-2 rows: <q, x~> = norm * (<R q, c[codes]> + sqrt(pi/2)/d * ||r|| * <S q, signs>),
+``tqb_scan_topk_prod`` -- no dense reconstruction of the database.
 """
 from __future__ import annotations
 
@@ -23,8 +24,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _native as N
-from .reference import (_make_qjl_matrix, dequantize_prod, lloyd_max_codebook, make_rotation_matrix,
-                        quantize_mse, quantize_prod)
+from .reference import _make_qjl_matrix, lloyd_max_codebook, make_rotation_matrix, quantize_mse, quantize_prod
 
 HEADER_FORMAT = "<BII"  # bit_width (u8), dim (u32), n_vectors (u32) -- upstream search.py:29
 HEADER_SIZE = struct.calcsize(HEADER_FORMAT)
@@ -32,7 +32,6 @@ MODE_MSE, MODE_PROD = 0, 1
 TQIX_MAGIC, TQIX_VERSION = 0x54514958, 1  # upstream csrc/core/turboquant_core.cpp:520-521
 
 _QUERY_CHUNK = 512      # queries per scan call (bounds the candidate workspace)
-_PROD_ROW_CHUNK = 1 << 18
 
 
 def merge_topk(scores: torch.Tensor, ids: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -239,24 +238,29 @@ class TurboQuantIndex:
         return out_s, out_i
 
     def _search_prod(self, q: torch.Tensor, k: int):
-        best_s = best_i = None
-        for lo in range(0, self.n_vectors, _PROD_ROW_CHUNK):
-            hi = min(self.n_vectors, lo + _PROD_ROW_CHUNK)
-            recon = dequantize_prod(self._packed_codes[lo:hi], self._qjl_signs[lo:hi], self._residual_norms[lo:hi],
-                                    self._norms[lo:hi], self.bit_width, self.dim, rotation=self._rotation,
-                                    codebook=self._codebook, S_matrix=self._S_matrix)
-            sc = q @ recon.t()
-            kk = min(k, hi - lo)
-            s, i = torch.topk(sc, kk, dim=-1)
-            i = i + lo + self.id_offset
-            if kk < k:
-                s = torch.cat([s, s.new_full((s.shape[0], k - kk), float("-inf"))], 1)
-                i = torch.cat([i, i.new_full((i.shape[0], k - kk), -1)], 1)
-            if best_s is None:
-                best_s, best_i = s, i
-            else:
-                best_s, best_i = merge_topk(torch.stack([best_s, s], 1), torch.stack([best_i, i], 1), k)
-        return best_s, best_i
+        """Prod-mode search over the packed rows (upstream search.py:229-252 dequantises every row and multiplies
+        by the queries): <q, x~> = norm * (<R q, c[codes]> + sqrt(pi/2)/d * ||r|| * <S q, signs>), streamed row by
+        row by the scan kernel, top-k merged on the GPU -- no dense reconstruction of the database."""
+        if k > N.SCAN_MAX_K:
+            raise RuntimeError(f"k = {k} exceeds the scan's limit of {N.SCAN_MAX_K}")
+        L = N.lib()
+        nq = q.shape[0]
+        out_s = torch.empty(nq, k, dtype=torch.float32, device=self.device)
+        out_i = torch.empty(nq, k, dtype=torch.int64, device=self.device)
+        with torch.cuda.device(self.device):
+            for lo in range(0, nq, _QUERY_CHUNK):
+                qc = q[lo:lo + _QUERY_CHUNK].contiguous()
+                n = qc.shape[0]
+                need = L.tqb_scan_topk_prod_workspace_bytes(n, self.n_vectors, self.dim, self.bit_width, k)
+                if self._workspace is None or self._workspace.numel() < need:
+                    self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+                N.check(L.tqb_scan_topk_prod(N.ptr(qc), n, N.ptr(self._packed_codes), N.ptr(self._qjl_signs),
+                                             N.ptr(self._residual_norms), N.ptr(self._norms), self.n_vectors, self.dim,
+                                             self.bit_width, N.ptr(self._rotation), N.ptr(self._codebook[1]),
+                                             N.ptr(self._S_matrix), k, self.id_offset, N.ptr(self._workspace),
+                                             self._workspace.numel(), N.ptr(out_s[lo:lo + n]), N.ptr(out_i[lo:lo + n]),
+                                             N.stream_of(qc)))
+        return out_s, out_i
 
     # ------------------------------------------------------------------------------------------
     def save(self, path: str, format: str = "python"):
