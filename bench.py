@@ -662,7 +662,8 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
     sc_h, ids_h = index.search(hq, k)
     torch.cuda.synchronize()
     ms_host = sync_max((time.perf_counter() - t0) * 1e3)
-    passes = math.ceil(nq / 4)
+    per_pass = 8 if nq > 4 else 4        # calls with more than four queries take eight per pass (one fp16 column each)
+    passes = math.ceil(nq / per_pass)
     scan_parity = None
     if world == 1 and not args.no_cpu and args.scan_parity_queries > 0:
         scan_parity = scan_reference_check(torch, index.local, queries[:args.scan_parity_queries], sc, ids, k)
@@ -672,7 +673,7 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         "single_query_hbm_frac": rows_local * row_bytes / (ms1 * 1e-3) / 1e9 / peaks["hbm_gbs"],
         "single_query_note": "includes query rotation and merge launches and the host-side call overhead",
         "qps": nq / (msq * 1e-3), "qps_e2e_host_buffers": nq / (ms_host * 1e-3),
-        "queries_per_pass": 4, "passes": passes,
+        "queries_per_pass": per_pass, "passes": passes,
         "batched_hbm_gbs_per_gpu": passes * rows_local * row_bytes / (msq * 1e-3) / 1e9,
         "add_vectors_per_s_per_gpu": rows_local / (t_add * 1e-3), "gpu_launches": launches,
         "ids_checksum": int(ids.sum().item()) if rank == 0 else None,
@@ -925,7 +926,7 @@ def run_case(args) -> None:
             idx.add(gam.sample((min(1_000_000, args.scan_rows - c0), 128)).clamp_(0, 255).round_())
         qs = gam.sample((max(args.queries_per_call, 1), 128)).clamp_(0, 255).round_()
         ms = timed(lambda: idx.search(qs, 10))
-        nbytes = args.scan_rows * 68 * math.ceil(qs.shape[0] / 4)
+        nbytes = args.scan_rows * 68 * math.ceil(qs.shape[0] / (8 if qs.shape[0] > 4 else 4))
         out.update(ms_per_call=ms, queries=qs.shape[0], bytes=nbytes, gbs=nbytes / ms / 1e6,
                    frac=nbytes / ms / 1e6 / peaks["hbm_gbs"])
     elif args.case == "quantize":

@@ -36,7 +36,8 @@ constexpr int SCAN_TILE = 16;
 constexpr int SCAN_MARGIN = 8;          // extra candidates a list keeps beyond k
 constexpr int SCAN_SELECT_MARGIN = 24;  // extra candidates the merge re-scores exactly beyond k
 constexpr int SCAN_WARPS = 8;
-constexpr int QG = 4;                   // queries per tensor-core pass
+constexpr int QG = 4;                   // queries per tensor-core pass over upstream rows (fp16 hi + lo query columns)
+constexpr int RQ = 8;                   // queries per pass over records (one fp16 column each: the pass only ranks)
 constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
 constexpr float QUERY_SCALE = 16.0f;
 constexpr int ID_NONE = 0x7fffffff;
@@ -121,38 +122,40 @@ __device__ __forceinline__ void list_insert(float* ls, int* li, int kk, float s,
 // =================================================================================================
 // 1. query rotation (+ B fragments for the tensor-core path)
 // =================================================================================================
-// One CTA per group of QG queries.  q_rot[j] = sum_k q[k] * R[j][k], accumulated in k order with
+// One CTA per group of QN queries (QN for scans over upstream rows, RQ for scans over records).  q_rot[j] = sum_k q[k] * R[j][k], accumulated in k order with
 // separate multiply and add, the arithmetic of csrc/core/turboquant_core.cpp:425-433.
 // Fragment word layout: qfrag[group][ks][lane] = uint2 {half 0, half 1} of the B operand;
-// MMA column n = lane/4 holds query n/2 of the group: even n its fp16 hi part, odd n its lo part,
+// QN = QN: MMA column n = lane/4 holds query n/2 of the group: even n its fp16 hi part, odd n its lo part,
 // so that the two columns of a query add up to a 22-bit query against the fp16 centroids.
+// QN = RQ: column n holds query n, fp16 (the pass over records only ranks; survivors are re-scored exactly).
+template <int QN>
 __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, int use_mma) {
     extern __shared__ float sm[];
-    float* qr = sm + p.dim;             // QG * dim (rotated queries); the raw queries follow
-    __shared__ float qmax[QG];
+    float* qr = sm + p.dim;             // QN * dim (rotated queries); the raw queries follow
+    __shared__ float qmax[QN];
     const int grp = blockIdx.x;
     pdl_wait();
     pdl_trigger();
     if (grp == 0 && threadIdx.x == 0) *p.status = 0;
-    // all QG queries of the group go through one pass over R: row j is read once (128-bit loads), each
+    // all QN queries of the group go through one pass over R: row j is read once (128-bit loads), each
     // query keeps its own sum, accumulated in k order with separate multiply and add
-    float* qin_all = qr + QG * p.dim;        // QG * dim (the caller sizes the shared memory for it)
-    for (int e = threadIdx.x; e < QG * p.dim; e += blockDim.x) {
-        const int jq = e / p.dim, k = e - jq * p.dim, q = grp * QG + jq;
+    float* qin_all = qr + QN * p.dim;        // QN * dim (the caller sizes the shared memory for it)
+    for (int e = threadIdx.x; e < QN * p.dim; e += blockDim.x) {
+        const int jq = e / p.dim, k = e - jq * p.dim, q = grp * QN + jq;
         qin_all[e] = q < p.nq ? p.queries[(int64_t)q * p.dim + k] : 0.0f;
     }
     __syncthreads();
     for (int j = threadIdx.x; j < p.dim; j += blockDim.x) {
         const float4* row = reinterpret_cast<const float4*>(p.rot + (int64_t)j * p.dim);
-        float s[QG];
+        float s[QN];
 #pragma unroll
-        for (int jq = 0; jq < QG; jq++) s[jq] = 0.0f;
-        const int nvalid = min(QG, p.nq - grp * QG);     // queries of this group that exist
+        for (int jq = 0; jq < QN; jq++) s[jq] = 0.0f;
+        const int nvalid = min(QN, p.nq - grp * QN);     // queries of this group that exist
 #pragma unroll 8
         for (int k4 = 0; k4 < p.dim / 4; k4++) {
             const float4 r = __ldg(row + k4);
 #pragma unroll
-            for (int jq = 0; jq < QG; jq++) {
+            for (int jq = 0; jq < QN; jq++) {
                 if (jq >= nvalid) break;
                 const float* qv = qin_all + jq * p.dim + 4 * k4;
                 s[jq] = __fadd_rn(s[jq], __fmul_rn(qv[0], r.x));
@@ -162,21 +165,21 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
             }
         }
 #pragma unroll
-        for (int jq = 0; jq < QG; jq++) {
-            const int q = grp * QG + jq;
+        for (int jq = 0; jq < QN; jq++) {
+            const int q = grp * QN + jq;
             if (q < p.nq) p.qrot[(int64_t)q * p.dim + j] = s[jq];
             qr[jq * p.dim + j] = q < p.nq ? s[jq] : 0.0f;
         }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp < QG) {
+    for (int jq = warp; jq < QN; jq += (int)(blockDim.x >> 5)) {
         float mx = 0.0f;
-        for (int k = lane; k < p.dim; k += 32) mx = fmaxf(mx, fabsf(qr[warp * p.dim + k]));
+        for (int k = lane; k < p.dim; k += 32) mx = fmaxf(mx, fabsf(qr[jq * p.dim + k]));
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         if (lane == 0) {
-            qmax[warp] = mx;
-            const int q = grp * QG + warp;
+            qmax[jq] = mx;
+            const int q = grp * QN + jq;
             if (q < p.nq) p.qscale[q] = mx / (CENT_SCALE * QUERY_SCALE);
         }
     }
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanParams p, i
     const int ksteps = p.dim >> 4;
     for (int idx = threadIdx.x; idx < ksteps * 32; idx += blockDim.x) {
         const int ks = idx >> 5, fl = idx & 31, g = fl >> 2, t = fl & 3;
-        const int jq = g >> 1, part = g & 1;
+        const int jq = QN == RQ ? g : g >> 1, part = QN == RQ ? 0 : g & 1;
         const float inv = qmax[jq] > 0.0f ? QUERY_SCALE / qmax[jq] : 0.0f;
         uint32_t w[2];
         for (int half = 0; half < 2; half++) {
@@ -384,7 +387,7 @@ struct RecScanCfg {
 };
 
 // NT records at once: acc[i] = this lane's part of the 16 x 8 score tile of record i.
-// qf[ks] = B fragment {[q_hi | q_lo] half 0, half 1}.
+// qf[ks] = B fragment {half 0, half 1}: column n = query n of the group, fp16.
 template <int D, int BITS, int NT>
 __device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, const uint2 (&qf)[D / 16],
                                                int lane, float (&acc)[NT][4]) {
@@ -415,11 +418,11 @@ __device__ __forceinline__ void rec_scan_tiles(uint32_t rec0, uint32_t tab, cons
 }
 
 // Candidate lists of up to 32 entries live in registers: lane e holds entry e (best first) of each of the
-// QG queries.  Insertion of (s, id) into the list of query bq (warp-uniform): the entries better than the
+// RQ queries.  Insertion of (s, id) into the list of query bq (warp-uniform): the entries better than the
 // candidate form a prefix, everything behind it moves down one lane.
 struct RegLists {
-    float s[QG];
-    int i[QG];
+    float s[RQ];
+    int i[RQ];
 };
 template <int JQ>
 __device__ __forceinline__ void reg_list_insert(RegLists& L, int kk, float s, int id, int lane) {
@@ -453,8 +456,13 @@ __device__ __noinline__ ScanThreshold rec_scan_offer(float* ls, int* li, int kk,
     return thr;
 }
 
-template <int D, int BITS>
+// NQ = RQ: eight queries per pass, one fp16 column each (calls with more than four queries and register lists);
+// NQ = QG: four queries per pass in hi + lo column pairs.  REGL: candidate lists of up to 32 entries in
+// registers (k <= 24), else in shared memory.
+template <int D, int BITS, int NQ, bool REGL>
 __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_kernel(const ScanParams p) {
+    constexpr bool PAIR = NQ == RQ;                  // a lane serves two queries (columns 2t, 2t+1)
+    static_assert(!PAIR || REGL, "eight queries per pass need the register lists");
     using C = RecScanCfg<D, BITS>;
     constexpr int WARPS = C::WARPS, GROUPS = C::GROUPS, WPG = C::WPG, RPW = C::RPW, SR = C::SR, NT = C::NT;
     constexpr uint32_t F_END = 1u << 31;
@@ -477,15 +485,15 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     const uint32_t full_addr = misc, empty_addr = misc + 64, meta_addr = misc + 128, cent_addr = misc + 192;
     // Candidate lists of up to 32 entries live in registers while the rows stream; they are written to
     // shared memory only once the stream has ended, over the then idle second part of the ring.
-    const bool reg_lists = p.kk <= 32;
-    const uint32_t lists_bytes = (uint32_t)WARPS * QG * p.kk * 8;
+    constexpr bool reg_lists = REGL;                 // (the host picks REGL = (kk <= 32))
+    const uint32_t lists_bytes = (uint32_t)WARPS * NQ * p.kk * 8;
     const uint32_t ringB = (misc + C::FIXED + (reg_lists ? 0u : lists_bytes) + 127u) & ~127u;
     const uint32_t lists_addr = reg_lists ? ringB : misc + C::FIXED;
     const int slotsB = ringB < end ? (int)((end - ringB) / C::STAGE) : 0;
     const int NS = min(C::MAX_NS, slotsA + slotsB);
     uint8_t* const smem_gen = smem_raw - base;       // generic pointer of shared address 0
     float* lists_s = reinterpret_cast<float*>(smem_gen + lists_addr);
-    int* lists_i = reinterpret_cast<int*>(lists_s + WARPS * QG * p.kk);
+    int* lists_i = reinterpret_cast<int*>(lists_s + WARPS * NQ * p.kk);
     if (NS < 2 || lists_addr + lists_bytes > end) {  // the host sizes kk so that this cannot happen
         if (threadIdx.x == 0) atomicExch(p.status, 2);
         return;
@@ -504,7 +512,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (!reg_lists)
-        for (int e = threadIdx.x; e < WARPS * QG * p.kk; e += blockDim.x) { lists_s[e] = -__builtin_huge_valf(); lists_i[e] = ID_NONE; }
+        for (int e = threadIdx.x; e < WARPS * NQ * p.kk; e += blockDim.x) { lists_s[e] = -__builtin_huge_valf(); lists_i[e] = ID_NONE; }
     __syncthreads();
     {
         const float* cf = reinterpret_cast<const float*>(smem_gen + cent_addr);
@@ -521,7 +529,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     const int64_t nstages = (nrec + SR - 1) / SR;
     RegLists RL;
 #pragma unroll
-    for (int jq = 0; jq < QG; jq++) { RL.s[jq] = -__builtin_huge_valf(); RL.i[jq] = ID_NONE; }
+    for (int jq = 0; jq < RQ; jq++) { RL.s[jq] = -__builtin_huge_valf(); RL.i[jq] = ID_NONE; }
 
     if (warp == WARPS) {
         // ---- producer: stage index blockIdx.x, + gridDim.x, ...; one bulk copy per stage ----
@@ -565,12 +573,14 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
 #pragma unroll
             for (int ks = 0; ks < C::KS; ks++) qf[ks] = src[ks * 32];
         }
-        float* ls = lists_s + (size_t)warp * QG * p.kk;
-        int* li = lists_i + (size_t)warp * QG * p.kk;
-        const int myq = grp * QG + t;                 // the query whose scores this lane receives
-        const float qsc = myq < p.nq ? p.qscale[myq] : 0.0f;
-        ScanThreshold thr{-__builtin_huge_valf(), ID_NONE};
-        const bool live = myq < p.nq;
+        float* ls = lists_s + (size_t)warp * NQ * p.kk;
+        int* li = lists_i + (size_t)warp * NQ * p.kk;
+        // PAIR: this lane receives the scores of queries 2t and 2t+1 of the group (MMA columns 2t, 2t+1);
+        // else of query t (columns 2t, 2t+1 = its fp16 hi and lo parts, added up)
+        const int qa = PAIR ? grp * NQ + 2 * t : grp * NQ + t, qb = qa + 1;
+        const bool live_a = qa < p.nq, live_b = PAIR && qb < p.nq;
+        const float qsc_a = live_a ? p.qscale[qa] : 0.0f, qsc_b = live_b ? p.qscale[qb] : 0.0f;
+        ScanThreshold thr_a{-__builtin_huge_valf(), ID_NONE}, thr_b{-__builtin_huge_valf(), ID_NONE};
         const int r0w = RPW * (warp % WPG);
         int s = warp / WPG - GROUPS;                  // slot of this group's current stage and its parity
         uint32_t par = 0;
@@ -600,41 +610,64 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
                     if (i0 + i >= mine) break;
                     uint2 nr;                          // norms of rows g and g + 8
                     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(nr.x), "=r"(nr.y) : "r"(rec + i * C::REC + C::KSEC + 8 * g));
-                    const float sc0 = (acc[i][0] + acc[i][1]) * (__uint_as_float(nr.x) * qsc);
-                    const float sc1 = (acc[i][2] + acc[i][3]) * (__uint_as_float(nr.y) * qsc);
+                    const float n0 = __uint_as_float(nr.x), n1 = __uint_as_float(nr.y);
+                    // candidate c: row (c >> 1 ? g + 8 : g), query (c & 1 ? qb : qa)
+                    const float sc[4] = {PAIR ? acc[i][0] * (n0 * qsc_a) : (acc[i][0] + acc[i][1]) * (n0 * qsc_a),
+                                         PAIR ? acc[i][1] * (n0 * qsc_b) : 0.0f,
+                                         PAIR ? acc[i][2] * (n1 * qsc_a) : (acc[i][2] + acc[i][3]) * (n1 * qsc_a),
+                                         PAIR ? acc[i][3] * (n1 * qsc_b) : 0.0f};
                     const int id0 = (int)(meta.x + r0w + i0 + i) * SCAN_TILE + g, id1 = id0 + 8;
-                    const bool ok0 = live && better(sc0, id0, thr.s, thr.i);
-                    const bool ok1 = live && better(sc1, id1, thr.s, thr.i);
-                    if (__any_sync(0xffffffffu, ok0 || ok1)) {
-                        if (reg_lists) {
+                    const bool any = (live_a && (better(sc[0], id0, thr_a.s, thr_a.i) || better(sc[2], id1, thr_a.s, thr_a.i))) ||
+                                     (live_b && (better(sc[1], id0, thr_b.s, thr_b.i) || better(sc[3], id1, thr_b.s, thr_b.i)));
+                    if (__any_sync(0xffffffffu, any)) {
 #pragma unroll 1
-                            for (int r = 0; r < 2; r++) {
-                                const float sc = r ? sc1 : sc0;
-                                const int id = r ? id1 : id0;
-                                uint32_t mask = __ballot_sync(0xffffffffu, live && better(sc, id, thr.s, thr.i));
+                        for (int c = 0; c < 4; c += PAIR ? 1 : 2) {
+                            const int col = c & 1, id = c >> 1 ? id1 : id0;
+                            const float v = c == 0 ? sc[0] : c == 1 ? sc[1] : c == 2 ? sc[2] : sc[3];
+                            const bool lv = col ? live_b : live_a;
+                            const ScanThreshold th = col ? thr_b : thr_a;
+                            const bool offer = lv && better(v, id, th.s, th.i);
+                            if (reg_lists) {
+                                uint32_t mask = __ballot_sync(0xffffffffu, offer);
                                 while (mask) {
                                     const int leader = __ffs(mask) - 1;
                                     mask &= mask - 1;
-                                    const float bs = __shfl_sync(0xffffffffu, sc, leader);
+                                    const float bs = __shfl_sync(0xffffffffu, v, leader);
                                     const int bid = __shfl_sync(0xffffffffu, id, leader);
-                                    switch (leader & 3) {
+                                    // (a candidate that no longer beats its list's tail finds no place: harmless)
+                                    switch (PAIR ? 2 * (leader & 3) + col : leader & 3) {
                                         case 0: reg_list_insert<0>(RL, p.kk, bs, bid, lane); break;
                                         case 1: reg_list_insert<1>(RL, p.kk, bs, bid, lane); break;
                                         case 2: reg_list_insert<2>(RL, p.kk, bs, bid, lane); break;
-                                        default: reg_list_insert<3>(RL, p.kk, bs, bid, lane); break;
+                                        case 3: reg_list_insert<3>(RL, p.kk, bs, bid, lane); break;
+                                        case 4: reg_list_insert<4>(RL, p.kk, bs, bid, lane); break;
+                                        case 5: reg_list_insert<5>(RL, p.kk, bs, bid, lane); break;
+                                        case 6: reg_list_insert<6>(RL, p.kk, bs, bid, lane); break;
+                                        default: reg_list_insert<7>(RL, p.kk, bs, bid, lane); break;
                                     }
                                 }
-                                // every lane's threshold = the tail of the list of the query it serves
-                                const float t0 = __shfl_sync(0xffffffffu, RL.s[0], p.kk - 1), t1 = __shfl_sync(0xffffffffu, RL.s[1], p.kk - 1);
-                                const float t2 = __shfl_sync(0xffffffffu, RL.s[2], p.kk - 1), t3 = __shfl_sync(0xffffffffu, RL.s[3], p.kk - 1);
-                                const int j0 = __shfl_sync(0xffffffffu, RL.i[0], p.kk - 1), j1 = __shfl_sync(0xffffffffu, RL.i[1], p.kk - 1);
-                                const int j2 = __shfl_sync(0xffffffffu, RL.i[2], p.kk - 1), j3 = __shfl_sync(0xffffffffu, RL.i[3], p.kk - 1);
-                                thr.s = t == 0 ? t0 : t == 1 ? t1 : t == 2 ? t2 : t3;
-                                thr.i = t == 0 ? j0 : t == 1 ? j1 : t == 2 ? j2 : j3;
+                            } else {
+                                thr_a = rec_scan_offer(ls, li, p.kk, v, id, offer, thr_a, lane);
                             }
-                        } else {
-                            thr = rec_scan_offer(ls, li, p.kk, sc0, id0, ok0, thr, lane);
-                            thr = rec_scan_offer(ls, li, p.kk, sc1, id1, live && better(sc1, id1, thr.s, thr.i), thr, lane);
+                        }
+                        if (reg_lists) {
+                            // every lane's thresholds = the tails of the lists of the two queries it serves
+                            float ts[RQ];
+                            int tj[RQ];
+#pragma unroll
+                            for (int jq = 0; jq < NQ; jq++) {
+                                ts[jq] = __shfl_sync(0xffffffffu, RL.s[jq], p.kk - 1);
+                                tj[jq] = __shfl_sync(0xffffffffu, RL.i[jq], p.kk - 1);
+                            }
+                            if (PAIR) {
+                                thr_a.s = t == 0 ? ts[0] : t == 1 ? ts[2] : t == 2 ? ts[4] : ts[6];
+                                thr_a.i = t == 0 ? tj[0] : t == 1 ? tj[2] : t == 2 ? tj[4] : tj[6];
+                                thr_b.s = t == 0 ? ts[1] : t == 1 ? ts[3] : t == 2 ? ts[5] : ts[7];
+                                thr_b.i = t == 0 ? tj[1] : t == 1 ? tj[3] : t == 2 ? tj[5] : tj[7];
+                            } else {
+                                thr_a.s = t == 0 ? ts[0] : t == 1 ? ts[1] : t == 2 ? ts[2] : ts[3];
+                                thr_a.i = t == 0 ? tj[0] : t == 1 ? tj[1] : t == 2 ? tj[2] : tj[3];
+                            }
                         }
                     }
                 }
@@ -648,34 +681,34 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     __syncthreads();                                  // nobody reads a stage any more: the ring may be reused
     if (reg_lists && warp < WARPS && lane < p.kk) {
 #pragma unroll
-        for (int jq = 0; jq < QG; jq++) {
-            lists_s[(warp * QG + jq) * p.kk + lane] = RL.s[jq];
-            lists_i[(warp * QG + jq) * p.kk + lane] = RL.i[jq];
+        for (int jq = 0; jq < NQ; jq++) {
+            lists_s[(warp * NQ + jq) * p.kk + lane] = RL.s[jq];
+            lists_i[(warp * NQ + jq) * p.kk + lane] = RL.i[jq];
         }
     }
     __syncthreads();
     if (p.combine) {
         // one list per CTA and query: rank every candidate among the CTA's WARPS * kk by counting
         const int per_q = WARPS * p.kk;
-        for (int idx = threadIdx.x; idx < QG * p.kk; idx += blockDim.x) {
-            const int jq = idx / p.kk, e = idx - jq * p.kk, q = grp * QG + jq;
+        for (int idx = threadIdx.x; idx < NQ * p.kk; idx += blockDim.x) {
+            const int jq = idx / p.kk, e = idx - jq * p.kk, q = grp * NQ + jq;
             if (q >= p.nq) continue;
             const int64_t o = ((int64_t)q * p.lists_per_query + blockIdx.x) * p.kk + e;
             p.cand_s[o] = -__builtin_huge_valf();
             p.cand_id[o] = ID_NONE;
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < QG * per_q; idx += blockDim.x) {
-            const int jq = idx / per_q, c = idx - jq * per_q, q = grp * QG + jq;
+        for (int idx = threadIdx.x; idx < NQ * per_q; idx += blockDim.x) {
+            const int jq = idx / per_q, c = idx - jq * per_q, q = grp * NQ + jq;
             if (q >= p.nq) continue;
             const int w = c / p.kk, e = c - w * p.kk;
-            const float s = lists_s[(w * QG + jq) * p.kk + e];
-            const int id = lists_i[(w * QG + jq) * p.kk + e];
+            const float s = lists_s[(w * NQ + jq) * p.kk + e];
+            const int id = lists_i[(w * NQ + jq) * p.kk + e];
             if (id == ID_NONE) continue;
             int rank = 0;
             for (int w2 = 0; w2 < WARPS; w2++) {
-                const float* s2 = lists_s + (w2 * QG + jq) * p.kk;
-                const int* i2 = lists_i + (w2 * QG + jq) * p.kk;
+                const float* s2 = lists_s + (w2 * NQ + jq) * p.kk;
+                const int* i2 = lists_i + (w2 * NQ + jq) * p.kk;
                 for (int e2 = 0; e2 < p.kk; e2++) rank += better(s2[e2], i2[e2], s, id) ? 1 : 0;
             }
             if (rank < p.kk) {
@@ -686,13 +719,13 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         }
     } else if (warp < WARPS) {
         const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
-        for (int jq = 0; jq < QG; jq++) {
-            const int q = grp * QG + jq;
+        for (int jq = 0; jq < NQ; jq++) {
+            const int q = grp * NQ + jq;
             if (q >= p.nq) break;
             const int64_t o = ((int64_t)q * p.lists_per_query + wid) * p.kk;
             for (int e = lane; e < p.kk; e += 32) {
-                p.cand_s[o + e] = lists_s[(warp * QG + jq) * p.kk + e];
-                p.cand_id[o + e] = lists_i[(warp * QG + jq) * p.kk + e];
+                p.cand_s[o + e] = lists_s[(warp * NQ + jq) * p.kk + e];
+                p.cand_id[o + e] = lists_i[(warp * NQ + jq) * p.kk + e];
             }
         }
     }
@@ -1039,12 +1072,17 @@ namespace tqb {
 // (rank by counting among 16 * kk entries); beyond that every consumer warp writes its own list.
 static bool rec_combine(int kk) { return 16 * kk <= 1024; }
 
+// Eight queries per pass (one fp16 column each) for calls with more than four queries whose candidate lists fit
+// the registers; else four (hi + lo columns): a single query then pays for no columns it does not use.
+static int rec_queries_per_pass(int kk, int nq) { return kk <= 32 && nq > QG ? RQ : QG; }
+
 static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
     ScanPlan pl{};
     pl.mma = true;
     pl.kk = scan_kk(k);
     pl.lists = sm_count() * (rec_combine(pl.kk) ? 1 : 16);
-    pl.ngroups = (nq + QG - 1) / QG;
+    const int per = rec_queries_per_pass(pl.kk, nq);
+    pl.ngroups = (nq + per - 1) / per;
     size_t off = 0;
     pl.off_status = off; off = s_align(off + 256);
     pl.off_qrot = off;   off = s_align(off + (size_t)nq * dim * 4);
@@ -1061,14 +1099,16 @@ static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
 template <int D, int BITS>
 static int launch_scan_records(const ScanParams& p, int ngroups, int grid_x, cudaStream_t st) {
     using C = RecScanCfg<D, BITS>;
+    const bool regl = p.kk <= 32, pair = rec_queries_per_pass(p.kk, p.nq) == RQ;
     // at least two stages must fit beside the table and the candidate lists
-    const size_t lists = (size_t)C::WARPS * QG * p.kk * 8;
+    const size_t lists = regl ? 0 : (size_t)C::WARPS * QG * p.kk * 8;
     const size_t worst = (C::KBYTE ? 2 * 65536 : C::LUT_BYTES + 4096) + C::FIXED + lists + 256;
     const size_t tail = worst < (size_t)C::DYN ? (size_t)C::DYN - worst : 0;
     const size_t stages = tail / C::STAGE + (C::KBYTE ? (65536 - 4096) / C::STAGE : 0);
     if (stages < 2 || worst >= (size_t)C::DYN)
         return fail(TQB_ERR_UNSUPPORTED, "scan_records_topk: k = %d leaves no room for the pipeline in shared memory", p.k);
-    auto kern = scan_records_kernel<D, BITS>;
+    auto kern = pair ? scan_records_kernel<D, BITS, RQ, true>
+                     : regl ? scan_records_kernel<D, BITS, QG, true> : scan_records_kernel<D, BITS, QG, false>;
     TQB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::DYN));
     dim3 grid(grid_x, ngroups);
     // (programmatic dependent launch: the table build overlaps the end of the preparation kernel)
@@ -1119,7 +1159,10 @@ extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t
     const int grid_x = sm_count();
     p.lists_per_query = grid_x * (p.combine ? 1 : 16);
 
-    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, 2);
+    if (rec_queries_per_pass(pl.kk, nq) == RQ)
+        scan_prepare_kernel<RQ><<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * RQ) * dim, st>>>(p, 2);
+    else
+        scan_prepare_kernel<QG><<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, 2);
     if (int e = check_launch("scan_prepare")) return e;
     int e = TQB_ERR_UNSUPPORTED;
 #define TQB_CASE(d, b) if (dim == d && bits == b) e = launch_scan_records<d, b>(p, pl.ngroups, grid_x, st);
@@ -1175,7 +1218,7 @@ extern "C" int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed
     const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(sm_count(), ceil_div(ntiles, SCAN_WARPS)));
     p.lists_per_query = gx * SCAN_WARPS;
 
-    scan_prepare_kernel<<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, pl.mma ? 1 : 0);
+    scan_prepare_kernel<QG><<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * QG) * dim, st>>>(p, pl.mma ? 1 : 0);
     if (int e = check_launch("scan_prepare")) return e;
 
     if (pl.mma) {
@@ -1248,11 +1291,11 @@ extern "C" int tqb_scan_topk_prod(const float* queries, int nq, const uint8_t* m
 
     // R q and S q: the same kernel twice (row j of the matrix times the query, float32, k ascending)
     const size_t psmem = sizeof(float) * (size_t)(1 + 2 * QG) * dim;
-    scan_prepare_kernel<<<pl.ngroups, 128, psmem, st>>>(p, 0);
+    scan_prepare_kernel<QG><<<pl.ngroups, 128, psmem, st>>>(p, 0);
     if (int e = check_launch("scan_prepare")) return e;
     ScanParams ps = p;
     ps.rot = S; ps.qrot = qsign;
-    scan_prepare_kernel<<<pl.ngroups, 128, psmem, st>>>(ps, 0);
+    scan_prepare_kernel<QG><<<pl.ngroups, 128, psmem, st>>>(ps, 0);
     if (int e = check_launch("scan_prepare")) return e;
 
     const size_t smem = sizeof(float) * ((size_t)dim * (1 << mb) + dim) + (size_t)SCAN_WARPS * p.kk * 8;
