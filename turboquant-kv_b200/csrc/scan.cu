@@ -21,7 +21,12 @@
 // it through that rounding: 8 within the few thousand rows one warp sees, 24 within the whole database.
 //
 // Dims 64 and 128 with 2..4 bits take the tensor-core path; every other supported shape takes
-// scan_generic_kernel (one row per lane, float32 table lookups) with the same list and merge code.
+// scan_generic_kernel (one row per lane, float32 table lookups) with the same list and merge code; so do
+// Prod-mode rows (tqb_scan_topk_prod), with a second term for the QJL sign plane.
+//
+// scan_records_kernel is the same scan over the key-only records of tiled_layout.cuh (what TurboQuantIndex
+// stores): one table lookup per two codes, one MMA per 16 dims on the centroids' fp16 values, and eight
+// queries per pass as single fp16 columns for batched calls (four as hi + lo pairs for short calls).
 #include "common.cuh"
 #include "decode_bits.cuh"
 #include "pipe.cuh"
