@@ -43,6 +43,9 @@ constexpr int SCAN_SELECT_MARGIN = 24;  // extra candidates the merge re-scores 
 constexpr int SCAN_WARPS = 8;
 constexpr int QG = 4;                   // queries per tensor-core pass over upstream rows (fp16 hi + lo query columns)
 constexpr int RQ = 8;                   // queries per pass over records (one fp16 column each: the pass only ranks)
+// A CTA of the record scan that merges its warps' lists emits its best REC_OUT_LISTS * kk candidates, as that many
+// sorted lists: with few CTAs per query the margin beyond k has to come from within the CTA.
+constexpr int REC_OUT_LISTS = 2;
 constexpr float CENT_SCALE = 1024.0f;   // keeps the fp16 lo parts out of the subnormal range
 constexpr float QUERY_SCALE = 16.0f;
 constexpr int ID_NONE = 0x7fffffff;
@@ -82,7 +85,8 @@ __device__ __forceinline__ bool better(float s, int id, float ts, int tid) {
 struct ScanParams {
     const uint8_t* packed; const float* norms; int64_t n;
     const uint8_t* records;             // non-null: the database as key-only 16-row records (tiled_layout.cuh)
-    int combine;                        // record scan: one merged candidate list per CTA instead of one per warp
+    int combine;                        // record scan: sorted candidate lists a CTA emits after merging its warps'
+                                        // (1 or REC_OUT_LISTS); 0 = every warp writes its own list
     int dim, bits, nq, k, kk;           // kk = scan_kk(k) candidates kept per list
     const float* rot; const float* cent; const float* queries;
     // Prod-mode rows (Algorithm 2): `packed` holds the MSE codes at `bits` (= bit_width - 1), plus one QJL sign
@@ -693,12 +697,13 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     }
     __syncthreads();
     if (p.combine) {
-        // one list per CTA and query: rank every candidate among the CTA's WARPS * kk by counting
-        const int per_q = WARPS * p.kk;
-        for (int idx = threadIdx.x; idx < NQ * p.kk; idx += blockDim.x) {
-            const int jq = idx / p.kk, e = idx - jq * p.kk, q = grp * NQ + jq;
+        // p.combine sorted lists per CTA and query (ranks 0..kk-1, kk..2kk-1, ...): every candidate is ranked
+        // among the CTA's WARPS * kk by counting
+        const int per_q = WARPS * p.kk, nout = p.combine * p.kk;
+        for (int idx = threadIdx.x; idx < NQ * nout; idx += blockDim.x) {
+            const int jq = idx / nout, e = idx - jq * nout, q = grp * NQ + jq;
             if (q >= p.nq) continue;
-            const int64_t o = ((int64_t)q * p.lists_per_query + blockIdx.x) * p.kk + e;
+            const int64_t o = ((int64_t)q * p.lists_per_query + (int64_t)blockIdx.x * p.combine) * p.kk + e;
             p.cand_s[o] = -__builtin_huge_valf();
             p.cand_id[o] = ID_NONE;
         }
@@ -716,8 +721,8 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
                 const int* i2 = lists_i + (w2 * NQ + jq) * p.kk;
                 for (int e2 = 0; e2 < p.kk; e2++) rank += better(s2[e2], i2[e2], s, id) ? 1 : 0;
             }
-            if (rank < p.kk) {
-                const int64_t o = ((int64_t)q * p.lists_per_query + blockIdx.x) * p.kk + rank;
+            if (rank < nout) {
+                const int64_t o = ((int64_t)q * p.lists_per_query + (int64_t)blockIdx.x * p.combine) * p.kk + rank;
                 p.cand_s[o] = s;
                 p.cand_id[o] = id;
             }
@@ -1085,7 +1090,7 @@ static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
     ScanPlan pl{};
     pl.mma = true;
     pl.kk = scan_kk(k);
-    pl.lists = sm_count() * (rec_combine(pl.kk) ? 1 : 16);
+    pl.lists = sm_count() * (rec_combine(pl.kk) ? REC_OUT_LISTS : 16);
     const int per = rec_queries_per_pass(pl.kk, nq);
     pl.ngroups = (nq + per - 1) / per;
     size_t off = 0;
@@ -1159,10 +1164,15 @@ extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t
     p.cand_s = reinterpret_cast<float*>(ws + pl.off_cs);
     p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
     p.out_scores = out_scores; p.out_ids = out_ids;
-    p.combine = rec_combine(pl.kk) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const int grid_x = sm_count();
-    p.lists_per_query = grid_x * (p.combine ? 1 : 16);
+    // CTAs per query group.  A CTA's fixed cost (lookup table, pipeline fill, ranking its warps' lists) is paid
+    // per (CTA, group), so a call with many groups gives each group few CTAs -- about four CTAs per SM in all,
+    // which still balances the tail -- and a call with one group (up to eight queries) takes every SM.
+    // Measured with 512 queries over 10 M rows: 148 CTAs per group 16.1 k QPS, 10 CTAs per group 38 k.
+    const int grid_x = (int)std::min<int64_t>(sm_count(), std::max<int64_t>(2, ceil_div((int64_t)4 * sm_count(), pl.ngroups)));
+    // with few CTAs per query the margin beyond k has to come from within the CTA: it then emits more lists
+    p.combine = rec_combine(pl.kk) ? (grid_x < 16 ? REC_OUT_LISTS : 1) : 0;
+    p.lists_per_query = grid_x * (p.combine ? p.combine : 16);
 
     if (rec_queries_per_pass(pl.kk, nq) == RQ)
         scan_prepare_kernel<RQ><<<pl.ngroups, 128, sizeof(float) * (size_t)(1 + 2 * RQ) * dim, st>>>(p, 2);

@@ -31,7 +31,7 @@ HEADER_SIZE = struct.calcsize(HEADER_FORMAT)
 MODE_MSE, MODE_PROD = 0, 1
 TQIX_MAGIC, TQIX_VERSION = 0x54514958, 1  # upstream csrc/core/turboquant_core.cpp:520-521
 
-_QUERY_CHUNK = 512      # queries per scan call (bounds the candidate workspace)
+_QUERY_CHUNK = 1024     # queries per scan call (bounds the candidate workspace)
 
 
 def merge_topk(scores: torch.Tensor, ids: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
