@@ -139,12 +139,14 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU arm (the reference arm and the cpu_baseline leg)
 # ------------------------------------------------------------------------------------------------
-def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice = slice(0, KV_HEADS), threads: int = 0):
+def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice = slice(0, KV_HEADS), threads: int = 0,
+               min_seconds: float = 0.0):
     """Dequantise-then-attend on the host for `sample_seqs` sequences x 8 KV heads of ONE layer.
 
     Returns (tokens_per_s extrapolated to the full step, seconds per sample step, cores, description,
     data) -- data holds the sample's inputs/outputs for the parity check of the GPU arm.  `heads` keeps a
-    slice of the KV heads (and their query heads) of the same sample: a rank's share under head sharding."""
+    slice of the KV heads (and their query heads) of the same sample: a rank's share under head sharding.
+    With `min_seconds` the timed loop goes on past `steps` until that much host time has been spent."""
     import numpy as np
 
     from oracle import build as obuild
@@ -193,12 +195,14 @@ def cpu_sample(ctx: int, sample_seqs: int, steps: int, warmup: int, heads: slice
     for _ in range(warmup):
         out = one_step()
     t0 = time.perf_counter()
-    for _ in range(steps):
+    done = 0
+    while done < steps or (time.perf_counter() - t0 < min_seconds and done < 1000):
         out = one_step()
-    dt = (time.perf_counter() - t0) / max(steps, 1)
+        done += 1
+    dt = (time.perf_counter() - t0) / max(done, 1)
     full_step = dt * LAYERS * BATCH / sample_seqs
     desc = (f"{sample_seqs} of {BATCH} sequences x {KV_HEADS} KV heads of 1 of {LAYERS} layers at context {ctx}, "
-            f"scaled by {LAYERS * BATCH // sample_seqs}")
+            f"scaled by {LAYERS * BATCH // sample_seqs}; {done} timed passes of {dt:.3f} s")
     data = dict(q=q, kp=kp, kn=kn, vp=vp, vn=vn, out=out, kind="reference" if use_ref else "port")
     return BATCH / full_step, dt, cores, desc, data
 
@@ -429,7 +433,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int) -> None:
             "hbm_gbs_whole_step": LAYERS * bytes_per_launch / (ms_step * 1e-3) / 1e9}
 
     if rank == 0 and world == 1 and not args.no_cpu:
-        value, dt, cores, desc, data = cpu_sample(ctx, args.cpu_seqs, 1, 0)
+        value, dt, cores, desc, data = cpu_sample(ctx, args.cpu_seqs, 1, 1, min_seconds=10.0)
         line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cores, "kind": data["kind"], "sample": desc,
                                 "sample_step_s": dt, "note": CPU_NOTE[data["kind"]]}
         line["parity"] = parity_check(torch, data, device)
