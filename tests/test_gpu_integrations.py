@@ -114,3 +114,70 @@ def test_hf_cache_prod_mode_matches_upstream_fixture(orc, golden):
     assert cache.memory_bytes() == 2 * 2 * 8 * ((2 * 8 + 8 + 8) + (3 * 8 + 8 + 8))
     with pytest.raises(RuntimeError):
         cache.decode_attention(torch.zeros(2, 2, 64, device="cuda"), 0)
+
+
+def _tiny_llama(dtype=torch.float16):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=512)
+    return LlamaForCausalLM(cfg).to("cuda", dtype).eval()
+
+
+def test_hf_model_runs_the_fused_kernel_through_the_attention_registry(monkeypatch):
+    """A stock transformers model with an attached cache: decode steps never rebuild the dense history
+    (upstream hf_integration.py:373-390 does), and the logits stay those of the dense contract up to the
+    quantisation of the one new token."""
+    from turboquant_kv import TurboQuantCache
+    from turboquant_kv import hf_integration as hf
+
+    model = _tiny_llama()
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 512, (2, 40), generator=gen).cuda()
+    steps = torch.randint(0, 512, (2, 6), generator=gen).cuda()
+
+    def run(cache, mask=None):
+        logits = []
+        with torch.no_grad():
+            out = model(input_ids=prompt, past_key_values=cache, attention_mask=mask, use_cache=True)
+            logits.append(out.logits[:, -1].float())
+            for t in range(steps.shape[1]):
+                if mask is not None:
+                    mask = torch.cat([mask, mask.new_ones(2, 1)], dim=1)
+                out = model(input_ids=steps[:, t:t + 1], past_key_values=cache, attention_mask=mask, use_cache=True)
+                logits.append(out.logits[:, -1].float())
+        return torch.stack(logits)
+
+    model.set_attn_implementation("sdpa")
+    dense_cache = TurboQuantCache(key_bits=4, value_bits=2, seed=42)
+    dense = run(dense_cache)
+
+    calls = {"fused": 0, "dense": 0}
+    real_decode, real_dense = hf._LayerQuantStore.decode_attention, hf._LayerQuantStore._dense
+    monkeypatch.setattr(hf._LayerQuantStore, "decode_attention",
+                        lambda self, *a, **k: (calls.__setitem__("fused", calls["fused"] + 1), real_decode(self, *a, **k))[1])
+    monkeypatch.setattr(hf._LayerQuantStore, "_dense",
+                        lambda self, *a, **k: (calls.__setitem__("dense", calls["dense"] + (self.seq_len > 0)), real_dense(self, *a, **k))[1])
+    fused_cache = TurboQuantCache(key_bits=4, value_bits=2, seed=42).attach(model)
+    assert model.config._attn_implementation == hf.ATTENTION_NAME
+    fused = run(fused_cache)
+    assert calls == {"fused": 2 * steps.shape[1], "dense": 0}        # 2 layers x 6 steps, no dequantisation at all
+    assert fused_cache.get_seq_length(0) == 46 and fused_cache.get_mask_sizes(1, 0) == (47, 0)
+    # layer 0 sees the same tokens in both runs: its packed records are the same bytes
+    for a, b in zip(dense_cache._layer_stores[0].export(), fused_cache._layer_stores[0].export()):
+        assert torch.equal(a, b)
+    assert torch.equal(dense[0], fused[0])                            # the prompt pass is the same computation
+    cos = torch.nn.functional.cosine_similarity(dense.flatten(1), fused.flatten(1), dim=1)
+    assert float(cos.min()) > 0.999, cos
+    assert float((dense - fused).abs().max()) < 0.05 * float(dense.abs().max())
+
+    # a padded batch keeps the dense contract (old tokens dequantised, new token exact): same logits as before attach
+    mask = torch.ones(2, 40, dtype=torch.long, device="cuda")
+    mask[1, :5] = 0
+    model.set_attn_implementation("sdpa")
+    want = run(TurboQuantCache(key_bits=4, value_bits=2, seed=42), mask)
+    calls.update(fused=0, dense=0)
+    got = run(TurboQuantCache(key_bits=4, value_bits=2, seed=42).attach(model), mask)
+    assert calls["fused"] == 0 and calls["dense"] > 0
+    assert torch.allclose(want, got, atol=2e-3, rtol=2e-3)

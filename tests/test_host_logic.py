@@ -206,3 +206,32 @@ def test_vllm_v1_backend_conforms_to_the_installed_interface():
         B.get_impl_cls()(32, 64, 0.125, 8, sliding_window=128)
     builder = B.get_builder_cls()(None, ["l0"], None, "cpu")
     assert builder.layer_names == ["l0"]
+
+
+def test_attention_function_registers_with_transformers_and_defaults_to_the_library_path():
+    """Without an attached cache the registered attention function is transformers' own SDPA call."""
+    pytest.importorskip("transformers")
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+
+    from turboquant_kv import hf_integration as hf
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    model = LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, 128, (2, 9))
+
+    def run():
+        cache = DynamicCache()
+        with torch.no_grad():
+            a = model(input_ids=ids[:, :8], past_key_values=cache, use_cache=True).logits
+            b = model(input_ids=ids[:, 8:], past_key_values=cache, use_cache=True).logits
+        return a, b
+
+    model.set_attn_implementation("sdpa")
+    want = run()
+    name = hf.register_turboquant_attention()
+    assert name == hf.ATTENTION_NAME == "turboquant"
+    model.set_attn_implementation(name)
+    got = run()
+    assert torch.equal(want[0], got[0]) and torch.equal(want[1], got[1])

@@ -8,12 +8,16 @@ Same constructor and ``DynamicCache`` surface as upstream ``turboquant_kv/hf_int
 tokens exact (hf_integration.py:383-390) -- but all sequences of a batch share one record store
 (batch * heads units of 16-token records, see csrc/tiled_layout.cuh) that the fused kernels write and
 read; the per-head, per-batch Python loops of upstream are gone.  ``decode_attention`` is the fast path that skips the dense
-round trip altogether for one-token steps.
+round trip altogether for one-token steps; ``TurboQuantCache.attach(model)`` routes a stock
+``transformers`` model there through the attention-function registry (``attn_implementation="turboquant"``),
+so that ``model(...)`` / ``generate`` never rebuild the dense history in a decode step -- the step upstream
+pays O(context) dequantisation for at hf_integration.py:373-390.
 """
 from __future__ import annotations
 
 import math
 import warnings
+import weakref
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -66,8 +70,9 @@ class _LayerQuantStore:
         self.seq_len += T
         self._len_dev += T
 
-    def _dense(self, which: str, dtype) -> torch.Tensor:
-        B, H, S, D = self.batch, self.num_heads, self.seq_len, self.head_dim
+    def _dense(self, which: str, dtype, upto: Optional[int] = None) -> torch.Tensor:
+        B, H, D = self.batch, self.num_heads, self.head_dim
+        S = self.seq_len if upto is None else upto
         if S == 0:
             return torch.zeros(B, H, 0, D, dtype=dtype, device=self.device)
         rm = N.RowMap(S, self.capacity, 1, 0, None, 1, None, 1)
@@ -75,11 +80,11 @@ class _LayerQuantStore:
         out = self.kv.dequantize(kp if which == "key" else vp, kn if which == "key" else vn, which, dtype)
         return out.view(B, H, S, D)
 
-    def get_keys(self, dtype=torch.float32) -> torch.Tensor:
-        return self._dense("key", dtype)
+    def get_keys(self, dtype=torch.float32, upto: Optional[int] = None) -> torch.Tensor:
+        return self._dense("key", dtype, upto)
 
-    def get_values(self, dtype=torch.float32) -> torch.Tensor:
-        return self._dense("value", dtype)
+    def get_values(self, dtype=torch.float32, upto: Optional[int] = None) -> torch.Tensor:
+        return self._dense("value", dtype, upto)
 
     def export(self):
         """Upstream-layout rows of everything stored: k_packed (B, H, S, pk), k_norms (B, H, S), v_packed, v_norms."""
@@ -205,6 +210,7 @@ class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
         self._layer_stores: Dict[int, _LayerQuantStore] = {}
         self._fp_key_cache: Dict[int, List[torch.Tensor]] = {}
         self._fp_value_cache: Dict[int, List[torch.Tensor]] = {}
+        self.fused_attention = False     # set by attach(): one-token updates return the new token only
 
     def _store(self, layer_idx: int, like: torch.Tensor) -> _LayerQuantStore:
         st = self._layer_stores.get(layer_idx)
@@ -226,6 +232,10 @@ class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
             self._fp_value_cache.setdefault(layer_idx, []).append(value_states)
             return torch.cat(self._fp_key_cache[layer_idx], dim=2), torch.cat(self._fp_value_cache[layer_idx], dim=2)
         st = self._store(layer_idx, key_states)
+        if self.fused_attention and key_states.shape[2] == 1 and isinstance(st, _LayerQuantStore):
+            # the attention function registered by attach() reads the packed records itself
+            st.append(key_states, value_states)
+            return key_states, value_states
         dt = key_states.dtype if key_states.dtype in (torch.float16, torch.bfloat16) else torch.float32
         k_old, v_old = st.get_keys(dt), st.get_values(dt)
         st.append(key_states, value_states)
@@ -244,6 +254,30 @@ class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
         squeeze = query.dim() == 4
         out = st.decode_attention(query[:, :, 0] if squeeze else query, scale)
         return out.unsqueeze(2) if squeeze else out
+
+    def attach(self, model) -> "TurboQuantCache":
+        """Route `model`'s attention through the packed cache: registers the ``"turboquant"`` attention
+        function with ``transformers``, selects it on the model and ties this cache to every attention module
+        (the registry's functions receive the module, not the cache).  Afterwards a one-token ``update`` stores
+        the token and returns it alone, and the attention function runs the fused kernel over the packed
+        records; longer updates, protected and Prod-mode layers and padded batches keep the dense contract of
+        ``update``.  The new token is attended in its quantised form (as ``QuantizedKVCache.decode_attention``
+        does, cache.py:200-263), where the dense contract keeps it exact."""
+        register_turboquant_attention()
+        for mod in model.modules():
+            if hasattr(mod, "layer_idx") and hasattr(mod, "q_proj"):
+                mod._turboquant_cache = weakref.ref(self)
+        if hasattr(model, "set_attn_implementation"):
+            model.set_attn_implementation(ATTENTION_NAME)
+        else:  # pragma: no cover
+            model.config._attn_implementation = ATTENTION_NAME
+        self.fused_attention = True
+        return self
+
+    def get_mask_sizes(self, query_length, layer_idx: int = 0) -> Tuple[int, int]:
+        """(kv_length, kv_offset) of the mask a layer call needs: everything stored plus the new tokens."""
+        new = int(query_length.shape[0]) if isinstance(query_length, torch.Tensor) else int(query_length)
+        return self.get_seq_length(layer_idx) + new, 0
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         if layer_idx < self._protected_layers:
@@ -299,4 +333,47 @@ class TurboQuantCache(_DynamicCache):  # type: ignore[misc]
             yield self[idx]
 
 
-__all__ = ["TurboQuantCache"]
+ATTENTION_NAME = "turboquant"
+
+
+def turboquant_attention_forward(module, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                 attention_mask: Optional[torch.Tensor] = None, dropout: float = 0.0,
+                                 scaling: Optional[float] = None, **kwargs):
+    """Attention function for ``transformers``' registry (same signature and return as its
+    ``sdpa_attention_forward``: output (batch, q_len, q_heads, head_dim), no weights).
+
+    query (batch, q_heads, q_len, head_dim).  For a one-token step on a layer whose cache was attached with
+    ``TurboQuantCache.attach`` the fused kernel attends over the packed records; `key` / `value` then hold the
+    new token only.  With an attention mask (padded batches) the old tokens are dequantised here instead and the
+    call, like every other one, goes to the library's SDPA function."""
+    from transformers.integrations.sdpa_attention import sdpa_attention_forward
+
+    ref = getattr(module, "_turboquant_cache", None)
+    cache = ref() if ref is not None else None
+    layer_idx = getattr(module, "layer_idx", None)
+    st = cache._layer_stores.get(layer_idx) if cache is not None and cache.fused_attention else None
+    if isinstance(st, _LayerQuantStore) and query.shape[2] == 1 and key.shape[2] != st.seq_len:
+        # update() returned the new token alone
+        if attention_mask is None and dropout == 0.0:
+            out = st.decode_attention(query[:, :, 0], scaling)
+            return out.unsqueeze(1).to(query.dtype), None
+        dt = key.dtype if key.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        key = torch.cat([st.get_keys(dt, st.seq_len - 1).to(key.dtype), key], dim=2)
+        value = torch.cat([st.get_values(dt, st.seq_len - 1).to(value.dtype), value], dim=2)
+    return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+
+
+def register_turboquant_attention() -> str:
+    """Register ``turboquant_attention_forward`` (and SDPA-style masks for it) with ``transformers``; returns the
+    name to pass as ``attn_implementation``."""
+    if not _TRANSFORMERS_AVAILABLE:
+        raise ImportError("transformers is required for register_turboquant_attention")
+    from transformers import AttentionInterface
+    from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
+
+    AttentionInterface.register(ATTENTION_NAME, turboquant_attention_forward)
+    AttentionMaskInterface.register(ATTENTION_NAME, sdpa_mask)
+    return ATTENTION_NAME
+
+
+__all__ = ["TurboQuantCache", "turboquant_attention_forward", "register_turboquant_attention", "ATTENTION_NAME"]
