@@ -1106,6 +1106,26 @@ static ScanPlan plan_scan_records(int nq, int dim, int bits, int k) {
     return pl;
 }
 
+// CTAs per query group.  A CTA has an SM to itself and all CTAs of a launch take equally long, so a launch
+// costs (waves of CTAs) x (time of one CTA), and a CTA's time is its share of the records plus a fixed part:
+// the lookup table, the pipeline fill and above all the candidate lists of its warps, which take insertions
+// until their thresholds have tightened (about k ln(rows) of them whatever the share).  Measured with groups
+// of eight queries, that part is worth REC_CTA_FIXED records of streaming (0.45 ms against 33 ns per record).
+// One group therefore takes every SM, and many groups take few, large CTAs each in as few full waves as
+// possible: 5 groups over 4 M rows 1.51 ms with 118 CTAs each, 0.85 ms with 29; 64 groups 5.9 ms with 9 CTAs
+// each, 4.8 ms with 2.  At least two CTAs per group keep the candidate margin the exact re-scoring relies on.
+constexpr int64_t REC_CTA_FIXED = 14000;
+static int rec_ctas_per_group(int ngroups, int64_t nrec, int sms) {
+    int best = 2;
+    int64_t best_cost = INT64_MAX;
+    for (int x = 2; x <= sms; ++x) {
+        const int64_t waves = ceil_div((int64_t)ngroups * x, (int64_t)sms);
+        const int64_t cost = waves * (REC_CTA_FIXED + ceil_div(nrec, (int64_t)x));
+        if (cost < best_cost) { best_cost = cost; best = x; }
+    }
+    return best;
+}
+
 template <int D, int BITS>
 static int launch_scan_records(const ScanParams& p, int ngroups, int grid_x, cudaStream_t st) {
     using C = RecScanCfg<D, BITS>;
@@ -1165,11 +1185,7 @@ extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t
     p.cand_id = reinterpret_cast<int*>(ws + pl.off_ci);
     p.out_scores = out_scores; p.out_ids = out_ids;
     cudaStream_t st = (cudaStream_t)stream;
-    // CTAs per query group.  A CTA's fixed cost (lookup table, pipeline fill, ranking its warps' lists) is paid
-    // per (CTA, group), so a call with many groups gives each group few CTAs -- about four CTAs per SM in all,
-    // which still balances the tail -- and a call with one group (up to eight queries) takes every SM.
-    // Measured with 512 queries over 10 M rows: 148 CTAs per group 16.1 k QPS, 10 CTAs per group 38 k.
-    const int grid_x = (int)std::min<int64_t>(sm_count(), std::max<int64_t>(2, ceil_div((int64_t)4 * sm_count(), pl.ngroups)));
+    const int grid_x = rec_ctas_per_group(pl.ngroups, ceil_div(n, (int64_t)16), sm_count());
     // with few CTAs per query the margin beyond k has to come from within the CTA: it then emits more lists
     p.combine = rec_combine(pl.kk) ? (grid_x < 16 ? REC_OUT_LISTS : 1) : 0;
     p.lists_per_query = grid_x * (p.combine ? p.combine : 16);
