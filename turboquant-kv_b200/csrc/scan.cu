@@ -392,7 +392,8 @@ struct RecScanCfg {
     static constexpr int THREADS = (WARPS + 1) * 32;         // + the producer warp
     static constexpr int DYN = 227 * 1024;
     static constexpr int MAX_NS = 8;
-    static constexpr int FIXED = 8 * (8 + 8 + 8) + 64;       // barriers, stage headers, centroids
+    static constexpr int SHARE_OFF = 8 * (8 + 8 + 8) + 64;   // barriers, stage headers, centroids come first
+    static constexpr int FIXED = SHARE_OFF + 8 * (WARPS + 1) * RQ;   // + shared thresholds (one key per warp and query, one per query)
 };
 
 // NT records at once: acc[i] = this lane's part of the 16 x 8 score tile of record i.
@@ -449,6 +450,20 @@ __device__ __forceinline__ void reg_list_insert(RegLists& L, int kk, float s, in
 // the instruction cache: lanes flagged `ok` offer (sc, id) to the list of the query their lane serves
 // (query = lane % 4).  Returns the caller's updated threshold (the tail of its query's list).
 struct ScanThreshold { float s; int i; };
+// (score, id) as one 64-bit key whose unsigned order is the order of better(): larger key = better candidate
+__device__ __forceinline__ unsigned long long thr_key(float s, int id) {
+    uint32_t b = __float_as_uint(s + 0.0f);          // (-0 becomes +0: better() holds them equal)
+    b ^= (b >> 31) ? 0xffffffffu : 0x80000000u;
+    return ((unsigned long long)b << 32) | (uint32_t)(ID_NONE - id);
+}
+__device__ __forceinline__ ScanThreshold key_thr(unsigned long long k) {
+    uint32_t b = (uint32_t)(k >> 32);
+    b ^= (b >> 31) ? 0x80000000u : 0xffffffffu;
+    return {__uint_as_float(b), ID_NONE - (int)(uint32_t)k};
+}
+__device__ __forceinline__ ScanThreshold thr_max(ScanThreshold a, ScanThreshold b) {
+    return better(b.s, b.i, a.s, a.i) ? b : a;
+}
 __device__ __noinline__ ScanThreshold rec_scan_offer(float* ls, int* li, int kk, float sc, int id, bool ok,
                                                      ScanThreshold thr, int lane) {
     const int t = lane & 3;
@@ -492,6 +507,15 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     }
     misc = tab_base + C::LUT_BYTES;
     const uint32_t full_addr = misc, empty_addr = misc + 64, meta_addr = misc + 128, cent_addr = misc + 192;
+    // Thresholds shared by the CTA's warps.  A CTA emits its best `nout` candidates per query, so a candidate
+    // below the r-th best of EVERY warp (r = ceil(nout / WARPS): WARPS * r candidates of distinct rows are
+    // better) cannot be among them.  Each warp publishes its r-th best per query (warp_key), the minimum over the
+    // warps is the CTA's threshold (cta_key), far tighter than the tail of a warp's own list while the lists
+    // fill.  Keys only ever grow; a stale or overwritten smaller value is a looser, still valid bound.
+    unsigned long long* const warp_key = reinterpret_cast<unsigned long long*>(smem_raw - base + misc + C::SHARE_OFF);
+    unsigned long long* const cta_key = warp_key + WARPS * RQ;
+    const bool share = REGL && p.combine > 0;
+    const int share_lane = share ? (p.combine * p.kk + WARPS - 1) / WARPS - 1 : 0;
     // Candidate lists of up to 32 entries live in registers while the rows stream; they are written to
     // shared memory only once the stream has ended, over the then idle second part of the ring.
     constexpr bool reg_lists = REGL;                 // (the host picks REGL = (kk <= 32))
@@ -515,6 +539,7 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
     if (threadIdx.x < 16)
         reinterpret_cast<float*>(smem_gen + cent_addr)[threadIdx.x] =
             threadIdx.x < (1 << BITS) ? p.cent[threadIdx.x] * CENT_SCALE : 0.0f;
+    if (threadIdx.x < (WARPS + 1) * RQ) warp_key[threadIdx.x] = thr_key(-__builtin_huge_valf(), ID_NONE);
     if (threadIdx.x < C::MAX_NS) {
         mbar_init(full_addr + threadIdx.x * 8, 1);
         mbar_init(empty_addr + threadIdx.x * 8, WPG);
@@ -593,9 +618,34 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
         const int r0w = RPW * (warp % WPG);
         int s = warp / WPG - GROUPS;                  // slot of this group's current stage and its parity
         uint32_t par = 0;
+        const int ja = PAIR ? 2 * t : t;              // this lane's queries within the group
+        bool fresh = false;                           // this warp's lists changed since it last looked at the others'
         for (;;) {
             s += GROUPS;
             if (s >= NS) { s -= NS; par ^= 1; }
+            if (share && fresh) {
+                // CTA threshold of each query = the minimum over the warps' published keys
+                fresh = false;
+                const int w = lane & 15, half = lane >> 4;
+                unsigned long long m[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) m[j] = warp_key[w * RQ + (half * 4 + j) % NQ];
+#pragma unroll
+                for (int off = 8; off; off >>= 1)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const unsigned long long o = __shfl_xor_sync(0xffffffffu, m[j], off);
+                        m[j] = o < m[j] ? o : m[j];
+                    }
+                if (w == 0 && half * 4 < NQ) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        if (m[j] > cta_key[half * 4 + j]) cta_key[half * 4 + j] = m[j];
+                }
+                __syncwarp();
+                thr_a = thr_max(thr_a, key_thr(cta_key[ja]));
+                if (PAIR) thr_b = thr_max(thr_b, key_thr(cta_key[ja + 1]));
+            }
             const bool ok = mbar_wait(full_addr + 8 * s, par);
             if (!__all_sync(0xffffffffu, ok)) {
                 if (lane == 0) atomicExch(p.status, 1);
@@ -676,6 +726,15 @@ __global__ void __launch_bounds__(RecScanCfg<D, BITS>::THREADS, 1) scan_records_
                             } else {
                                 thr_a.s = t == 0 ? ts[0] : t == 1 ? ts[1] : t == 2 ? ts[2] : ts[3];
                                 thr_a.i = t == 0 ? tj[0] : t == 1 ? tj[1] : t == 2 ? tj[2] : tj[3];
+                            }
+                            if (share) {
+                                fresh = true;
+                                if (lane == share_lane) {
+#pragma unroll
+                                    for (int jq = 0; jq < NQ; jq++) warp_key[warp * RQ + jq] = thr_key(RL.s[jq], RL.i[jq]);
+                                }
+                                thr_a = thr_max(thr_a, key_thr(cta_key[ja]));
+                                if (PAIR) thr_b = thr_max(thr_b, key_thr(cta_key[ja + 1]));
                             }
                         }
                     }
