@@ -89,7 +89,7 @@ def test_v1_backend_prefill_decode_and_mixed_batches(orc, dim, kb, vb):
         run([(20, 37), (5, 6), (64, 65)])                   # mixed: chunked prefill + two decodes
         run([(37, 38), (6, 7), (65, 66)])                   # pure decode batch -> fused paged kernel
         run([(38, 40), (7, 8), (66, 67)])                   # a two-token query (speculative verification shape)
-        # the library fallback for oversized expansions gives the same answers
+        # oversized expansions take several launches (here: one per query token) and give the same answers
         K2 = [k.clone() for k in K]
         impl.MAX_EXPANDED_TABLE = 0
         cache.zero_()

@@ -17,8 +17,8 @@ so vLLM's block ids and slot mapping address it directly.  Requests with one new
 fused paged decode kernel.  Batches with several new tokens per request (prefill, chunked prefill,
 speculative verification) run the same kernel with every query token as a sequence of its own (its
 request's block-table row, its causal prefix as the length): nothing is dequantised, but every token
-streams its prefix again -- right for short chunks, quadratic for long prompts.  Beyond a size limit a
-library path (export + dequantise + ``scaled_dot_product_attention``) takes over.
+streams its prefix again -- right for short chunks, quadratic for long prompts.  Very large calls are split
+into several launches of that kernel; there is no library attention path.
 
 vLLM is imported when this module is imported; nothing else in the package depends on it.
 """
@@ -141,7 +141,7 @@ class TurboQuantV1Impl(AttentionImpl[TurboQuantV1Metadata]):
         self.kv_cache_dtype = kv_cache_dtype
         self._kv: Optional[PackedKVStore] = None
 
-    # largest (tokens x blocks per request) table the multi-token path materialises (int32 entries)
+    # largest (tokens x blocks per request) table the multi-token path materialises per launch (int32 entries)
     MAX_EXPANDED_TABLE = 1 << 26
 
     def _store(self, device) -> PackedKVStore:
@@ -195,45 +195,25 @@ class TurboQuantV1Impl(AttentionImpl[TurboQuantV1Metadata]):
 
         # 2b. requests with several new tokens (prefill chunks, speculative verification): every query token is
         # handed to the fused kernel as a sequence of its own -- the request's block-table row and its causal
-        # prefix as the length -- so nothing is dequantised.  (Each token streams its prefix again; a kernel
-        # that shares the stream between the tokens of a request is not part of this build.)
-        if n * bt.shape[1] <= self.MAX_EXPANDED_TABLE:
-            qsl = md.query_start_loc.to(torch.int64)
-            qlens = qsl[1:md.num_reqs + 1] - qsl[:md.num_reqs]
-            req = torch.repeat_interleave(torch.arange(md.num_reqs, device=q.device), qlens, output_size=n)
-            if md.causal:
-                pos = torch.arange(n, device=q.device) - qsl[req]
-                tok_lens = (lens.to(torch.int64)[req] - qlens[req] + pos + 1).to(torch.int32)
-            else:
-                tok_lens = lens[req]
-            tok_tables = bt[req].contiguous()
-            res = kv.decode_attention(pool, q, HK, tok_lens.contiguous(), md.max_seq_len, block_tables=tok_tables,
-                                      block_size=block_size, scale=self.scale)
-            out.copy_(res)
-            return output
-
-        # 2c. fallback for very large expansions: dequantise the request's rows, causal attention in torch
-        starts = md.query_start_loc_cpu.tolist()
-        lens_cpu = lens.cpu().tolist()
-        group = H // HK
-        for r in range(md.num_reqs):
-            q0, q1 = starts[r], starts[r + 1]
-            S, T = lens_cpu[r], q1 - q0
-            if T == 0:
-                continue
-            tok = torch.arange(S, device=q.device, dtype=torch.int64)
-            tslots = bt[r, tok // block_size].to(torch.int64) * block_size + tok % block_size
-            rmr = N.RowMap(HK, 0, 0, 0, None, 1, N.ptr(tslots), block_size)
-            kp, kn, vp, vn = kv.export_rows(pool, S * HK, rmr)
-            kd = kv.dequantize(kp, kn, "key", torch.float32).view(S, HK, D).transpose(0, 1)     # (HK, S, D)
-            vd = kv.dequantize(vp, vn, "value", torch.float32).view(S, HK, D).transpose(0, 1)
-            qr = q[q0:q1].float().transpose(0, 1)                                                # (H, T, D)
-            kd, vd = kd.repeat_interleave(group, dim=0), vd.repeat_interleave(group, dim=0)
-            mask = None
-            if md.causal:   # query i is token S - T + i of the request
-                mask = tok[None, :] <= (S - T + torch.arange(T, device=q.device))[:, None]
-            o = torch.nn.functional.scaled_dot_product_attention(qr, kd, vd, attn_mask=mask, scale=self.scale)
-            out[q0:q1] = o.transpose(0, 1).to(out.dtype)
+        # prefix as the length -- so nothing is dequantised and no library attention runs.  The per-token copy of
+        # the block table is built for at most MAX_EXPANDED_TABLE entries at a time: larger calls take several
+        # launches.  (Each token streams its prefix again; a kernel that shares the stream between the tokens
+        # of a request is not part of this build.)
+        qsl = md.query_start_loc.to(torch.int64)
+        qlens = qsl[1:md.num_reqs + 1] - qsl[:md.num_reqs]
+        req = torch.repeat_interleave(torch.arange(md.num_reqs, device=q.device), qlens, output_size=n)
+        if md.causal:
+            pos = torch.arange(n, device=q.device) - qsl[req]
+            tok_lens = (lens.to(torch.int64)[req] - qlens[req] + pos + 1).to(torch.int32)
+        else:
+            tok_lens = lens[req].to(torch.int32)
+        step = max(1, self.MAX_EXPANDED_TABLE // max(1, bt.shape[1]))
+        for c0 in range(0, n, step):
+            c1 = min(n, c0 + step)
+            res = kv.decode_attention(pool, q[c0:c1].contiguous(), HK, tok_lens[c0:c1].contiguous(), md.max_seq_len,
+                                      block_tables=bt[req[c0:c1]].contiguous(), block_size=block_size,
+                                      scale=self.scale)
+            out[c0:c1].copy_(res)
         return output
 
 
