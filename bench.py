@@ -541,6 +541,32 @@ def extras(torch, dist, args, rank: int, world: int, device) -> dict:
         res["paged_decode_llama3_8b"] = {"error": repr(exc)}
     torch.cuda.empty_cache()
 
+    # ---- multi-token requests (prefill chunks) as the vLLM v1 backend runs them: one pass per query token ----
+    if world == 1:
+        def timed_prefill(fn):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / 5
+
+        try:
+            ms, nbytes, status, finite = prefill_per_token(torch, device, 8, 32, 8, 1024, timed_prefill)
+            res["prefill_attention_per_token_passes"] = {
+                "requests": 8, "new_tokens_per_request": 1024, "head_dim": 128, "kv_heads": 8, "q_heads": 32,
+                "ms_per_layer_call": ms, "prefill_tokens_per_s_per_layer": 8 * 1024 / ms * 1e3,
+                "record_bytes_read": nbytes, "hbm_gbs": nbytes / ms / 1e6, "status": status, "finite": finite,
+                "note": "no prefill kernel in this build: every query token is a sequence of its own for the paged "
+                        "decode kernel (65,536 work items of 5 to 27 us of set-up each, the prefix streamed again "
+                        "per token); a kernel sharing one stream per request would read 1/512 of these bytes"}
+        except Exception as exc:
+            res["prefill_attention_per_token_passes"] = {"error": repr(exc)}
+        torch.cuda.empty_cache()
+
     # ---- quantise: MSE 4-bit round trip (65,536 unit vectors, d = 128) and Prod 3-bit estimator ----
     if rank == 0:
         from turboquant_kv import dequantize_mse, dequantize_prod, quantize_mse, quantize_prod
@@ -876,12 +902,42 @@ def paged_layer(torch, device, kvh: int, qh: int, ctx: int, timed, contiguous: b
     return ms, nbytes, kv.status(), bool(torch.isfinite(o.float()).all())
 
 
+def prefill_per_token(torch, device, kvh: int, qh: int, reqs: int, tokens: int, timed):
+    """Causal attention of `reqs` requests x `tokens` new tokens over their own packed K/V (head_dim 128, K4/V3,
+    16-token pages), run the way the vLLM v1 backend runs multi-token requests: every query token is a sequence of
+    its own -- its request's block-table row, its causal prefix as the length -- in one launch of the paged decode
+    kernel.  Token t of a request streams t + 1 records' worth of tokens, so the launch reads (tokens + 1) / 2
+    times what a kernel sharing one stream per request would.  Random codes (timing only).
+    Returns (ms per call, record bytes read, status word, output finite)."""
+    from turboquant_kv.kvstore import PackedKVStore
+
+    dim, bs = 128, 16
+    kv = PackedKVStore(dim, 4, 3, 42, "dense_qr", device)
+    pages = reqs * (tokens // bs)
+    gen = torch.Generator(device=device).manual_seed(2)
+    pool = torch.randint(0, 256, (pages * kvh, bs // 16, kv.record_bytes), dtype=torch.uint8, device=device,
+                         generator=gen)
+    norms = pool.view(pages * kvh, -1)[:, -128:].view(torch.float32)
+    norms.copy_(torch.rand(norms.shape, device=device, generator=gen) * 8 + 4)
+    tables = torch.randperm(pages, device=device, generator=gen).to(torch.int32).view(reqs, tokens // bs)
+    req = torch.arange(reqs, device=device).repeat_interleave(tokens)
+    tok_lens = (torch.arange(tokens, device=device, dtype=torch.int32) + 1).repeat(reqs).contiguous()
+    tok_tables = tables[req].contiguous()
+    q = torch.randn(reqs * tokens, qh, dim, device=device, generator=gen).bfloat16()
+    o = torch.empty_like(q)
+    ms = timed(lambda: kv.decode_attention(pool, q, kvh, tok_lens, tokens, block_tables=tok_tables, block_size=bs, out=o))
+    nbytes = reqs * kvh * (tokens * (tokens + 1) // 2) * (64 + 48 + 8)
+    return ms, nbytes, kv.status(), bool(torch.isfinite(o.float()).all())
+
+
 def run_case(args) -> None:
     """Single-kernel cases for profilers: a few eager launches of one hot kernel, timed with CUDA events.
 
     decode    one layer-call = decode_attention over `--layers` layers of the decode workload
     paged     one layer-call of paged decode attention, Llama-3-8B geometry (head_dim 128, K4/V3, 16-token
               pages, batch 64, context `--ctx`), random codes
+    prefill   causal attention of `--prefill-reqs` x `--prefill-tokens` new tokens, one pass of the paged decode
+              kernel per query token (the multi-token path of the vLLM v1 backend)
     scan      single-query passes of the 4-bit index scan over `--scan-rows` rows
     quantize  quantize_mse of `--rows` float32 vectors of dim 128 at 4 bits
     """
@@ -921,6 +977,11 @@ def run_case(args) -> None:
         ms, nbytes, status, finite = paged_layer(torch, device, 8, 32, args.ctx, timed, args.contiguous)
         out.update(contiguous=bool(args.contiguous), ms_per_layer_call=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"],
                    status=status, finite=finite)
+    elif args.case == "prefill":
+        ms, nbytes, status, finite = prefill_per_token(torch, device, 8, 32, args.prefill_reqs, args.prefill_tokens, timed)
+        out.update(requests=args.prefill_reqs, tokens=args.prefill_tokens, ms_per_layer_call=ms, bytes=nbytes,
+                   gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm_gbs"], status=status, finite=finite,
+                   prefill_tokens_per_s_per_layer=args.prefill_reqs * args.prefill_tokens / ms * 1e3)
     elif args.case == "scan":
         from turboquant_kv import TurboQuantIndex
 
@@ -949,7 +1010,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["decode", "paged", "scan", "quantize"],
+    ap.add_argument("--case", default=None, choices=["decode", "paged", "prefill", "scan", "quantize"],
                     help="run one single-kernel case (for profilers) instead of the benchmark")
     ap.add_argument("--layers", type=int, default=LAYERS, help="--case decode: layers to build")
     ap.add_argument("--rows", type=int, default=65536, help="--case quantize: vectors")
@@ -969,6 +1030,8 @@ def main() -> None:
     ap.add_argument("--scan-parity-queries", type=int, default=32,
                     help="queries searched again with the upstream C++ core over all rows (1 GPU only; 0 = skip)")
     ap.add_argument("--paged-ctx", type=int, default=32768, help="context of the paged 32-layer configuration")
+    ap.add_argument("--prefill-reqs", type=int, default=8, help="--case prefill: requests")
+    ap.add_argument("--prefill-tokens", type=int, default=1024, help="--case prefill: new tokens per request (multiple of 16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
