@@ -235,3 +235,6 @@ def test_attention_function_registers_with_transformers_and_defaults_to_the_libr
     model.set_attn_implementation(name)
     got = run()
     assert torch.equal(want[0], got[0]) and torch.equal(want[1], got[1])
+    # an empty cache announces masks of the size of the new tokens (DynamicCache's convention)
+    assert hf.TurboQuantCache().get_mask_sizes(5, 0) == (5, 0)
+    assert hf.TurboQuantCache().get_mask_sizes(torch.arange(3), 1) == (3, 0)
