@@ -181,3 +181,11 @@ def test_hf_model_runs_the_fused_kernel_through_the_attention_registry(monkeypat
     got = run(TurboQuantCache(key_bits=4, value_bits=2, seed=42).attach(model), mask)
     assert calls["fused"] == 0 and calls["dense"] > 0
     assert torch.allclose(want, got, atol=2e-3, rtol=2e-3)
+
+    # generate() drives the same path: every decode step of every layer runs the fused kernel
+    calls.update(fused=0, dense=0)
+    cache = TurboQuantCache(key_bits=4, value_bits=2, seed=42).attach(model)
+    tokens = model.generate(input_ids=prompt, attention_mask=torch.ones_like(prompt), past_key_values=cache,
+                            max_new_tokens=5, min_new_tokens=5, do_sample=False, pad_token_id=0)
+    assert tokens.shape == (2, 45) and cache.get_seq_length(0) == 44
+    assert calls == {"fused": 2 * 4, "dense": 0}
