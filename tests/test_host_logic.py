@@ -238,3 +238,73 @@ def test_attention_function_registers_with_transformers_and_defaults_to_the_libr
     # an empty cache announces masks of the size of the new tokens (DynamicCache's convention)
     assert hf.TurboQuantCache().get_mask_sizes(5, 0) == (5, 0)
     assert hf.TurboQuantCache().get_mask_sizes(torch.arange(3), 1) == (3, 0)
+
+
+def test_attention_function_dispatch_rules_with_a_stand_in_store():
+    """Which path the registered attention function takes: the fused kernel for a one-token step on an attached,
+    quantised layer without a mask; old tokens dequantised + the new token exact when a mask is given; the plain
+    library call for everything else (prefill, a detached module)."""
+    pytest.importorskip("transformers")
+    import weakref
+
+    from turboquant_kv import hf_integration as hf
+
+    B, HK, G, S, D = 2, 2, 2, 7, 16
+    gen = torch.Generator().manual_seed(0)
+    old_k, old_v = torch.randn(B, HK, S - 1, D, generator=gen), torch.randn(B, HK, S - 1, D, generator=gen)
+    marker = torch.full((B, HK * G, D), 3.0)
+
+    class Store(hf._LayerQuantStore):
+        def __init__(self):                      # no device buffers: only what the attention function touches
+            self.seq_len, self.asked = S, []
+
+        def get_keys(self, dtype=torch.float32, upto=None):
+            self.asked.append(("k", upto))
+            return old_k[:, :, :upto].to(dtype)
+
+        def get_values(self, dtype=torch.float32, upto=None):
+            self.asked.append(("v", upto))
+            return old_v[:, :, :upto].to(dtype)
+
+        def decode_attention(self, query, scale):
+            self.asked.append(("fused", tuple(query.shape), scale))
+            return marker
+
+    class Cache:
+        fused_attention = True
+
+        def __init__(self):
+            self._layer_stores = {0: Store()}
+
+    class Module(torch.nn.Module):
+        layer_idx, num_key_value_groups = 0, G
+
+    cache, mod = Cache(), Module()
+    mod._turboquant_cache = weakref.ref(cache)
+    q = torch.randn(B, HK * G, 1, D, generator=gen)
+    k_new, v_new = torch.randn(B, HK, 1, D, generator=gen), torch.randn(B, HK, 1, D, generator=gen)
+
+    out, weights = hf.turboquant_attention_forward(mod, q, k_new, v_new, None, scaling=0.25)
+    assert weights is None and out.shape == (B, 1, HK * G, D) and torch.equal(out[:, 0], marker)
+    assert cache._layer_stores[0].asked == [("fused", (B, HK * G, D), 0.25)]
+
+    # with a mask: dense keys = old (dequantised) + new (exact), through the library's SDPA call
+    cache._layer_stores[0].asked.clear()
+    mask = torch.zeros(B, 1, 1, S)
+    mask[1, :, :, :2] = float("-inf")
+    out, _ = hf.turboquant_attention_forward(mod, q, k_new, v_new, mask, scaling=0.25)
+    k_all = torch.cat([old_k, k_new], 2).repeat_interleave(G, 1)
+    v_all = torch.cat([old_v, v_new], 2).repeat_interleave(G, 1)
+    want = torch.nn.functional.scaled_dot_product_attention(q, k_all, v_all, attn_mask=mask, scale=0.25).transpose(1, 2)
+    assert torch.allclose(out, want, atol=1e-5)
+    assert cache._layer_stores[0].asked == [("k", S - 1), ("v", S - 1)]
+
+    # prefill (several query tokens) and a module without a cache never touch the store
+    cache._layer_stores[0].asked.clear()
+    q3 = torch.randn(B, HK * G, 3, D, generator=gen)
+    k3, v3 = torch.randn(B, HK, 3, D, generator=gen), torch.randn(B, HK, 3, D, generator=gen)
+    hf.turboquant_attention_forward(mod, q3, k3, v3, None, scaling=0.25)
+    hf.turboquant_attention_forward(Module(), q, k_new, v_new, None, scaling=0.25)
+    cache.fused_attention = False
+    hf.turboquant_attention_forward(mod, q, k_new, v_new, None, scaling=0.25)
+    assert cache._layer_stores[0].asked == []
