@@ -27,6 +27,8 @@
 // scan_records_kernel is the same scan over the key-only records of tiled_layout.cuh (what TurboQuantIndex
 // stores): one table lookup per two codes, one MMA per 16 dims on the centroids' fp16 values, and eight
 // queries per pass as single fp16 columns for batched calls (four as hi + lo pairs for short calls).
+// A call with many query groups gives each group few, large CTAs in full waves (rec_ctas_per_group), and the
+// warps of a CTA share a threshold per query (the r-th best of every warp bounds what the CTA can emit).
 #include "common.cuh"
 #include "decode_bits.cuh"
 #include "pipe.cuh"
