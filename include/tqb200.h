@@ -251,6 +251,10 @@ int tqb_scan_topk(const float* queries, int nq, const uint8_t* packed, const flo
  * This is what TurboQuantIndex.search (turboquant_kv/search.py:206-227) runs on for dim 64 / 128 and
  * 2-4 bits.  records: ceil(n / 16) records, 16-byte aligned; rows n..16*ceil(n/16)-1 are ignored. */
 size_t tqb_scan_records_workspace_bytes(int nq, int dim, int bits, int k);
+/* Host-side planning figure, no device work: how many CTAs tqb_scan_records_topk gives each group of up to
+ * eight queries of a call with `groups` groups over n rows on a GPU of `sms` SMs (<= 0: the current device's).
+ * One group takes every SM; many groups take few, large CTAs each, in full waves, never fewer than two. */
+int tqb_scan_records_ctas_per_group(int groups, int64_t n, int sms);
 int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, int64_t n, int dim, int bits,
                           const float* rotation, const float* centroids, int k, int64_t id_offset,
                           void* workspace, size_t workspace_bytes, float* out_scores, int64_t* out_ids,

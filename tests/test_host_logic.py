@@ -308,3 +308,27 @@ def test_attention_function_dispatch_rules_with_a_stand_in_store():
     cache.fused_attention = False
     hf.turboquant_attention_forward(mod, q, k_new, v_new, None, scaling=0.25)
     assert cache._layer_stores[0].asked == []
+
+
+def test_scan_gives_query_groups_full_waves_of_few_large_ctas():
+    """The planning rule of the batched index scan: one group takes every SM; many groups take few CTAs each, the
+    whole grid a whole number of waves or nearly so, never fewer than two CTAs per group."""
+    lib = ctypes.CDLL(LIB)
+    f = lib.tqb_scan_records_ctas_per_group
+    f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]
+    sms = 148
+    assert f(1, 10_000_000, sms) == sms                       # a call of up to eight queries
+    assert f(2, 10_000_000, sms) == sms // 2                  # two groups side by side, one wave
+    assert f(5, 4_000_000, sms) == 29                         # 145 CTAs: one wave
+    assert f(64, 4_000_000, sms) == 2                         # 128 CTAs: one wave of large CTAs
+    assert f(1250, 10_000_000, sms) == 2                      # 10,000 queries
+    assert f(0, 1000, sms) == 0 and f(3, -1, sms) == 0
+    # the rule itself: waves of CTAs x (a CTA's share of the 16-row records + a fixed part worth 14,000 records)
+    def cost(groups, rows, x):
+        return -(-groups * x // sms) * (14_000 + -(-(-(-rows // 16)) // x))
+
+    for groups in range(1, 400, 7):
+        for rows in (1_000, 1_000_000, 10_000_000):
+            x = f(groups, rows, sms)
+            assert 2 <= x <= sms
+            assert cost(groups, rows, x) == min(cost(groups, rows, y) for y in range(2, sms + 1)), (groups, rows, x)

@@ -1214,6 +1214,11 @@ extern "C" size_t tqb_scan_records_workspace_bytes(int nq, int dim, int bits, in
     return tqb::plan_scan_records(nq, dim, bits, k).total;
 }
 
+extern "C" int tqb_scan_records_ctas_per_group(int groups, int64_t n, int sms) {
+    if (groups <= 0 || n < 0) return 0;
+    return tqb::rec_ctas_per_group(groups, tqb::ceil_div(n, (int64_t)16), sms > 0 ? sms : tqb::sm_count());
+}
+
 extern "C" int tqb_scan_records_topk(const float* queries, int nq, const uint8_t* records, int64_t n, int dim,
                                      int bits, const float* rotation, const float* centroids, int k,
                                      int64_t id_offset, void* workspace, size_t workspace_bytes,

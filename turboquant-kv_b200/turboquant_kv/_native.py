@@ -45,6 +45,8 @@ def lib():
         L.tqb_abi_version.restype = c_int
         L.tqb_decode_attention_workspace_bytes.restype = c_size_t
         L.tqb_decode_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int, c_int64]
+        L.tqb_scan_records_ctas_per_group.restype = c_int
+        L.tqb_scan_records_ctas_per_group.argtypes = [c_int, c_int64, c_int]
         L.tqb_scan_topk_workspace_bytes.restype = c_size_t
         L.tqb_scan_topk_workspace_bytes.argtypes = [c_int, c_int64, c_int, c_int, c_int]
         L.tqb_pack_codes.argtypes = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]
